@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the neighbourhood-attention hot path (fused forward + backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2]
+
+One "step" is one forward + one backward of the workload through the C ABI
+(``natten_fused_fwd`` + ``natten_fused_bwd``) on tensors already resident in HBM.
+Prints ONE JSON line (rank 0).  With N > 1 (launched by torchrun, one rank per
+GPU) every rank runs the same per-GPU workload on its own shard of the global
+batch -- the path has no exchange step, so there is no collective in the timed
+region; NCCL only carries the barrier and the max-over-ranks of the timings.
+
+``--impl reference`` times the CPU restatement of the reference's pure backend
+(``oracle/``) on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# name -> (rank, B, spatial, Hq, Hkv, D, kernel, dilation, stride, causal, dtype)
+WORKLOADS = {
+    "c2": dict(rank=2, B=8, spatial=(64, 64), Hq=8, Hkv=8, D=64, kernel=(7, 7), dilation=(1, 1),
+               stride=(1, 1), causal=(False, False), dtype="bf16",
+               desc="na2d bf16 fwd+bwd B=8 64x64 heads=8 head_dim=64 kernel=7x7"),
+    "c3": dict(rank=2, B=4, spatial=(128, 128), Hq=8, Hkv=8, D=64, kernel=(13, 13), dilation=(2, 2),
+               stride=(1, 1), causal=(False, False), dtype="bf16",
+               desc="na2d bf16 fwd+bwd B=4 128x128 heads=8 head_dim=64 kernel=13x13 dilation=2"),
+    "c4": dict(rank=3, B=2, spatial=(16, 32, 32), Hq=8, Hkv=8, D=64, kernel=(3, 7, 7),
+               dilation=(1, 1, 1), stride=(1, 1, 1), causal=(True, False, False), dtype="bf16",
+               desc="na3d bf16 fwd+bwd B=2 16x32x32 heads=8 head_dim=64 kernel=3x7x7 causal-D"),
+    "c1": dict(rank=1, B=2, spatial=(128,), Hq=4, Hkv=4, D=32, kernel=(7,), dilation=(1,),
+               stride=(1,), causal=(False,), dtype="f32",
+               desc="na1d fp32 fwd+bwd B=2 L=128 heads=4 head_dim=32 kernel=7"),
+}
+
+
+def mean_valid_keys(w) -> float:
+    """Average number of unmasked keys per query (only causal axes mask anything)."""
+    k_eff = 1.0
+    for L, K, dil, causal in zip(w["spatial"], w["kernel"], w["dilation"], w["causal"]):
+        if causal:
+            k_eff *= sum(min(K, p // dil + 1) for p in range(L)) / L
+        else:
+            k_eff *= K
+    return k_eff
+
+
+def algorithmic(w, batch):
+    """(flops fwd+bwd, bytes fwd, bytes bwd) of one step: 12*N_qh*K_eff*D flops; every
+    tensor touched once at its storage width, lse float32."""
+    n_tok = batch
+    for s in w["spatial"]:
+        n_tok *= s
+    esz = {"bf16": 2, "f16": 2, "f32": 4}[w["dtype"]]
+    n_qh = n_tok * w["Hq"]
+    flops = 12.0 * n_qh * mean_valid_keys(w) * w["D"]
+    q_bytes = n_tok * w["Hq"] * w["D"] * esz
+    kv_bytes = n_tok * w["Hkv"] * w["D"] * esz
+    lse_bytes = n_qh * 4
+    fwd = 2 * q_bytes + 2 * kv_bytes + lse_bytes                     # q, o, k, v, lse
+    bwd = 4 * q_bytes + 4 * kv_bytes + lse_bytes                     # q, o, do, dq, k, v, dk, dv, lse
+    return flops, fwd, bwd
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                     "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.rows.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._t.join(timeout=10)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle (port of the reference's pure backend) on the host cores
+# ---------------------------------------------------------------------------
+def cpu_port_run(w, steps, warmup, sample_batch):
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(0)
+    shp_q = (sample_batch, *w["spatial"], w["Hq"], w["D"])
+    shp_k = (sample_batch, *w["spatial"], w["Hkv"], w["D"])
+    q = rng.standard_normal(shp_q, dtype=np.float32)
+    k = rng.standard_normal(shp_k, dtype=np.float32)
+    v = rng.standard_normal(shp_k, dtype=np.float32)
+    go = rng.standard_normal(shp_q, dtype=np.float32)
+    kw = dict(kernel_size=w["kernel"], stride=w["stride"], dilation=w["dilation"], is_causal=w["causal"],
+              dtype=np.float32)
+
+    def step():
+        out, lse = oracle.na_forward(q, k, v, **kw)
+        oracle.na_backward(q, k, v, out, lse, go, **kw)
+
+    for _ in range(warmup):
+        step()
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    flops, _, _ = algorithmic(w, sample_batch)
+    sec = sum(times) / len(times)
+    return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"batch {sample_batch} of {w['B']} of the workload, float32, OpenMP over all host "
+                      f"cores, mean of {steps} step(s), {sec * 1e3:.1f} ms/step"}, sec
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 20))
+    cb, sec = cpu_port_run(w, steps, max(1, min(args.warmup, 2)), sample_batch=w["B"])
+    line = {
+        "impl": "reference", "metric": f"na{w['rank']}d fwd+bwd TFLOP/s", "value": cb["value"],
+        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps, "warmup": max(1, min(args.warmup, 2)),
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["desc"], "sample": cb["sample"]},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_ours(args, w):
+    import torch
+    from natten_mps_b200 import _backend, _cabi, functional as F
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the library has no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    tdt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[w["dtype"]]
+    B = w["B"]                                       # per-GPU batch (weak scaling)
+    g = torch.Generator(device="cpu").manual_seed(1000 + rank)
+    shp_q = (B, *w["spatial"], w["Hq"], w["D"])
+    shp_k = (B, *w["spatial"], w["Hkv"], w["D"])
+    host = [torch.randn(s, generator=g).to(tdt).pin_memory() for s in (shp_q, shp_k, shp_k, shp_q)]
+    q, k, v, go = [t.to(dev) for t in host]
+    geo = dict(kernel_size=w["kernel"], stride=w["stride"], dilation=w["dilation"], is_causal=w["causal"],
+               scale=w["D"] ** -0.5)
+
+    def step():
+        out, lse = _backend.fused_forward(q, k, v, **geo)
+        return _backend.fused_backward(q, k, v, out, lse, go, **geo)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sync_all()
+
+    # ---- device-resident timing: K steps between two events ------------------
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = _cabi.launch_count()
+    with ClockSampler(local) as clocks:
+        sync_all()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        sync_all()
+    launches = _cabi.launch_count() - launches0
+    ms_total = e0.elapsed_time(e1)
+    path = _cabi.last_path()
+
+    # ---- per-phase timing (forward kernel vs backward kernels) ---------------
+    fe = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    fwd_ms, bwd_ms = [], []
+    for _ in range(max(5, min(args.steps, 20))):
+        fe[0].record()
+        out, lse = _backend.fused_forward(q, k, v, **geo)
+        fe[1].record()
+        _backend.fused_backward(q, k, v, out, lse, go, **geo)
+        fe[2].record()
+        torch.cuda.synchronize()
+        fwd_ms.append(fe[0].elapsed_time(fe[1]))
+        bwd_ms.append(fe[1].elapsed_time(fe[2]))
+    fwd_t, bwd_t = statistics.median(fwd_ms), statistics.median(bwd_ms)
+
+    # ---- end to end through the public API with host buffers -----------------
+    fn = {1: F.na1d, 2: F.na2d, 3: F.na3d}[w["rank"]]
+    res_host = [torch.empty(s, dtype=tdt).pin_memory() for s in (shp_q, shp_k, shp_k)]
+
+    def e2e_step():
+        qd, kd, vd, gd = [t.to(dev, non_blocking=True) for t in host]
+        qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
+        o = fn(qd, kd, vd, kernel_size=w["kernel"], stride=w["stride"], dilation=w["dilation"],
+               is_causal=w["causal"])
+        o.backward(gd)
+        for dst, src in zip(res_host, (qd.grad, kd.grad, vd.grad)):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(3, min(args.steps, 10))
+    e2.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e3.record()
+    sync_all()
+    e2e_ms = e2.elapsed_time(e3) / e2e_steps
+
+    # ---- reduce over ranks ---------------------------------------------------
+    vals = torch.tensor([ms_total, e2e_ms, fwd_t, bwd_t], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms, fwd_t, bwd_t = vals.tolist()
+    ms_step = ms_total / args.steps
+    flops, fwd_bytes, bwd_bytes = algorithmic(w, B)
+    hbm_peak, tc_peak, which = measured_peaks()
+    dominant = ("backward", bwd_t, bwd_bytes) if bwd_t >= fwd_t else ("forward", fwd_t, fwd_bytes)
+    achieved = dominant[2] / (dominant[1] * 1e-3) / 1e9
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    d2h = sum(t.numel() * t.element_size() for t in res_host)
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            cpu, _ = cpu_port_run(w, steps=5, warmup=1, sample_batch=w["B"])
+        line = {
+            "metric": f"na{w['rank']}d fwd+bwd TFLOP/s", "value": world * flops / (ms_step * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": w["desc"], "per_gpu_batch": B, "global_batch": B * world,
+                       "sharding": "batch, no collective", "kernel_path": path,
+                       "l2": "working set per step (0.40 GB at c2) exceeds the 126 MB L2; no explicit flush",
+                       "algorithmic_gflop_per_step": flops / 1e9,
+                       "algorithmic_gb_per_step": (fwd_bytes + bwd_bytes) / 1e9},
+            "fwd_ms": fwd_t, "bwd_ms": bwd_t,
+            "roofline": {"bound": "hbm", "kernel": dominant[0], "achieved": achieved, "peak": hbm_peak,
+                         "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None,
+                         "peak_source": which,
+                         "step_frac": ((fwd_bytes + bwd_bytes) / (ms_step * 1e-3) / 1e9) / hbm_peak,
+                         "step_frac_nominal_8tbs": ((fwd_bytes + bwd_bytes) / (ms_step * 1e-3) / 1e9) / 8000.0},
+            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches,
+            "clocks": clocks.summary(),
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

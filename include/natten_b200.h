@@ -1,0 +1,124 @@
+/*
+ * natten_b200 -- C ABI of the B200 neighbourhood-attention library.
+ *
+ * Plain C: device pointers, sizes and a CUDA stream handle.  No PyTorch types.
+ * Every entry point is asynchronous on the given stream, allocates nothing,
+ * never synchronises, and returns 0 on success, a negative NATTEN_E_* code for
+ * a rejected argument, or a positive cudaError_t value.
+ *
+ * The reference (natten-mps) has no foreign-function interface: its backends
+ * are Python modules that implement the nine-function protocol of
+ * src/natten_mps/_core/ops.py:90-152.  Each function below names the protocol
+ * function(s) it stands in for; the Python package in this repository binds
+ * them with ctypes and re-creates that protocol on top.
+ *
+ * Tensor layout (heads last, same as the reference):
+ *   q      [B, *L, Hq,  D ]   strided: batch / token / head strides in elements,
+ *   k      [B, *L, Hkv, D ]            spatial axes collapsed to one token axis,
+ *   v      [B, *L, Hkv, Dv]            innermost axis contiguous
+ *   out    [B, *O, Hq,  Dv]   contiguous, O_a = ceil(L_a / stride_a)
+ *   lse    [B, *O, Hq]        contiguous, float (double when dtype is F64)
+ *   logits / attn [B, *O, Hq, prod(kernel)]  contiguous, slots row-major
+ *   extra_k [B, Ne, Hkv, D], extra_v [B, Ne, Hkv, Dv]  contiguous
+ *   gradients have the shape of what they differentiate and are contiguous.
+ */
+#ifndef NATTEN_B200_H
+#define NATTEN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { NATTEN_F32 = 0, NATTEN_F16 = 1, NATTEN_BF16 = 2, NATTEN_F64 = 3 };
+
+enum {
+    NATTEN_OK = 0,
+    NATTEN_E_INVALID = -1,      /* malformed params (rank, sizes, null pointers)   */
+    NATTEN_E_UNSUPPORTED = -2,  /* legal but outside what the kernels cover        */
+    NATTEN_E_WORKSPACE = -3,    /* workspace missing or too small                  */
+    NATTEN_E_DEVICE = -4        /* a kernel reported a bounded-wait timeout        */
+};
+
+enum {
+    NATTEN_FLAG_FORCE_SIMT = 1, /* skip the tensor-core kernels (tests compare)    */
+    NATTEN_FLAG_FORCE_TC = 2    /* fail with UNSUPPORTED instead of falling back   */
+};
+
+enum { NATTEN_OP_FUSED_FWD = 0, NATTEN_OP_FUSED_BWD = 1 };
+
+/* Which kernel family served the last call on this thread. */
+enum { NATTEN_PATH_NONE = 0, NATTEN_PATH_SIMT = 1, NATTEN_PATH_TCGEN05 = 2 };
+
+typedef struct natten_params {
+    int32_t rank;          /* 1, 2 or 3                                           */
+    int32_t dtype;         /* NATTEN_F32 / F16 / BF16 / F64                       */
+    int32_t batch, heads_q, heads_kv, dim, dim_v;
+    int32_t extent[3];     /* padded spatial sizes L_a (unused axes = 1)          */
+    int32_t kernel[3];     /* neighbourhood size per axis                         */
+    int32_t dilation[3];
+    int32_t stride[3];
+    int32_t causal[3];     /* 0 / 1 per axis                                      */
+    int32_t n_extra;       /* additional key/value tokens per sample (0 = none)   */
+    int32_t has_scale;     /* split QK only: 0 = return unscaled dot products     */
+    int32_t flags;         /* NATTEN_FLAG_*                                       */
+    float scale;           /* resolved logit scale                                */
+    int64_t q_stride[3];   /* batch, token, head strides of q (elements)          */
+    int64_t k_stride[3];
+    int64_t v_stride[3];
+    const int32_t* extents;/* device [batch, rank] per-sample sizes, or NULL      */
+} natten_params_t;
+
+/* Fused forward: softmax(scale * q k_n^T) v_n over each query's neighbourhood
+ * (plus the extra tokens, in the same softmax); writes out and lse.
+ * Stands in for na{1,2,3}d_forward of the backend protocol
+ * (src/natten_mps/_core/ops.py:90-96; oracle src/natten_mps/_core/pure.py:146-220,
+ * 397-433), for the additional-token merge of src/natten_mps/functional.py:285-295
+ * and for na{1,2,3}d_varlen_forward (src/natten_mps/_core/pure.py:573-673) when
+ * params->extents is set.                                                        */
+int natten_fused_fwd(const natten_params_t* params, const void* q, const void* k, const void* v,
+                     const void* extra_k, const void* extra_v, void* out, void* lse, void* stream);
+
+/* Fused backward: dq, dk, dv (and d_extra_k / d_extra_v) from dout and the
+ * optional dlse, without materialising the attention matrix.  Stands in for
+ * na{R}d_fused_backward of the accelerated backend
+ * (src/natten_mps/autograd/_factory.py:55-74) and for autograd through the pure
+ * backend (src/natten_mps/autograd/_factory.py:95-102).  `workspace` must hold
+ * natten_workspace_bytes(params, NATTEN_OP_FUSED_BWD) bytes.                      */
+int natten_fused_bwd(const natten_params_t* params, const void* q, const void* k, const void* v,
+                     const void* extra_k, const void* extra_v, const void* out, const void* lse,
+                     const void* dout, const void* dlse, void* dq, void* dk, void* dv,
+                     void* dextra_k, void* dextra_v, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
+/* Scratch bytes an op needs (0 when none). */
+size_t natten_workspace_bytes(const natten_params_t* params, int op);
+
+/* Split QK forward / backward: na{R}d_qk_forward / na{R}d_qk_backward
+ * (src/natten_mps/_core/ops.py:98-110, 126-138; oracle _core/pure.py:223-254,
+ * 294-332, 436-471).  Masked slots hold -inf (times scale when has_scale).       */
+int natten_qk_fwd(const natten_params_t* params, const void* q, const void* k, void* logits,
+                  void* stream);
+int natten_qk_bwd(const natten_params_t* params, const void* q, const void* k,
+                  const void* dlogits, void* dq, void* dk, void* stream);
+
+/* Split AV forward / backward: na{R}d_av_forward / na{R}d_av_backward
+ * (src/natten_mps/_core/ops.py:112-124, 140-152; oracle _core/pure.py:257-291,
+ * 520-565, 474-517).  heads_q/dim describe attn's head count; dim is unused.     */
+int natten_av_fwd(const natten_params_t* params, const void* attn, const void* v, void* out,
+                  void* stream);
+int natten_av_bwd(const natten_params_t* params, const void* attn, const void* v,
+                  const void* dout, void* dattn, void* dv, void* stream);
+
+/* Diagnostics. */
+const char* natten_strerror(int code);
+int natten_abi_version(void);
+int natten_last_path(void);              /* NATTEN_PATH_* of the last call, this thread */
+unsigned long long natten_launch_count(void); /* kernels launched by this library so far */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NATTEN_B200_H */

@@ -1,0 +1,921 @@
+// SIMT kernels: the all-feature path (every rank, dtype, head dim, kernel size,
+// stride, dilation, per-axis causal, GQA, additional tokens, per-sample extents).
+// They serve fp32 / fp64 (where tensor cores would break the 1e-5 parity bound),
+// shapes the tcgen05 kernels do not cover, and the split QK / AV ops.
+//
+// Mapping: one warp per (query, head) for query-centric work and one warp per
+// (key, kv head) for the inverse-neighbourhood work.  Inside a warp the score
+// phase runs lane-per-neighbour (each lane a full dot product, rows read with
+// 16-byte loads) and the accumulate phase runs lane-per-channel (coalesced row
+// reads, the weight broadcast by shuffle), so no per-neighbour warp reduction
+// is needed.  dK/dV are gathered per key in a fixed order: no float atomics,
+// results are bit-reproducible.
+#include "simt_kernels.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+namespace natten {
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr unsigned kFull = 0xffffffffu;
+
+template <typename T> struct AccOf { using type = float; };
+template <> struct AccOf<double> { using type = double; };
+
+__device__ __forceinline__ float to_acc(float x) { return x; }
+__device__ __forceinline__ float to_acc(__half x) { return __half2float(x); }
+__device__ __forceinline__ float to_acc(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ double to_acc(double x) { return x; }
+
+template <typename T, typename A> __device__ __forceinline__ T from_acc(A x);
+template <> __device__ __forceinline__ float from_acc<float, float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_acc<__half, float>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16, float>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ double from_acc<double, double>(double x) { return x; }
+
+__device__ __forceinline__ float exp_acc(float x) { return expf(x); }
+__device__ __forceinline__ double exp_acc(double x) { return exp(x); }
+__device__ __forceinline__ float log_acc(float x) { return logf(x); }
+__device__ __forceinline__ double log_acc(double x) { return log(x); }
+template <typename A> __device__ __forceinline__ A neg_inf();
+template <> __device__ __forceinline__ float neg_inf<float>() { return -CUDART_INF_F; }
+template <> __device__ __forceinline__ double neg_inf<double>() { return -CUDART_INF; }
+
+template <typename A> __device__ __forceinline__ A warp_max(A v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { A t = __shfl_xor_sync(kFull, v, o); v = t > v ? t : v; }
+    return v;
+}
+template <typename A> __device__ __forceinline__ A warp_sum(A v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+    return v;
+}
+template <typename P> __device__ __forceinline__ const P* shfl_ptr(const P* p, int src)
+{
+    return reinterpret_cast<const P*>(__shfl_sync(kFull, reinterpret_cast<unsigned long long>(p), src));
+}
+
+// dot(staged[0..n), row[0..n)) with 16-byte row loads when the launch allows it.
+template <typename T, typename A>
+__device__ __forceinline__ A dot_row(const A* __restrict__ staged, const T* __restrict__ row, int n, int vec_ok)
+{
+    constexpr int V = 16 / sizeof(T);
+    A acc = 0;
+    if (vec_ok) {
+        for (int d = 0; d < n; d += V) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(row + d);
+            const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc += staged[d + i] * to_acc(e[i]);
+        }
+    } else {
+        for (int d = 0; d < n; ++d) acc += staged[d] * to_acc(row[d]);
+    }
+    return acc;
+}
+
+struct QueryCtx {
+    int b, h, hk;
+    long long row;      // (b*otot + o)*Hq + h
+    long long pflat;    // flat input position of the query
+    int Ls[3], first[3];
+    bool inside;
+};
+
+__device__ __forceinline__ void decode_query(const Geo& g, long long row, QueryCtx& c)
+{
+    c.row = row;
+    c.h = (int)(row % g.Hq);
+    long long bo = row / g.Hq;
+    long long o = bo % g.otot;
+    c.b = (int)(bo / g.otot);
+    c.hk = c.h / g.group;
+    c.inside = true;
+    int pos[3] = {0, 0, 0};
+    for (int a = g.rank - 1; a >= 0; --a) {
+        pos[a] = (int)(o % g.O[a]) * g.st[a];
+        o /= g.O[a];
+        c.Ls[a] = g.extents ? g.extents[c.b * g.rank + a] : g.L[a];
+        if (pos[a] >= c.Ls[a]) c.inside = false;
+    }
+    c.pflat = 0;
+    for (int a = 0; a < g.rank; ++a) {
+        c.pflat = c.pflat * g.L[a] + pos[a];
+        c.first[a] = c.inside ? axis_first_key(pos[a], c.Ls[a], g.K[a], g.dil[a], g.causal[a]) : 0;
+    }
+}
+
+// Flat key position of neighbour slot j (row-major over the per-axis slots).
+__device__ __forceinline__ bool slot_key(const Geo& g, const QueryCtx& c, int j, long long& kflat)
+{
+    int kk[3] = {0, 0, 0};
+    for (int a = g.rank - 1; a >= 0; --a) { kk[a] = j % g.K[a]; j /= g.K[a]; }
+    bool valid = true;
+    kflat = 0;
+    for (int a = 0; a < g.rank; ++a) {
+        const int pos = c.first[a] + kk[a] * g.dil[a];
+        valid = valid && pos >= 0 && pos < c.Ls[a];
+        kflat = kflat * g.L[a] + pos;
+    }
+    return valid;
+}
+
+struct KeyCtx {
+    int b, hk;
+    long long nflat;
+    int n[3], Ls[3], base[3], cnt[3];
+    int ncand;          // candidate queries (positions) of this key
+    bool inside;
+};
+
+__device__ __forceinline__ void decode_key(const Geo& g, long long row, KeyCtx& c)
+{
+    c.hk = (int)(row % g.Hkv);
+    long long bn = row / g.Hkv;
+    c.nflat = bn % g.ltot;
+    c.b = (int)(bn / g.ltot);
+    long long n = c.nflat;
+    c.inside = true;
+    c.ncand = 1;
+    for (int a = g.rank - 1; a >= 0; --a) {
+        c.n[a] = (int)(n % g.L[a]);
+        n /= g.L[a];
+        c.Ls[a] = g.extents ? g.extents[c.b * g.rank + a] : g.L[a];
+        if (c.n[a] >= c.Ls[a]) c.inside = false;
+    }
+    for (int a = 0; a < 3; ++a) { c.base[a] = 0; c.cnt[a] = 1; }
+    if (c.inside)
+        for (int a = 0; a < g.rank; ++a) {
+            axis_candidates(c.n[a], c.Ls[a], g.K[a], g.dil[a], g.causal[a], c.base[a], c.cnt[a]);
+            c.ncand *= c.cnt[a];
+        }
+}
+
+// Candidate t (position index inside the candidate box) -> does that query attend
+// to this key?  Returns the query's flat output index, flat input position and slot.
+__device__ __forceinline__ bool candidate(const Geo& g, const KeyCtx& c, int t,
+                                          long long& oflat, long long& pflat, int& slot)
+{
+    int tt[3] = {0, 0, 0};
+    for (int a = g.rank - 1; a >= 0; --a) { tt[a] = t % c.cnt[a]; t /= c.cnt[a]; }
+    bool valid = true;
+    oflat = 0; pflat = 0; slot = 0;
+    for (int a = 0; a < g.rank; ++a) {
+        const int p = c.base[a] + tt[a] * g.dil[a];
+        if (p % g.st[a] != 0) valid = false;
+        const int s = axis_slot(p, c.n[a], c.Ls[a], g.K[a], g.dil[a], g.causal[a]);
+        if (s < 0) valid = false;
+        oflat = oflat * g.O[a] + p / g.st[a];
+        pflat = pflat * g.L[a] + p;
+        slot = slot * g.K[a] + s;
+    }
+    return valid;
+}
+
+// ---------------------------------------------------------------------------
+// Fused forward
+// ---------------------------------------------------------------------------
+template <typename T, int NDV>
+__global__ void __launch_bounds__(kWarps * 32)
+fused_fwd_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T* __restrict__ k,
+                 const T* __restrict__ v, const T* __restrict__ ek, const T* __restrict__ ev,
+                 T* __restrict__ out, typename AccOf<T>::type* __restrict__ lse, long long rows)
+{
+    using A = typename AccOf<T>::type;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    A* qsh = reinterpret_cast<A*>(smem_raw) + (size_t)warp * g.D;
+    const long long row = (long long)blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    QueryCtx c;
+    decode_query(g, row, c);
+    T* orow = out + row * g.Dv;
+    if (!c.inside) {
+        for (int d = lane; d < g.Dv; d += 32) orow[d] = from_acc<T, A>(A(0));
+        if (lane == 0) lse[row] = A(0);
+        return;
+    }
+    const T* qrow = q + c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
+    for (int d = lane; d < g.D; d += 32) qsh[d] = to_acc(qrow[d]);
+    __syncwarp();
+
+    A m = neg_inf<A>(), l = 0;
+    A acc[NDV];
+#pragma unroll
+    for (int i = 0; i < NDV; ++i) acc[i] = 0;
+    const int ntot = g.ktot + g.n_extra;
+    const A scale = (A)g.scale;
+    for (int base = 0; base < ntot; base += 32) {
+        const int j = base + lane;
+        const T* krow = nullptr;
+        const T* vrow = nullptr;
+        bool valid = false;
+        if (j < g.ktot) {
+            long long kf;
+            valid = slot_key(g, c, j, kf);
+            if (valid) {
+                krow = k + c.b * g.ks[0] + kf * g.ks[1] + c.hk * g.ks[2];
+                vrow = v + c.b * g.vs[0] + kf * g.vs[1] + c.hk * g.vs[2];
+            }
+        } else if (j < ntot) {
+            const long long e = ((long long)c.b * g.n_extra + (j - g.ktot)) * g.Hkv + c.hk;
+            krow = ek + e * g.D;
+            vrow = ev + e * g.Dv;
+            valid = true;
+        }
+        A s = neg_inf<A>();
+        if (valid) s = dot_row<T, A>(qsh, krow, g.D, g.vec_ok) * scale;
+        const A mx = warp_max(s);
+        const A m_new = mx > m ? mx : m;
+        if (m_new == neg_inf<A>()) continue;          // nothing valid yet
+        const A alpha = (m == neg_inf<A>()) ? A(0) : exp_acc(m - m_new);
+        const A p = valid ? exp_acc(s - m_new) : A(0);
+        l = l * alpha + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < NDV; ++i) acc[i] *= alpha;
+        m = m_new;
+        unsigned mask = __ballot_sync(kFull, valid);
+        while (mask) {
+            const int src = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const A pj = __shfl_sync(kFull, p, src);
+            const T* vr = shfl_ptr(vrow, src);
+#pragma unroll
+            for (int i = 0; i < NDV; ++i) {
+                const int d = lane + 32 * i;
+                if (d < g.Dv) acc[i] += pj * to_acc(vr[d]);
+            }
+        }
+    }
+    const A inv = A(1) / l;
+#pragma unroll
+    for (int i = 0; i < NDV; ++i) {
+        const int d = lane + 32 * i;
+        if (d < g.Dv) orow[d] = from_acc<T, A>(acc[i] * inv);
+    }
+    if (lane == 0) lse[row] = m + log_acc(l);
+}
+
+// delta[row] = sum_d out[row,d] * dout[row,d]
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+delta_kernel(const T* __restrict__ out, const T* __restrict__ dout,
+             typename AccOf<T>::type* __restrict__ delta, long long rows, int Dv)
+{
+    using A = typename AccOf<T>::type;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    A acc = 0;
+    for (int d = lane; d < Dv; d += 32) acc += to_acc(out[row * Dv + d]) * to_acc(dout[row * Dv + d]);
+    acc = warp_sum(acc);
+    if (lane == 0) delta[row] = acc;
+}
+
+// ---------------------------------------------------------------------------
+// Fused backward, query side: dQ
+// ---------------------------------------------------------------------------
+template <typename T, int ND>
+__global__ void __launch_bounds__(kWarps * 32)
+fused_bwd_dq_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T* __restrict__ k,
+                    const T* __restrict__ v, const T* __restrict__ ek, const T* __restrict__ ev,
+                    const typename AccOf<T>::type* __restrict__ lse,
+                    const typename AccOf<T>::type* __restrict__ delta,
+                    const T* __restrict__ dout, const typename AccOf<T>::type* __restrict__ dlse,
+                    T* __restrict__ dq, long long rows)
+{
+    using A = typename AccOf<T>::type;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    A* qsh = reinterpret_cast<A*>(smem_raw) + (size_t)warp * (g.D + g.Dv);
+    A* dosh = qsh + g.D;
+    const long long row = (long long)blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    QueryCtx c;
+    decode_query(g, row, c);
+    if (!c.inside) return;                       // dq was zero-filled by the launcher
+    const T* qrow = q + c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
+    for (int d = lane; d < g.D; d += 32) qsh[d] = to_acc(qrow[d]);
+    for (int d = lane; d < g.Dv; d += 32) dosh[d] = to_acc(dout[row * g.Dv + d]);
+    __syncwarp();
+    const A lse_i = lse[row];
+    const A extra = (dlse ? dlse[row] : A(0)) - delta[row];
+    const A scale = (A)g.scale;
+    A acc[ND];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acc[i] = 0;
+    const int ntot = g.ktot + g.n_extra;
+    for (int base = 0; base < ntot; base += 32) {
+        const int j = base + lane;
+        const T* krow = nullptr;
+        const T* vrow = nullptr;
+        bool valid = false;
+        if (j < g.ktot) {
+            long long kf;
+            valid = slot_key(g, c, j, kf);
+            if (valid) {
+                krow = k + c.b * g.ks[0] + kf * g.ks[1] + c.hk * g.ks[2];
+                vrow = v + c.b * g.vs[0] + kf * g.vs[1] + c.hk * g.vs[2];
+            }
+        } else if (j < ntot) {
+            const long long e = ((long long)c.b * g.n_extra + (j - g.ktot)) * g.Hkv + c.hk;
+            krow = ek + e * g.D;
+            vrow = ev + e * g.Dv;
+            valid = true;
+        }
+        A ds = 0;
+        if (valid) {
+            const A s = dot_row<T, A>(qsh, krow, g.D, g.vec_ok) * scale;
+            const A p = exp_acc(s - lse_i);
+            const A dp = dot_row<T, A>(dosh, vrow, g.Dv, g.vec_ok);
+            ds = p * (dp + extra) * scale;
+        }
+        unsigned mask = __ballot_sync(kFull, valid);
+        while (mask) {
+            const int src = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const A dsj = __shfl_sync(kFull, ds, src);
+            const T* kr = shfl_ptr(krow, src);
+#pragma unroll
+            for (int i = 0; i < ND; ++i) {
+                const int d = lane + 32 * i;
+                if (d < g.D) acc[i] += dsj * to_acc(kr[d]);
+            }
+        }
+    }
+    T* dqrow = dq + ((long long)c.b * g.ltot + c.pflat) * g.Hq * g.D + (long long)c.h * g.D;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+        const int d = lane + 32 * i;
+        if (d < g.D) dqrow[d] = from_acc<T, A>(acc[i]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Fused backward, key side: dK and dV gathered over the inverse neighbourhood
+// ---------------------------------------------------------------------------
+template <typename T, int ND, int NDV>
+__global__ void __launch_bounds__(kWarps * 32)
+fused_bwd_dkdv_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T* __restrict__ k,
+                      const T* __restrict__ v, const typename AccOf<T>::type* __restrict__ lse,
+                      const typename AccOf<T>::type* __restrict__ delta, const T* __restrict__ dout,
+                      const typename AccOf<T>::type* __restrict__ dlse,
+                      T* __restrict__ dk, T* __restrict__ dv, long long rows)
+{
+    using A = typename AccOf<T>::type;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    A* ksh = reinterpret_cast<A*>(smem_raw) + (size_t)warp * (g.D + g.Dv);
+    A* vsh = ksh + g.D;
+    const long long row = (long long)blockIdx.x * kWarps + warp;   // (b*ltot + n)*Hkv + hk
+    if (row >= rows) return;
+    KeyCtx c;
+    decode_key(g, row, c);
+    T* dkrow = dk + row * g.D;
+    T* dvrow = dv + row * g.Dv;
+    if (!c.inside) {
+        for (int d = lane; d < g.D; d += 32) dkrow[d] = from_acc<T, A>(A(0));
+        for (int d = lane; d < g.Dv; d += 32) dvrow[d] = from_acc<T, A>(A(0));
+        return;
+    }
+    const T* krow = k + c.b * g.ks[0] + c.nflat * g.ks[1] + c.hk * g.ks[2];
+    const T* vrow = v + c.b * g.vs[0] + c.nflat * g.vs[1] + c.hk * g.vs[2];
+    for (int d = lane; d < g.D; d += 32) ksh[d] = to_acc(krow[d]);
+    for (int d = lane; d < g.Dv; d += 32) vsh[d] = to_acc(vrow[d]);
+    __syncwarp();
+    const A scale = (A)g.scale;
+    A acck[ND], accv[NDV];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acck[i] = 0;
+#pragma unroll
+    for (int i = 0; i < NDV; ++i) accv[i] = 0;
+    const int total = c.ncand * g.group;
+    for (int base = 0; base < total; base += 32) {
+        const int cnd = base + lane;
+        bool valid = false;
+        const T* qrow = nullptr;
+        const T* dorow = nullptr;
+        A p = 0, ds = 0;
+        if (cnd < total) {
+            const int gi = cnd / c.ncand, t = cnd % c.ncand;
+            long long oflat, pflat; int slot;
+            valid = candidate(g, c, t, oflat, pflat, slot);
+            if (valid) {
+                const int h = c.hk * g.group + gi;
+                const long long r = ((long long)c.b * g.otot + oflat) * g.Hq + h;
+                qrow = q + c.b * g.qs[0] + pflat * g.qs[1] + h * g.qs[2];
+                dorow = dout + r * g.Dv;
+                const A s = dot_row<T, A>(ksh, qrow, g.D, g.vec_ok) * scale;
+                p = exp_acc(s - lse[r]);
+                const A dp = dot_row<T, A>(vsh, dorow, g.Dv, g.vec_ok);
+                ds = p * (dp - delta[r] + (dlse ? dlse[r] : A(0))) * scale;
+            }
+        }
+        unsigned mask = __ballot_sync(kFull, valid);
+        while (mask) {
+            const int src = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const A dsj = __shfl_sync(kFull, ds, src);
+            const A pj = __shfl_sync(kFull, p, src);
+            const T* qr = shfl_ptr(qrow, src);
+            const T* dor = shfl_ptr(dorow, src);
+#pragma unroll
+            for (int i = 0; i < ND; ++i) {
+                const int d = lane + 32 * i;
+                if (d < g.D) acck[i] += dsj * to_acc(qr[d]);
+            }
+#pragma unroll
+            for (int i = 0; i < NDV; ++i) {
+                const int d = lane + 32 * i;
+                if (d < g.Dv) accv[i] += pj * to_acc(dor[d]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+        const int d = lane + 32 * i;
+        if (d < g.D) dkrow[d] = from_acc<T, A>(acck[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < NDV; ++i) {
+        const int d = lane + 32 * i;
+        if (d < g.Dv) dvrow[d] = from_acc<T, A>(accv[i]);
+    }
+}
+
+// Gradients of the additional tokens: every query of the sample (and every
+// query head of the group) attends to them.  One block per (b, e, hk); warps
+// stride over the queries and are reduced in a fixed order through shared memory.
+template <typename T, int ND, int NDV>
+__global__ void __launch_bounds__(kWarps * 32)
+fused_bwd_extra_kernel(const __grid_constant__ Geo g, const T* __restrict__ q,
+                       const T* __restrict__ ek, const T* __restrict__ ev,
+                       const typename AccOf<T>::type* __restrict__ lse,
+                       const typename AccOf<T>::type* __restrict__ delta, const T* __restrict__ dout,
+                       const typename AccOf<T>::type* __restrict__ dlse,
+                       T* __restrict__ dek, T* __restrict__ dev)
+{
+    using A = typename AccOf<T>::type;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    A* ksh = reinterpret_cast<A*>(smem_raw);               // D + Dv staged once per block
+    A* vsh = ksh + g.D;
+    A* red = vsh + g.Dv;                                   // kWarps * (D + Dv)
+    const long long row = blockIdx.x;                      // (b*Ne + e)*Hkv + hk
+    const int hk = (int)(row % g.Hkv);
+    const int b = (int)(row / ((long long)g.Hkv * g.n_extra));
+    for (int d = threadIdx.x; d < g.D; d += blockDim.x) ksh[d] = to_acc(ek[row * g.D + d]);
+    for (int d = threadIdx.x; d < g.Dv; d += blockDim.x) vsh[d] = to_acc(ev[row * g.Dv + d]);
+    __syncthreads();
+    const A scale = (A)g.scale;
+    A acck[ND], accv[NDV];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acck[i] = 0;
+#pragma unroll
+    for (int i = 0; i < NDV; ++i) accv[i] = 0;
+    const long long total = g.otot * g.group;
+    for (long long base = (long long)warp * 32; base < total; base += kWarps * 32) {
+        const long long cnd = base + lane;
+        bool valid = false;
+        const T* qrow = nullptr;
+        const T* dorow = nullptr;
+        A p = 0, ds = 0;
+        if (cnd < total) {
+            const int gi = (int)(cnd / g.otot);
+            const int h = hk * g.group + gi;
+            QueryCtx c;
+            decode_query(g, ((long long)b * g.otot + cnd % g.otot) * g.Hq + h, c);
+            valid = c.inside;
+            if (valid) {
+                qrow = q + c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
+                dorow = dout + c.row * g.Dv;
+                const A s = dot_row<T, A>(ksh, qrow, g.D, g.vec_ok) * scale;
+                p = exp_acc(s - lse[c.row]);
+                const A dp = dot_row<T, A>(vsh, dorow, g.Dv, g.vec_ok);
+                ds = p * (dp - delta[c.row] + (dlse ? dlse[c.row] : A(0))) * scale;
+            }
+        }
+        unsigned mask = __ballot_sync(kFull, valid);
+        while (mask) {
+            const int src = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const A dsj = __shfl_sync(kFull, ds, src);
+            const A pj = __shfl_sync(kFull, p, src);
+            const T* qr = shfl_ptr(qrow, src);
+            const T* dor = shfl_ptr(dorow, src);
+#pragma unroll
+            for (int i = 0; i < ND; ++i) {
+                const int d = lane + 32 * i;
+                if (d < g.D) acck[i] += dsj * to_acc(qr[d]);
+            }
+#pragma unroll
+            for (int i = 0; i < NDV; ++i) {
+                const int d = lane + 32 * i;
+                if (d < g.Dv) accv[i] += pj * to_acc(dor[d]);
+            }
+        }
+    }
+    A* mine = red + (size_t)warp * (g.D + g.Dv);
+#pragma unroll
+    for (int i = 0; i < ND; ++i) { const int d = lane + 32 * i; if (d < g.D) mine[d] = acck[i]; }
+#pragma unroll
+    for (int i = 0; i < NDV; ++i) { const int d = lane + 32 * i; if (d < g.Dv) mine[g.D + d] = accv[i]; }
+    __syncthreads();
+    for (int d = threadIdx.x; d < g.D + g.Dv; d += blockDim.x) {
+        A s = 0;
+        for (int w = 0; w < kWarps; ++w) s += red[(size_t)w * (g.D + g.Dv) + d];
+        if (d < g.D) dek[row * g.D + d] = from_acc<T, A>(s);
+        else dev[row * g.Dv + (d - g.D)] = from_acc<T, A>(s);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Split QK
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+qk_fwd_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T* __restrict__ k,
+              T* __restrict__ logits, long long rows)
+{
+    using A = typename AccOf<T>::type;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    A* qsh = reinterpret_cast<A*>(smem_raw) + (size_t)warp * g.D;
+    const long long row = (long long)blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    QueryCtx c;
+    decode_query(g, row, c);
+    const T* qrow = q + c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
+    for (int d = lane; d < g.D; d += 32) qsh[d] = to_acc(qrow[d]);
+    __syncwarp();
+    for (int j = lane; j < g.ktot; j += 32) {
+        long long kf;
+        A val = neg_inf<A>();
+        if (slot_key(g, c, j, kf))
+            val = dot_row<T, A>(qsh, k + c.b * g.ks[0] + kf * g.ks[1] + c.hk * g.ks[2], g.D, g.vec_ok);
+        if (g.has_scale) val *= (A)g.scale;
+        logits[row * g.ktot + j] = from_acc<T, A>(val);
+    }
+}
+
+template <typename T, int ND>
+__global__ void __launch_bounds__(kWarps * 32)
+qk_bwd_dq_kernel(const __grid_constant__ Geo g, const T* __restrict__ k, const T* __restrict__ dlogits,
+                 T* __restrict__ dq, long long rows)
+{
+    using A = typename AccOf<T>::type;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    QueryCtx c;
+    decode_query(g, row, c);
+    const A scale = g.has_scale ? (A)g.scale : A(1);
+    A acc[ND];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acc[i] = 0;
+    for (int j = 0; j < g.ktot; ++j) {
+        long long kf;
+        if (!slot_key(g, c, j, kf)) continue;               // warp-uniform
+        const A w = to_acc(dlogits[row * g.ktot + j]) * scale;
+        const T* kr = k + c.b * g.ks[0] + kf * g.ks[1] + c.hk * g.ks[2];
+#pragma unroll
+        for (int i = 0; i < ND; ++i) {
+            const int d = lane + 32 * i;
+            if (d < g.D) acc[i] += w * to_acc(kr[d]);
+        }
+    }
+    T* dqrow = dq + ((long long)c.b * g.ltot + c.pflat) * g.Hq * g.D + (long long)c.h * g.D;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+        const int d = lane + 32 * i;
+        if (d < g.D) dqrow[d] = from_acc<T, A>(acc[i]);
+    }
+}
+
+// dK (QK backward) and dV (AV backward) share one gather: for every query that
+// attends to the key, weight[query, slot] * row[query].
+template <typename T, int ND>
+__global__ void __launch_bounds__(kWarps * 32)
+inverse_gather_kernel(const __grid_constant__ Geo g, const T* __restrict__ weights,
+                      const T* __restrict__ rows_src, long long src_bs, long long src_ts, long long src_hs,
+                      int src_is_query_input, int width, float wscale, T* __restrict__ dst, long long rows)
+{
+    using A = typename AccOf<T>::type;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * kWarps + warp;   // (b*ltot + n)*Hkv + hk
+    if (row >= rows) return;
+    KeyCtx c;
+    decode_key(g, row, c);
+    A acc[ND];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acc[i] = 0;
+    const int total = c.inside ? c.ncand * g.group : 0;
+    for (int base = 0; base < total; base += 32) {
+        const int cnd = base + lane;
+        bool valid = false;
+        const T* src = nullptr;
+        A w = 0;
+        if (cnd < total) {
+            const int gi = cnd / c.ncand, t = cnd % c.ncand;
+            long long oflat, pflat; int slot;
+            valid = candidate(g, c, t, oflat, pflat, slot);
+            if (valid) {
+                const int h = c.hk * g.group + gi;
+                const long long r = ((long long)c.b * g.otot + oflat) * g.Hq + h;
+                w = to_acc(weights[r * g.ktot + slot]) * (A)wscale;
+                // source row: q (indexed by input position, strided) or dout (by output row)
+                src = src_is_query_input ? rows_src + c.b * src_bs + pflat * src_ts + h * src_hs
+                                         : rows_src + r * (long long)width;
+            }
+        }
+        unsigned mask = __ballot_sync(kFull, valid);
+        while (mask) {
+            const int s = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const A wj = __shfl_sync(kFull, w, s);
+            const T* sr = shfl_ptr(src, s);
+#pragma unroll
+            for (int i = 0; i < ND; ++i) {
+                const int d = lane + 32 * i;
+                if (d < width) acc[i] += wj * to_acc(sr[d]);
+            }
+        }
+    }
+    T* drow = dst + row * width;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+        const int d = lane + 32 * i;
+        if (d < width) drow[d] = from_acc<T, A>(acc[i]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Split AV
+// ---------------------------------------------------------------------------
+template <typename T, int NDV>
+__global__ void __launch_bounds__(kWarps * 32)
+av_fwd_kernel(const __grid_constant__ Geo g, const T* __restrict__ attn, const T* __restrict__ v,
+              T* __restrict__ out, long long rows)
+{
+    using A = typename AccOf<T>::type;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    QueryCtx c;
+    decode_query(g, row, c);
+    A acc[NDV];
+#pragma unroll
+    for (int i = 0; i < NDV; ++i) acc[i] = 0;
+    for (int j = 0; j < g.ktot; ++j) {
+        long long kf;
+        if (!slot_key(g, c, j, kf)) continue;
+        const A w = to_acc(attn[row * g.ktot + j]);
+        const T* vr = v + c.b * g.vs[0] + kf * g.vs[1] + c.hk * g.vs[2];
+#pragma unroll
+        for (int i = 0; i < NDV; ++i) {
+            const int d = lane + 32 * i;
+            if (d < g.Dv) acc[i] += w * to_acc(vr[d]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NDV; ++i) {
+        const int d = lane + 32 * i;
+        if (d < g.Dv) out[row * g.Dv + d] = from_acc<T, A>(acc[i]);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+av_bwd_dattn_kernel(const __grid_constant__ Geo g, const T* __restrict__ v, const T* __restrict__ dout,
+                    T* __restrict__ dattn, long long rows)
+{
+    using A = typename AccOf<T>::type;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    A* dosh = reinterpret_cast<A*>(smem_raw) + (size_t)warp * g.Dv;
+    const long long row = (long long)blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    QueryCtx c;
+    decode_query(g, row, c);
+    for (int d = lane; d < g.Dv; d += 32) dosh[d] = to_acc(dout[row * g.Dv + d]);
+    __syncwarp();
+    for (int j = lane; j < g.ktot; j += 32) {
+        long long kf;
+        A val = 0;
+        if (slot_key(g, c, j, kf))
+            val = dot_row<T, A>(dosh, v + c.b * g.vs[0] + kf * g.vs[1] + c.hk * g.vs[2], g.Dv, g.vec_ok);
+        dattn[row * g.ktot + j] = from_acc<T, A>(val);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Launch helpers
+// ---------------------------------------------------------------------------
+unsigned long long g_launches = 0;
+
+inline unsigned grid_for(long long rows) { return (unsigned)((rows + kWarps - 1) / kWarps); }
+
+#define NATTEN_DISPATCH_N(n, NAME, ...)                                     \
+    do {                                                                    \
+        if ((n) <= 32) { constexpr int NAME = 1; __VA_ARGS__; }             \
+        else if ((n) <= 64) { constexpr int NAME = 2; __VA_ARGS__; }        \
+        else if ((n) <= 128) { constexpr int NAME = 4; __VA_ARGS__; }       \
+        else { constexpr int NAME = 8; __VA_ARGS__; }                       \
+    } while (0)
+
+template <typename T>
+cudaError_t fused_fwd_t(const Geo& g, const void* q, const void* k, const void* v, const void* ek,
+                        const void* ev, void* out, void* lse, cudaStream_t s)
+{
+    using A = typename AccOf<T>::type;
+    const long long rows = (long long)g.B * g.otot * g.Hq;
+    if (rows == 0) return cudaSuccess;
+    const size_t smem = (size_t)kWarps * g.D * sizeof(A);
+    NATTEN_DISPATCH_N(g.Dv, NDV,
+        fused_fwd_kernel<T, NDV><<<grid_for(rows), kWarps * 32, smem, s>>>(
+            g, (const T*)q, (const T*)k, (const T*)v, (const T*)ek, (const T*)ev, (T*)out, (A*)lse, rows));
+    ++g_launches;
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t fused_bwd_t(const Geo& g, const void* q, const void* k, const void* v, const void* ek,
+                        const void* ev, const void* out, const void* lse, const void* dout,
+                        const void* dlse, void* dq, void* dk, void* dv, void* dek, void* dev,
+                        void* workspace, cudaStream_t s)
+{
+    using A = typename AccOf<T>::type;
+    const long long qrows = (long long)g.B * g.otot * g.Hq;
+    const long long krows = (long long)g.B * g.ltot * g.Hkv;
+    A* delta = (A*)workspace;
+    cudaError_t err;
+    bool dq_partial = g.extents != nullptr;
+    for (int a = 0; a < g.rank; ++a) dq_partial = dq_partial || g.st[a] != 1;
+    if (dq_partial) {
+        err = cudaMemsetAsync(dq, 0, sizeof(T) * (size_t)g.B * g.ltot * g.Hq * g.D, s);
+        if (err != cudaSuccess) return err;
+    }
+    if (qrows > 0) {
+        delta_kernel<T><<<grid_for(qrows), kWarps * 32, 0, s>>>((const T*)out, (const T*)dout, delta, qrows, g.Dv);
+        ++g_launches;
+        const size_t smem = (size_t)kWarps * (g.D + g.Dv) * sizeof(A);
+        NATTEN_DISPATCH_N(g.D, ND,
+            fused_bwd_dq_kernel<T, ND><<<grid_for(qrows), kWarps * 32, smem, s>>>(
+                g, (const T*)q, (const T*)k, (const T*)v, (const T*)ek, (const T*)ev, (const A*)lse, delta,
+                (const T*)dout, (const A*)dlse, (T*)dq, qrows));
+        ++g_launches;
+    }
+    if (krows > 0) {
+        const size_t smem = (size_t)kWarps * (g.D + g.Dv) * sizeof(A);
+        const int dmax = g.D > g.Dv ? g.D : g.Dv;
+        NATTEN_DISPATCH_N(dmax, ND,
+            fused_bwd_dkdv_kernel<T, ND, ND><<<grid_for(krows), kWarps * 32, smem, s>>>(
+                g, (const T*)q, (const T*)k, (const T*)v, (const A*)lse, delta, (const T*)dout,
+                (const A*)dlse, (T*)dk, (T*)dv, krows));
+        ++g_launches;
+    }
+    if (g.n_extra > 0 && g.B > 0) {
+        const size_t smem = (size_t)(kWarps + 1) * (g.D + g.Dv) * sizeof(A);
+        const int dmax = g.D > g.Dv ? g.D : g.Dv;
+        const unsigned blocks = (unsigned)((long long)g.B * g.n_extra * g.Hkv);
+        NATTEN_DISPATCH_N(dmax, ND,
+            fused_bwd_extra_kernel<T, ND, ND><<<blocks, kWarps * 32, smem, s>>>(
+                g, (const T*)q, (const T*)ek, (const T*)ev, (const A*)lse, delta, (const T*)dout,
+                (const A*)dlse, (T*)dek, (T*)dev));
+        ++g_launches;
+    }
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t qk_fwd_t(const Geo& g, const void* q, const void* k, void* logits, cudaStream_t s)
+{
+    using A = typename AccOf<T>::type;
+    const long long rows = (long long)g.B * g.otot * g.Hq;
+    if (rows == 0) return cudaSuccess;
+    qk_fwd_kernel<T><<<grid_for(rows), kWarps * 32, (size_t)kWarps * g.D * sizeof(A), s>>>(
+        g, (const T*)q, (const T*)k, (T*)logits, rows);
+    ++g_launches;
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t qk_bwd_t(const Geo& g, const void* q, const void* k, const void* dlogits, void* dq, void* dk,
+                     cudaStream_t s)
+{
+    const long long qrows = (long long)g.B * g.otot * g.Hq;
+    const long long krows = (long long)g.B * g.ltot * g.Hkv;
+    bool partial = false;
+    for (int a = 0; a < g.rank; ++a) partial = partial || g.st[a] != 1;
+    if (partial) {
+        cudaError_t err = cudaMemsetAsync(dq, 0, sizeof(T) * (size_t)g.B * g.ltot * g.Hq * g.D, s);
+        if (err != cudaSuccess) return err;
+    }
+    if (qrows > 0) {
+        NATTEN_DISPATCH_N(g.D, ND,
+            qk_bwd_dq_kernel<T, ND><<<grid_for(qrows), kWarps * 32, 0, s>>>(
+                g, (const T*)k, (const T*)dlogits, (T*)dq, qrows));
+        ++g_launches;
+    }
+    if (krows > 0) {
+        NATTEN_DISPATCH_N(g.D, ND,
+            inverse_gather_kernel<T, ND><<<grid_for(krows), kWarps * 32, 0, s>>>(
+                g, (const T*)dlogits, (const T*)q, g.qs[0], g.qs[1], g.qs[2], 1, g.D,
+                g.has_scale ? g.scale : 1.0f, (T*)dk, krows));
+        ++g_launches;
+    }
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t av_fwd_t(const Geo& g, const void* attn, const void* v, void* out, cudaStream_t s)
+{
+    const long long rows = (long long)g.B * g.otot * g.Hq;
+    if (rows == 0) return cudaSuccess;
+    NATTEN_DISPATCH_N(g.Dv, NDV,
+        av_fwd_kernel<T, NDV><<<grid_for(rows), kWarps * 32, 0, s>>>(
+            g, (const T*)attn, (const T*)v, (T*)out, rows));
+    ++g_launches;
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t av_bwd_t(const Geo& g, const void* attn, const void* v, const void* dout, void* dattn, void* dv,
+                     cudaStream_t s)
+{
+    using A = typename AccOf<T>::type;
+    const long long qrows = (long long)g.B * g.otot * g.Hq;
+    const long long krows = (long long)g.B * g.ltot * g.Hkv;
+    if (qrows > 0) {
+        av_bwd_dattn_kernel<T><<<grid_for(qrows), kWarps * 32, (size_t)kWarps * g.Dv * sizeof(A), s>>>(
+            g, (const T*)v, (const T*)dout, (T*)dattn, qrows);
+        ++g_launches;
+    }
+    if (krows > 0) {
+        NATTEN_DISPATCH_N(g.Dv, ND,
+            inverse_gather_kernel<T, ND><<<grid_for(krows), kWarps * 32, 0, s>>>(
+                g, (const T*)attn, (const T*)dout, 0, 0, 0, 0, g.Dv, 1.0f, (T*)dv, krows));
+        ++g_launches;
+    }
+    return cudaGetLastError();
+}
+
+#define NATTEN_BY_DTYPE(dtype, CALL)                                   \
+    switch (dtype) {                                                   \
+        case 0: { using T = float; return CALL; }                      \
+        case 1: { using T = __half; return CALL; }                     \
+        case 2: { using T = __nv_bfloat16; return CALL; }              \
+        case 3: { using T = double; return CALL; }                     \
+        default: return cudaErrorInvalidValue;                         \
+    }
+
+} // namespace
+
+unsigned long long simt_launch_count() { return g_launches; }
+void simt_count_launch(int n) { g_launches += n; }
+
+cudaError_t simt_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const void* v,
+                           const void* ek, const void* ev, void* out, void* lse, cudaStream_t s)
+{
+    NATTEN_BY_DTYPE(dtype, fused_fwd_t<T>(g, q, k, v, ek, ev, out, lse, s));
+}
+
+cudaError_t simt_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const void* v,
+                           const void* ek, const void* ev, const void* out, const void* lse,
+                           const void* dout, const void* dlse, void* dq, void* dk, void* dv,
+                           void* dek, void* dev, void* workspace, cudaStream_t s)
+{
+    NATTEN_BY_DTYPE(dtype, fused_bwd_t<T>(g, q, k, v, ek, ev, out, lse, dout, dlse, dq, dk, dv, dek, dev,
+                                          workspace, s));
+}
+
+cudaError_t simt_qk_fwd(int dtype, const Geo& g, const void* q, const void* k, void* logits, cudaStream_t s)
+{
+    NATTEN_BY_DTYPE(dtype, qk_fwd_t<T>(g, q, k, logits, s));
+}
+
+cudaError_t simt_qk_bwd(int dtype, const Geo& g, const void* q, const void* k, const void* dlogits,
+                        void* dq, void* dk, cudaStream_t s)
+{
+    NATTEN_BY_DTYPE(dtype, qk_bwd_t<T>(g, q, k, dlogits, dq, dk, s));
+}
+
+cudaError_t simt_av_fwd(int dtype, const Geo& g, const void* attn, const void* v, void* out, cudaStream_t s)
+{
+    NATTEN_BY_DTYPE(dtype, av_fwd_t<T>(g, attn, v, out, s));
+}
+
+cudaError_t simt_av_bwd(int dtype, const Geo& g, const void* attn, const void* v, const void* dout,
+                        void* dattn, void* dv, cudaStream_t s)
+{
+    NATTEN_BY_DTYPE(dtype, av_bwd_t<T>(g, attn, v, dout, dattn, dv, s));
+}
+
+} // namespace natten

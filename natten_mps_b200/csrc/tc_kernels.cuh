@@ -1,0 +1,17 @@
+// Launchers of the tcgen05 / TMA kernels.  They return NATTEN_E_UNSUPPORTED (-2)
+// for configurations they do not cover so that the caller can take the SIMT path.
+#pragma once
+#include "geometry.cuh"
+#include <stddef.h>
+
+namespace natten {
+
+int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const void* v,
+                 const void* ek, const void* ev, void* out, void* lse, cudaStream_t s);
+int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const void* v,
+                 const void* ek, const void* ev, const void* out, const void* lse, const void* dout,
+                 const void* dlse, void* dq, void* dk, void* dv, void* dek, void* dev,
+                 void* workspace, cudaStream_t s);
+size_t tc_bwd_workspace_bytes(int dtype, const Geo& g);
+
+} // namespace natten
