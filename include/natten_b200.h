@@ -64,7 +64,7 @@ typedef struct natten_params {
     int32_t n_extra;       /* additional key/value tokens per sample (0 = none)   */
     int32_t has_scale;     /* split QK only: 0 = return unscaled dot products     */
     int32_t flags;         /* NATTEN_FLAG_*                                       */
-    float scale;           /* resolved logit scale                                */
+    double scale;          /* resolved logit scale                                */
     int64_t q_stride[3];   /* batch, token, head strides of q (elements)          */
     int64_t k_stride[3];
     int64_t v_stride[3];
@@ -117,6 +117,9 @@ const char* natten_strerror(int code);
 int natten_abi_version(void);
 int natten_last_path(void);              /* NATTEN_PATH_* of the last call, this thread */
 unsigned long long natten_launch_count(void); /* kernels launched by this library so far */
+/* Synchronises the device and reports whether any kernel of this library gave up
+ * on a bounded wait since the library was loaded (NATTEN_OK or NATTEN_E_DEVICE). */
+int natten_device_status(void);
 
 #ifdef __cplusplus
 }

@@ -22,7 +22,7 @@ PATH_NAMES = {0: "none", 1: "simt", 2: "tcgen05"}
 EXPORTS = (
     "natten_fused_fwd", "natten_fused_bwd", "natten_workspace_bytes", "natten_qk_fwd",
     "natten_qk_bwd", "natten_av_fwd", "natten_av_bwd", "natten_strerror",
-    "natten_abi_version", "natten_last_path", "natten_launch_count",
+    "natten_abi_version", "natten_last_path", "natten_launch_count", "natten_device_status",
 )
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.float64: F64}
@@ -38,7 +38,7 @@ class Params(ctypes.Structure):
         ("dilation", ctypes.c_int32 * 3), ("stride", ctypes.c_int32 * 3),
         ("causal", ctypes.c_int32 * 3),
         ("n_extra", ctypes.c_int32), ("has_scale", ctypes.c_int32), ("flags", ctypes.c_int32),
-        ("scale", ctypes.c_float),
+        ("scale", ctypes.c_double),
         ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3),
         ("v_stride", ctypes.c_int64 * 3),
         ("extents", ctypes.c_void_p),
@@ -85,6 +85,11 @@ def set_force(path: Optional[str]) -> None:
 
 def last_path() -> str:
     return PATH_NAMES[lib().natten_last_path()]
+
+
+def device_status() -> int:
+    """0 when no kernel ever gave up on a bounded wait (synchronises the device)."""
+    return int(lib().natten_device_status())
 
 
 def launch_count() -> int:

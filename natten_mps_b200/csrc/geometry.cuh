@@ -16,7 +16,7 @@ struct Geo {
     long long ltot, otot;
     long long qs[3], ks[3], vs[3];   // batch, token, head strides (elements)
     const int* extents;              // [B, rank] or nullptr
-    float scale;
+    double scale;
 };
 
 __host__ __device__ __forceinline__ int window_start(int index, int length, int kernel_size, int dilation)

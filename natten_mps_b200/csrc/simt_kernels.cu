@@ -605,7 +605,7 @@ template <typename T, int ND>
 __global__ void __launch_bounds__(kWarps * 32)
 inverse_gather_kernel(const __grid_constant__ Geo g, const T* __restrict__ weights,
                       const T* __restrict__ rows_src, long long src_bs, long long src_ts, long long src_hs,
-                      int src_is_query_input, int width, float wscale, T* __restrict__ dst, long long rows)
+                      int src_is_query_input, int width, double wscale, T* __restrict__ dst, long long rows)
 {
     using A = typename AccOf<T>::type;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -828,7 +828,7 @@ cudaError_t qk_bwd_t(const Geo& g, const void* q, const void* k, const void* dlo
         NATTEN_DISPATCH_N(g.D, ND,
             inverse_gather_kernel<T, ND><<<grid_for(krows), kWarps * 32, 0, s>>>(
                 g, (const T*)dlogits, (const T*)q, g.qs[0], g.qs[1], g.qs[2], 1, g.D,
-                g.has_scale ? g.scale : 1.0f, (T*)dk, krows));
+                g.has_scale ? g.scale : 1.0, (T*)dk, krows));
         ++g_launches;
     }
     return cudaGetLastError();
@@ -861,7 +861,7 @@ cudaError_t av_bwd_t(const Geo& g, const void* attn, const void* v, const void* 
     if (krows > 0) {
         NATTEN_DISPATCH_N(g.Dv, ND,
             inverse_gather_kernel<T, ND><<<grid_for(krows), kWarps * 32, 0, s>>>(
-                g, (const T*)attn, (const T*)dout, 0, 0, 0, 0, g.Dv, 1.0f, (T*)dv, krows));
+                g, (const T*)attn, (const T*)dout, 0, 0, 0, 0, g.Dv, 1.0, (T*)dv, krows));
         ++g_launches;
     }
     return cudaGetLastError();

@@ -13,5 +13,9 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
                  const void* dlse, void* dq, void* dk, void* dv, void* dek, void* dev,
                  void* workspace, cudaStream_t s);
 size_t tc_bwd_workspace_bytes(int dtype, const Geo& g);
+void tc_count_launch();
+unsigned long long tc_launch_count();
+// 0 = clean; 1 = some kernel gave up on a bounded wait (synchronises the device).
+int tc_device_status();
 
 } // namespace natten

@@ -37,7 +37,7 @@ def test_fused_against_golden_and_oracle(case, dtype, path):
         tol_scale = 2e4 if case["n_extra"] else 1.0
         for name in ("out", "dq", "dk", "dv", "dek", "dev", "lse"):
             if name in a and got.get(name) is not None:
-                g = got[name].double().cpu().numpy()
+                g = got[name].detach().double().cpu().numpy()
                 assert np.abs(g - a[name]).max() <= 1e-10 * tol_scale * max(1.0, np.abs(a[name]).max()), name
 
 
@@ -69,8 +69,8 @@ def test_split_ops_against_golden(case, dtype):
     if dtype == torch.float64:
         assert np.abs(logits.detach().cpu().numpy()[np.isfinite(a["logits"])]
                       - a["logits"][np.isfinite(a["logits"])]).max() < 1e-10
-        assert np.abs(dk.cpu().numpy() - a["dk"]).max() < 1e-10
-        assert np.abs(dv.cpu().numpy() - a["dv"]).max() < 1e-10
+        assert np.abs(dk.detach().cpu().numpy() - a["dk"]).max() < 1e-10
+        assert np.abs(dv.detach().cpu().numpy() - a["dv"]).max() < 1e-10
 
 
 @pytest.mark.parametrize("path", PATHS)
@@ -85,7 +85,7 @@ def test_varlen_against_golden(case, dtype, path):
     compare_fused(got, want, dtype)
     if dtype == torch.float64:
         for name in ("out", "dq", "dk", "dv"):
-            assert np.abs(got[name].cpu().numpy() - a[name]).max() < 1e-10, name
+            assert np.abs(got[name].detach().cpu().numpy() - a[name]).max() < 1e-10, name
     # rows past each sample's extent are exactly zero, forward and backward
     sizes = case["sizes"]
     for b, ext in enumerate(sizes):
