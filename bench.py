@@ -234,6 +234,12 @@ def run_ours(args, w):
     ms_total = e0.elapsed_time(e1)
     path = _cabi.last_path()
 
+    if args.kernels_only:
+        if rank == 0:
+            print(json.dumps({"ms_per_step": ms_total / args.steps, "kernel_path": path,
+                              "gpu_launches": launches}), flush=True)
+        return
+
     # ---- per-phase timing (forward kernel vs backward kernels) ---------------
     fe = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     fwd_ms, bwd_ms = [], []
@@ -327,8 +333,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the per-GPU batch (small cases for profiler captures)")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="only the device-resident timed loop (for profiler captures)")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        w["B"] = args.batch
+        w["desc"] += f" (batch overridden to {args.batch})"
     if args.impl == "reference":
         run_reference(args, w)
     else:

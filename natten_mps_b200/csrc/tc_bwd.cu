@@ -1,0 +1,499 @@
+// Fused neighbourhood-attention backward on tcgen05 tensor cores (sm_100a).
+//
+// Two launches of one kernel template, neither materialises P or dS in memory:
+//   * query side (kQuerySide): rows = a box of 128 queries, columns = chunks of the
+//     key box.  S = Q K^T, dP = dO V^T (tensor cores, TMEM); threads turn them into
+//     dS = P (dP - delta) * scale with P = exp2(S*scale*log2e - lse*log2e); dQ += dS K.
+//   * key side (kKeySide): rows = a box of 128 keys, columns = chunks of the box of
+//     queries that attend to them (the inverse neighbourhood, a contiguous range per
+//     axis for odd kernels), for every query head of the GQA group.  S^T = K Q^T,
+//     dP^T = V dO^T; dV += P^T dO, dK += dS^T Q.  Per-column lse / delta are staged in
+//     shared memory by a helper warp.
+// The row accumulators live in TMEM for the whole CTA, so dK/dV are reduced in a
+// fixed order: results are bit-reproducible, no atomics.
+//
+// Warps: 16 compute warps (four per TMEM lane quadrant, each owns one 32-column piece
+// of the chunk), one TMA + MMA issuing warp, one column-statistics warp.
+// TMEM (512 columns): S [0,128) dP [128,256) P [256,320) dS [320,384) acc1 [384,448) acc2 [448,512).
+#include "tc_kernels.cuh"
+
+#include "tc_plan.cuh"
+
+namespace natten {
+
+using namespace tc;
+using namespace tcplan;
+
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kComputeWarps = 16;
+constexpr int kThreads = (kComputeWarps + 2) * 32;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColDP = 128, kColP = 256, kColDS = 320, kColA1 = 384, kColA2 = 448;
+constexpr int kTile = kTileRows * 128;      // bytes of one [128 x 64] 16-bit tile
+
+struct Smem {
+    static constexpr int kR1 = 0;
+    static constexpr int kR2 = kR1 + kTile;
+    static constexpr int kC1 = kR2 + kTile;                     // [kStages]
+    static constexpr int kC2 = kC1 + kStages * kTile;           // [kStages]
+    static constexpr int kStats = kC2 + kStages * kTile;        // [kStages][2][128] float
+    static constexpr int kBar = kStats + kStages * 1024;
+    static constexpr int kTotal = kBar + 256;
+};
+
+__device__ __forceinline__ int ws1(int p, int L, int K) { return window_start(p, L, K, 1); }
+
+// Queries attending to key n on one axis (odd kernel, unit dilation inside the sub-grid).
+__device__ __forceinline__ void inverse_range(int n, int L, int K, int causal, int& qlo, int& qhi)
+{
+    if (causal) {
+        qlo = n;
+        qhi = n + K - 1 < L - 1 ? n + K - 1 : L - 1;
+    } else {
+        qlo = (n <= K - 1) ? 0 : n - K / 2;
+        qhi = (n >= L - K) ? L - 1 : n + K / 2;
+    }
+}
+
+template <bool BF16, bool kKeySide>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
+              const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2,
+              const __grid_constant__ TcParams P, const float* __restrict__ lse,
+              const float* __restrict__ delta, uint16_t* __restrict__ out1, uint16_t* __restrict__ out2)
+{
+    constexpr int DH = 64;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // query side: blockIdx.y = query head.  key side: blockIdx.y = kv head.
+    const int hy = blockIdx.y, b = blockIdx.z;
+    const int n_heads_col = kKeySide ? P.group : 1;          // column passes (query heads of the group)
+
+    // ---- CTA geometry -------------------------------------------------------
+    int gidx = blockIdx.x / P.ntiles, tidx = blockIdx.x % P.ntiles;
+    int rg[3], origin[3], Lp[3], boxlo[3], nc[3];
+    bool cta_active = true;
+    for (int a = 2; a >= 0; --a) {
+        rg[a] = gidx % P.dil[a]; gidx /= P.dil[a];
+        origin[a] = (tidx % P.ntile[a]) * P.tile[a]; tidx /= P.ntile[a];
+        const int ea = a - (3 - P.rank);
+        const int Ls = (P.extents && ea >= 0) ? P.extents[b * P.rank + ea] : P.L[a];
+        Lp[a] = rg[a] < Ls ? (Ls - rg[a] + P.dil[a] - 1) / P.dil[a] : 0;
+        if (origin[a] >= Lp[a]) cta_active = false;
+    }
+    int nchunks = 1;
+    if (cta_active)
+        for (int a = 0; a < 3; ++a) {
+            const int last = origin[a] + P.tile[a] - 1 < Lp[a] - 1 ? origin[a] + P.tile[a] - 1 : Lp[a] - 1;
+            int hi;
+            if (kKeySide) {
+                int t;
+                inverse_range(origin[a], Lp[a], P.K[a], P.causal[a], boxlo[a], t);
+                inverse_range(last, Lp[a], P.K[a], P.causal[a], t, hi);
+            } else {
+                boxlo[a] = P.causal[a] ? origin[a] - (P.K[a] - 1) : ws1(origin[a], Lp[a], P.K[a]);
+                hi = P.causal[a] ? last : ws1(last, Lp[a], P.K[a]) + P.K[a] - 1;
+            }
+            nc[a] = (hi - boxlo[a] + P.cb[a]) / P.cb[a];
+            nchunks *= nc[a];
+        }
+
+    // ---- per-thread row ------------------------------------------------------
+    int f[3] = {0, 0, 0}, e[3] = {0, 0, 0};
+    bool valid_row = false, in_tensor = false;
+    long long out_row = 0;
+    float row_lse2 = 0.f, row_delta = 0.f;
+    const int quad = warp & 3, piece = warp >> 2;            // compute warps only
+    if (warp < kComputeWarps) {
+        int r = quad * 32 + lane;
+        int ri[3];
+        ri[2] = r % P.tile[2]; r /= P.tile[2];
+        ri[1] = r % P.tile[1]; r /= P.tile[1];
+        ri[0] = r;
+        valid_row = true; in_tensor = true;
+        long long pflat = 0;
+        for (int a = 0; a < 3; ++a) {
+            const int xa = origin[a] + ri[a];
+            const int pa = rg[a] + P.dil[a] * xa;
+            if (xa >= Lp[a]) valid_row = false;
+            if (pa >= P.L[a]) in_tensor = false;
+            pflat = pflat * P.L[a] + pa;
+            if (cta_active) {
+                if (kKeySide) {
+                    int qlo, qhi;
+                    inverse_range(xa, Lp[a], P.K[a], P.causal[a], qlo, qhi);
+                    f[a] = qlo - boxlo[a];
+                    e[a] = qhi + 1 - boxlo[a];
+                } else {
+                    const int first = P.causal[a] ? xa - (P.K[a] - 1) : ws1(xa, Lp[a], P.K[a]);
+                    f[a] = (first > 0 ? first : 0) - boxlo[a];
+                    e[a] = (first + P.K[a] < Lp[a] ? first + P.K[a] : Lp[a]) - boxlo[a];
+                }
+            }
+        }
+        if (!valid_row) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
+        out_row = ((long long)b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + hy;
+        if (!kKeySide && valid_row && cta_active) {
+            row_lse2 = lse[out_row] * 1.4426950408889634f;
+            row_delta = delta[out_row];
+        }
+    }
+
+    if (!cta_active) {                       // padding rows get zero gradients
+        if (warp < kComputeWarps && in_tensor) {
+            uint4* o1 = reinterpret_cast<uint4*>(out1 + out_row * DH + piece * 16);
+            o1[0] = make_uint4(0, 0, 0, 0); o1[1] = make_uint4(0, 0, 0, 0);
+            if (kKeySide) {
+                uint4* o2 = reinterpret_cast<uint4*>(out2 + out_row * DH + piece * 16);
+                o2[0] = make_uint4(0, 0, 0, 0); o2[1] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        return;
+    }
+
+    // ---- shared memory, barriers, TMEM --------------------------------------
+    const uint32_t sbase = smem_u32(smem);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kBar + 128);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Smem::kBar + 136);
+    const uint32_t bar_row = sbase + Smem::kBar + 0;
+    const uint32_t bar_col = sbase + Smem::kBar + 8;          // [kStages] C1, C2 landed
+    const uint32_t bar_stats = sbase + Smem::kBar + 40;       // [kStages] column lse / delta staged
+    const uint32_t bar_s = sbase + Smem::kBar + 72;           // S and dP of the chunk are in TMEM
+    const uint32_t bar_sp = sbase + Smem::kBar + 80;          // threads consumed S/dP, wrote P/dS
+    const uint32_t bar_acc = sbase + Smem::kBar + 88;         // accumulating MMAs of the chunk finished
+    float* stats = reinterpret_cast<float*>(smem + Smem::kStats);
+
+    if (tid == 0) {
+        *abort_flag = ((sbase & 1023u) || *reinterpret_cast<volatile int*>(P.status)) ? 1 : 0;
+        mbar_init(bar_row, 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar_col + 8 * s, 1); mbar_init(bar_stats + 8 * s, 32); }
+        mbar_init(bar_s, 1);
+        mbar_init(bar_sp, kComputeWarps * 32);
+        mbar_init(bar_acc, 1);
+        mbar_init_fence();
+    }
+    if (warp == kComputeWarps) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        if (lane == 0) { tma_prefetch_desc(&tmR1); tma_prefetch_desc(&tmR2); tma_prefetch_desc(&tmC1); tma_prefetch_desc(&tmC2); }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int total = nchunks * n_heads_col;                 // column passes of this CTA
+
+    auto chunk_index = [&](int cc, int (&ci)[3], int& head_col) {
+        head_col = kKeySide ? hy * P.group + cc / nchunks : hy;
+        int c = cc % nchunks;
+        ci[2] = c % nc[2]; c /= nc[2];
+        ci[1] = c % nc[1]; c /= nc[1];
+        ci[0] = c;
+    };
+    const int head_row = hy;                                  // head coordinate of the row tensors
+    const int head_kv = kKeySide ? hy : hy / P.group;
+
+    if (warp == kComputeWarps) {
+        // =====================================================================
+        // TMA + MMA issue (one thread)
+        // =====================================================================
+        if (lane == 0 && !*abort_flag) {
+            auto issue_cols = [&](int cc) {
+                int ci[3], hc;
+                chunk_index(cc, ci, hc);
+                int X[3];
+                for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (boxlo[a] + ci[a] * P.cb[a]);
+                const int s = cc % kStages;
+                const uint32_t bar = bar_col + 8 * s;
+                // query side: columns are keys (kv head); key side: columns are queries (query head)
+                const int hx = (kKeySide ? hc : head_kv) * DH;
+                mbar_expect_tx(bar, 2 * kTile);
+                tma_load_5d(sbase + Smem::kC1 + s * kTile, &tmC1, bar, hx, X[2], X[1], X[0], b);
+                tma_load_5d(sbase + Smem::kC2 + s * kTile, &tmC2, bar, hx, X[2], X[1], X[0], b);
+            };
+            {
+                const int hx = (kKeySide ? head_kv : head_row) * DH;
+                mbar_expect_tx(bar_row, 2 * kTile);
+                tma_load_5d(sbase + Smem::kR1, &tmR1, bar_row, hx, rg[2] + P.dil[2] * origin[2],
+                            rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
+                tma_load_5d(sbase + Smem::kR2, &tmR2, bar_row, hx, rg[2] + P.dil[2] * origin[2],
+                            rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
+            }
+            for (int cc = 0; cc < total && cc < kStages; ++cc) issue_cols(cc);
+
+            constexpr uint32_t idesc_kk = instr_desc(BF16 ? 1 : 0, kChunk, 0, 0);   // both operands K-major
+            constexpr uint32_t idesc_acc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A from TMEM, B MN-major
+            auto issue_s_dp = [&](int cc) {
+                const int s = cc % kStages;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < DH / 16; ++ks)
+                    mma_ss(tmem + kColS, smem_desc(sbase + Smem::kR1 + ks * 32, 16, 1024),
+                           smem_desc(sbase + Smem::kC1 + s * kTile + ks * 32, 16, 1024), idesc_kk, ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < DH / 16; ++ks)
+                    mma_ss(tmem + kColDP, smem_desc(sbase + Smem::kR2 + ks * 32, 16, 1024),
+                           smem_desc(sbase + Smem::kC2 + s * kTile + ks * 32, 16, 1024), idesc_kk, ks > 0);
+                mma_commit(bar_s);
+            };
+            auto issue_acc = [&](int cc) {
+                const int s = cc % kStages;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kChunk / 16; ++ks)
+                    mma_ts(tmem + kColA1, tmem + kColDS + 8 * ks,
+                           smem_desc(sbase + Smem::kC1 + s * kTile + ks * 2048, kTile, 1024), idesc_acc,
+                           (cc > 0 || ks > 0) ? 1u : 0u);
+                if (kKeySide) {
+#pragma unroll
+                    for (int ks = 0; ks < kChunk / 16; ++ks)
+                        mma_ts(tmem + kColA2, tmem + kColP + 8 * ks,
+                               smem_desc(sbase + Smem::kC2 + s * kTile + ks * 2048, kTile, 1024), idesc_acc,
+                               (cc > 0 || ks > 0) ? 1u : 0u);
+                }
+                mma_commit(bar_acc);
+            };
+
+            bool ok = mbar_wait(bar_row, 0, abort_flag);
+            ok = ok && mbar_wait(bar_col, 0, abort_flag);
+            if (ok) issue_s_dp(0);
+            for (int cc = 0; cc < total && ok; ++cc) {
+                ok = mbar_wait(bar_sp, cc & 1, abort_flag);              // S/dP consumed, P/dS stored
+                if (!ok) break;
+                if (cc + 1 < total) {
+                    ok = mbar_wait(bar_col + 8 * ((cc + 1) % kStages), ((cc + 1) / kStages) & 1, abort_flag);
+                    if (!ok) break;
+                    issue_s_dp(cc + 1);                                  // next chunk's S/dP first ...
+                }
+                issue_acc(cc);                                           // ... then this chunk's accumulation
+                if (cc + kStages < total) {
+                    ok = mbar_wait(bar_acc, cc & 1, abort_flag);         // stage cc % kStages is free again
+                    if (!ok) break;
+                    issue_cols(cc + kStages);
+                }
+            }
+        }
+    } else if (warp == kComputeWarps + 1) {
+        // =====================================================================
+        // column statistics (key side): lse*log2e and delta of the chunk's queries
+        // =====================================================================
+        if (kKeySide) {
+            bool ok = !*abort_flag;
+            for (int cc = 0; cc < total; ++cc) {
+                const int s = cc % kStages;
+                if (cc >= kStages) ok = ok && mbar_wait(bar_acc, (cc - kStages) & 1, abort_flag);
+                int ci[3], hc;
+                chunk_index(cc, ci, hc);
+                float* st = stats + s * 256;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int j = lane + 32 * k;
+                    const int j2 = j & (P.cb[2] - 1);
+                    const int j1 = (j >> P.cb2_log) & (P.cb[1] - 1);
+                    const int j0 = j >> (P.cb2_log + P.cb1_log);
+                    const int jj[3] = {j0, j1, j2};
+                    bool inside = ok;
+                    long long pflat = 0;
+                    for (int a = 0; a < 3; ++a) {
+                        const int qa = boxlo[a] + ci[a] * P.cb[a] + jj[a];
+                        if (qa < 0 || qa >= Lp[a]) inside = false;
+                        pflat = pflat * P.L[a] + (rg[a] + P.dil[a] * qa);
+                    }
+                    float l2 = 0.f, dl = 0.f;
+                    if (inside) {
+                        const long long row = ((long long)b * P.ltot + pflat) * P.Hq + hc;
+                        l2 = lse[row] * 1.4426950408889634f;
+                        dl = delta[row];
+                    }
+                    st[j] = l2;
+                    st[128 + j] = dl;
+                }
+                mbar_arrive(bar_stats + 8 * s);
+            }
+        }
+    } else {
+        // =====================================================================
+        // compute warps: thread = (row, 32-column piece)
+        // =====================================================================
+        const uint32_t trow = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+        bool ok = true;
+        for (int cc = 0; cc < total; ++cc) {
+            int ci[3], hc;
+            chunk_index(cc, ci, hc);
+            const uint32_t word = piece_word(P, ci, piece, f, e);
+            const bool any = __any_sync(0xffffffffu, word != 0u);
+
+            ok = ok && mbar_wait(bar_s, cc & 1, abort_flag);
+            tc_fence_after();
+            uint32_t pk_p[16], pk_ds[16];
+            if (any && ok) {
+                uint32_t s[32], dp[32];
+                tmem_ld32(trow + kColS + 32 * piece, s);
+                tmem_ld32(trow + kColDP + 32 * piece, dp);
+                const float* st = stats + (cc % kStages) * 256 + 32 * piece;
+                if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (cc % kStages), (cc / kStages) & 1, abort_flag);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float pv[2], dsv[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int j = 2 * i + u;
+                        const float l2 = kKeySide ? st[j] : row_lse2;
+                        const float dl = kKeySide ? st[128 + j] : row_delta;
+                        const bool on = (word >> j) & 1u;
+                        const float p = on ? fast_exp2(__uint_as_float(s[j]) * P.scale_log2 - l2) : 0.f;
+                        pv[u] = p;
+                        dsv[u] = p * (__uint_as_float(dp[j]) - dl) * P.scale;
+                    }
+                    pk_p[i] = pack16(pv[0], pv[1], BF16);
+                    pk_ds[i] = pack16(dsv[0], dsv[1], BF16);
+                }
+            } else {
+                if (kKeySide && !any) ok = ok && mbar_wait(bar_stats + 8 * (cc % kStages), (cc / kStages) & 1, abort_flag);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { pk_p[i] = 0u; pk_ds[i] = 0u; }
+            }
+            if (cc > 0) ok = ok && mbar_wait(bar_acc, (cc - 1) & 1, abort_flag);   // previous P/dS consumed
+            tc_fence_after();
+            tmem_st16(trow + kColDS + 16 * piece, pk_ds);
+            if (kKeySide) tmem_st16(trow + kColP + 16 * piece, pk_p);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(bar_sp);
+        }
+
+        // ---- accumulators -> global: this warp owns 16 of the 64 channels ----
+        ok = ok && mbar_wait(bar_acc, (total - 1) & 1, abort_flag);
+        tc_fence_after();
+        if (in_tensor) {
+            const bool live = valid_row && ok;
+#pragma unroll
+            for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
+                uint32_t a[32];
+                // 32x32b.x32 reads 32 columns; only the 16 owned by this warp are used
+                tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + 32 * (piece >> 1), a);
+                tmem_ld_wait();
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int c0 = 16 * (piece & 1) + 2 * i;
+                    w[i] = live ? pack16(__uint_as_float(a[c0]), __uint_as_float(a[c0 + 1]), BF16) : 0u;
+                }
+                uint16_t* dst = (which == 0 ? out1 : out2) + out_row * DH + piece * 16;
+                uint4* d4 = reinterpret_cast<uint4*>(dst);
+                d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kComputeWarps) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+        if (lane == 0 && *abort_flag) atomicExch(P.status, 1);
+    }
+}
+
+// delta[row] = sum_d out[row,d]*dout[row,d] - dlse[row]
+template <bool BF16>
+__global__ void tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ dout,
+                                const float* __restrict__ dlse, float* __restrict__ delta, long long rows)
+{
+    // 8 threads per 64-channel row, 16 bytes each
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long row = t >> 3;
+    const int part = (int)(t & 7);
+    float acc = 0.f;
+    if (row < rows) {
+        const uint4 a = reinterpret_cast<const uint4*>(out + row * 64)[part];
+        const uint4 g = reinterpret_cast<const uint4*>(dout + row * 64)[part];
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 x, y;
+            if (BF16) {
+                x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+                y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+            } else {
+                x = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+                y = __half22float2(*reinterpret_cast<const __half2*>(&gw[i]));
+            }
+            acc += x.x * y.x + x.y * y.y;
+        }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    if (row < rows && part == 0) delta[row] = acc - (dlse ? dlse[row] : 0.f);
+}
+
+template <bool BF16>
+int launch_bwd(const Geo& g, const Plan& plan, const void* q, const void* k, const void* v,
+               const void* out, const void* lse, const void* dout, const void* dlse, void* dq, void* dk,
+               void* dv, float* delta, cudaStream_t s)
+{
+    const TcParams& p = plan.p;
+    const long long qrows = (long long)g.B * g.ltot * g.Hq;
+    tc_delta_kernel<BF16><<<(unsigned)((qrows * 8 + 255) / 256), 256, 0, s>>>(
+        (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, qrows);
+    tc_count_launch();
+
+    const long long dos[3] = {g.ltot * g.Hq * g.Dv, (long long)g.Hq * g.Dv, g.Dv};   // dout is contiguous
+    CUtensorMap q_tile, do_tile, k_chunk, v_chunk, k_tile, v_tile, q_chunk, do_chunk;
+    const bool bf = BF16;
+    if (!encode_map(&q_tile, q, bf, p, g.Hq, 64, g.qs, plan.box_q) ||
+        !encode_map(&do_tile, dout, bf, p, g.Hq, 64, dos, plan.box_q) ||
+        !encode_map(&k_chunk, k, bf, p, g.Hkv, 64, g.ks, plan.box_kv) ||
+        !encode_map(&v_chunk, v, bf, p, g.Hkv, 64, g.vs, plan.box_kv) ||
+        !encode_map(&k_tile, k, bf, p, g.Hkv, 64, g.ks, plan.box_q) ||
+        !encode_map(&v_tile, v, bf, p, g.Hkv, 64, g.vs, plan.box_q) ||
+        !encode_map(&q_chunk, q, bf, p, g.Hq, 64, g.qs, plan.box_kv) ||
+        !encode_map(&do_chunk, dout, bf, p, g.Hq, 64, dos, plan.box_kv))
+        return -2;
+    int ngroups = 1;
+    for (int a = 0; a < 3; ++a) ngroups *= p.dil[a];
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(tc_bwd_kernel<BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+        cudaFuncSetAttribute(tc_bwd_kernel<BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+        attr_done = true;
+    }
+    const dim3 grid_q((unsigned)(p.ntiles * ngroups), (unsigned)g.Hq, (unsigned)g.B);
+    const dim3 grid_k((unsigned)(p.ntiles * ngroups), (unsigned)g.Hkv, (unsigned)g.B);
+    tc_bwd_kernel<BF16, false><<<grid_q, kThreads, Smem::kTotal, s>>>(
+        q_tile, do_tile, k_chunk, v_chunk, p, (const float*)lse, delta, (uint16_t*)dq, nullptr);
+    tc_count_launch();
+    tc_bwd_kernel<BF16, true><<<grid_k, kThreads, Smem::kTotal, s>>>(
+        k_tile, v_tile, q_chunk, do_chunk, p, (const float*)lse, delta, (uint16_t*)dk, (uint16_t*)dv);
+    tc_count_launch();
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? 0 : (int)err;
+}
+
+} // namespace
+
+int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const void* v, const void* ek,
+                 const void* ev, const void* out, const void* lse, const void* dout, const void* dlse,
+                 void* dq, void* dk, void* dv, void* dek, void* dev, void* workspace, cudaStream_t s)
+{
+    (void)ek; (void)ev; (void)dek; (void)dev;
+    if (!tc_eligible(dtype, g, q, k, v)) return -2;
+    if (reinterpret_cast<uintptr_t>(dout) & 15u) return -2;
+    Plan plan;
+    if (!make_plan(g, plan)) return -2;
+    plan.p.status = status_ptr();
+    if (!plan.p.status) return -2;
+    if (g.B == 0) return 0;
+    if (g.Hq > 65535 || g.B > 65535) return -2;
+    float* delta = reinterpret_cast<float*>(workspace);
+    return dtype == 2 ? launch_bwd<true>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s)
+                      : launch_bwd<false>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s);
+}
+
+size_t tc_bwd_workspace_bytes(int, const Geo&) { return 0; }
+
+} // namespace natten

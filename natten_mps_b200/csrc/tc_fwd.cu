@@ -1,13 +1,13 @@
-// Fused neighbourhood attention on tcgen05 tensor cores (sm_100a).
+// Fused neighbourhood-attention forward on tcgen05 tensor cores (sm_100a).
 //
 // One CTA handles a box of 128 queries of one (batch, head): the union of their
 // neighbourhoods is a box of keys, walked in chunks of 128 keys.  Per chunk
 //   S = Q K^T      tcgen05.mma, operands staged by TMA (128-byte swizzle), accumulator in TMEM
-//   P = exp2(S*scale*log2e - max)   four softmax warps, one query row per thread, read S
-//                                   from TMEM, apply the window mask, write P (16-bit) to TMEM
+//   P = exp2(S*scale*log2e - max)   softmax warps, one query row per thread, read S from TMEM,
+//                                   apply the window mask, write P (16-bit) back to TMEM
 //   O_c = P V      tcgen05.mma with A = P from TMEM, B = V tile read MN-major
 // and the threads fold O_c into register accumulators with the usual running-max
-// rescale.  A fifth warp issues every TMA load and MMA.  Geometry (rank, window,
+// rescale.  One extra warp issues every TMA load and MMA.  Geometry (rank, window,
 // dilation, causal axes, per-sample extents) is runtime data; masks are built per
 // 32-column piece from per-row box ranges.  Dilation is handled as independent
 // sub-grids, loaded through the tensor map's element strides.
@@ -16,37 +16,30 @@
 // Shared memory per CTA: Q 16 KB + 3 stages x (K 16 KB + V 16 KB) = 112 KB -> two CTAs per SM.
 #include "tc_kernels.cuh"
 
-#include "tc_common.cuh"
-
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
-#include <mutex>
+#include "tc_plan.cuh"
 
 namespace natten {
 
 using namespace tc;
+using namespace tcplan;
+
+__device__ int g_tc_status = 0;
+
+namespace tcplan {
+int* status_ptr()
+{
+    int* p = nullptr;
+    cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_tc_status);
+    return p;
+}
+} // namespace tcplan
 
 namespace {
 
 constexpr int kStages = 3;
-constexpr int kTileRows = 128;           // queries per CTA  (MMA M)
-constexpr int kChunk = 128;              // keys per chunk   (MMA N of S, K of PV)
 constexpr int kThreads = 160;            // 4 softmax warps + 1 TMA/MMA warp
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColP = 128, kColO = 192;
-
-struct TcParams {
-    int L[3], K[3], dil[3], causal[3];
-    int tile[3], cb[3], nchunk[3], ntile[3];
-    int cb1_log, cb2_log;
-    int rank, B, Hq, Hkv, group, ntiles, nchunks;
-    float scale_log2;
-    const int* extents;
-    long long ltot;
-    int* status;
-};
-
-__device__ int g_tc_status = 0;
 
 // Shared-memory map (dynamic, base must be 1024-byte aligned).
 template <int DH>
@@ -62,13 +55,6 @@ struct SmemMap {
 };
 
 __device__ __forceinline__ int tc_window_start(int p, int L, int K) { return window_start(p, L, K, 1); }
-
-__device__ __forceinline__ float fast_exp2(float x)
-{
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 
 template <int DH, bool BF16>
 __global__ void __launch_bounds__(kThreads, (DH == 64 ? 2 : 1))
@@ -400,146 +386,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
 }
 
-// ---------------------------------------------------------------------------
-// host side
-// ---------------------------------------------------------------------------
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn get_encode()
-{
-    static EncodeFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeFn>(p);
-    });
-    return fn;
-}
-
-int ilog2(int x) { int l = 0; while ((1 << l) < x) ++l; return l; }
-int pow2ceil(int x) { return 1 << ilog2(x); }
-
-// Internal geometry always has three axes; lower ranks get leading axes of size 1.
-struct Plan {
-    TcParams p;
-    int box_q[3], box_kv[3];
-};
-
-// Pick the query-tile shape whose key box needs the fewest 128-key chunks.
-bool make_plan(const Geo& g, Plan& plan)
-{
-    TcParams& p = plan.p;
-    const int pad = 3 - g.rank;
-    for (int a = 0; a < 3; ++a) {
-        const int s = a - pad;
-        p.L[a] = s >= 0 ? g.L[s] : 1;
-        p.K[a] = s >= 0 ? g.K[s] : 1;
-        p.dil[a] = s >= 0 ? g.dil[s] : 1;
-        p.causal[a] = s >= 0 ? g.causal[s] : 0;
-    }
-    long long best = -1;
-    for (int t2 = 1; t2 <= 128; t2 *= 2)
-        for (int t1 = 1; t1 * t2 <= 128; t1 *= 2) {
-            const int t0 = 128 / (t1 * t2);
-            const int t[3] = {t0, t1, t2};
-            bool fits = true;
-            for (int a = 0; a < 3; ++a)
-                if (p.L[a] == 1 && t[a] != 1) fits = false;      // unused axis
-            if (!fits) continue;
-            const int E2 = t2 + p.K[2] - 1;
-            int cb2 = pow2ceil(E2);
-            if (cb2 > 128) cb2 = 128;
-            if (cb2 * p.dil[2] > 256) continue;                  // TMA box limit
-            const int E1 = t1 + p.K[1] - 1;
-            int cb1 = 128 / cb2;
-            if (p.L[1] == 1) cb1 = 1;
-            if (cb1 > pow2ceil(E1)) cb1 = pow2ceil(E1);
-            if (cb1 * p.dil[1] > 256) continue;
-            int cb0 = 128 / (cb2 * cb1);
-            if (p.L[0] == 1 && cb0 != 1) continue;               // would leave the chunk short of 128 keys
-            if (cb0 * p.dil[0] > 256) continue;
-            const int E0 = t0 + p.K[0] - 1;
-            const long long n = (long long)((E0 + cb0 - 1) / cb0) * ((E1 + cb1 - 1) / cb1) * ((E2 + cb2 - 1) / cb2);
-            // prefer fewer chunks, then wider innermost tiles
-            if (best < 0 || n < best) {
-                best = n;
-                for (int a = 0; a < 3; ++a) p.tile[a] = t[a];
-                p.cb[0] = cb0; p.cb[1] = cb1; p.cb[2] = cb2;
-                p.nchunk[0] = (E0 + cb0 - 1) / cb0; p.nchunk[1] = (E1 + cb1 - 1) / cb1; p.nchunk[2] = (E2 + cb2 - 1) / cb2;
-            }
-        }
-    if (best < 0) return false;
-    p.cb1_log = ilog2(p.cb[1]); p.cb2_log = ilog2(p.cb[2]);
-    p.nchunks = (int)best;
-    p.ntiles = 1;
-    for (int a = 0; a < 3; ++a) {
-        const int lp = (p.L[a] + p.dil[a] - 1) / p.dil[a];
-        p.ntile[a] = (lp + p.tile[a] - 1) / p.tile[a];
-        p.ntiles *= p.ntile[a];
-        plan.box_q[a] = p.tile[a] * p.dil[a];
-        plan.box_kv[a] = p.cb[a] * p.dil[a];
-        if (plan.box_q[a] > 256) return false;
-    }
-    p.rank = g.rank; p.B = g.B; p.Hq = g.Hq; p.Hkv = g.Hkv; p.group = g.group;
-    p.scale_log2 = (float)(g.scale * 1.4426950408889634);
-    p.extents = g.extents;
-    p.ltot = g.ltot;
-    return true;
-}
-
-// 5-D map over [B, X0, X1, X2, heads*D] (innermost first in the arrays below).
-bool encode_map(CUtensorMap* map, const void* base, bool bf16, const TcParams& p, int heads, int dh,
-                const long long strides[3], const int box[3])
-{
-    EncodeFn enc = get_encode();
-    if (!enc) return false;
-    const cuuint64_t tok = (cuuint64_t)strides[1] * 2;
-    cuuint64_t dims[5] = {(cuuint64_t)heads * dh, (cuuint64_t)p.L[2], (cuuint64_t)p.L[1], (cuuint64_t)p.L[0], (cuuint64_t)p.B};
-    cuuint64_t gstr[4] = {tok, tok * p.L[2], tok * p.L[2] * p.L[1], (cuuint64_t)strides[0] * 2};
-    cuuint32_t bx[5] = {64, (cuuint32_t)box[2], (cuuint32_t)box[1], (cuuint32_t)box[0], 1};
-    cuuint32_t es[5] = {1, (cuuint32_t)p.dil[2], (cuuint32_t)p.dil[1], (cuuint32_t)p.dil[0], 1};
-    if (dims[4] == 0) return false;
-    const CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
-                           const_cast<void*>(base), dims, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
-}
-
-bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, const void* v)
-{
-    if (dtype != 1 && dtype != 2) return false;                 // f16 / bf16
-    if (g.D != 64 || g.Dv != 64) return false;
-    if (g.n_extra != 0) return false;
-    if (!(g.scale > 0.0)) return false;
-    for (int a = 0; a < g.rank; ++a) {
-        if (g.st[a] != 1) return false;
-        if ((g.K[a] & 1) == 0) return false;                    // even kernels: SIMT path
-        if (g.extents && g.dil[a] != 1) return false;
-    }
-    // heads must be adjacent so that (head, channel) folds into one map dimension
-    if (g.qs[2] != g.D || g.ks[2] != g.D || g.vs[2] != g.Dv) return false;
-    const long long strs[6] = {g.qs[0], g.qs[1], g.ks[0], g.ks[1], g.vs[0], g.vs[1]};
-    for (long long s : strs)
-        if (s % 8 != 0) return false;                           // 16-byte global strides
-    const void* ptrs[3] = {q, k, v};
-    for (const void* p : ptrs)
-        if (reinterpret_cast<uintptr_t>(p) & 15u) return false;
-    return true;
-}
-
-int* status_ptr()
-{
-    int* p = nullptr;
-    cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_tc_status);
-    return p;
-}
-
 } // namespace
 
 int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const void* v, const void* ek,
@@ -577,15 +423,6 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     tc_count_launch();
     return err == cudaSuccess ? 0 : (int)err;
 }
-
-int tc_fused_bwd(int, const Geo&, const void*, const void*, const void*, const void*, const void*,
-                 const void*, const void*, const void*, const void*, void*, void*, void*, void*, void*,
-                 void*, cudaStream_t)
-{
-    return -2;
-}
-
-size_t tc_bwd_workspace_bytes(int, const Geo&) { return 0; }
 
 static unsigned long long g_tc_launches = 0;
 void tc_count_launch() { ++g_tc_launches; }

@@ -1,0 +1,213 @@
+// Shared by the tensor-core kernels: launch geometry (tile / chunk shapes), tensor-map
+// encoding, eligibility and the per-row mask words.
+#pragma once
+#include "geometry.cuh"
+#include "tc_common.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <mutex>
+
+namespace natten {
+namespace tcplan {
+
+using namespace tc;
+
+constexpr int kTileRows = 128;           // rows per CTA     (MMA M)
+constexpr int kChunk = 128;              // columns per chunk (MMA N of S, K of the second MMA)
+
+// Geometry is always three axes; lower ranks get leading axes of extent 1.
+struct TcParams {
+    int L[3], K[3], dil[3], causal[3];
+    int tile[3], cb[3], nchunk[3], ntile[3];
+    int cb1_log, cb2_log;
+    int rank, B, Hq, Hkv, group, ntiles, nchunks;
+    float scale_log2, scale;
+    const int* extents;
+    long long ltot;
+    int* status;
+};
+
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Validity bits of one 32-column piece of a chunk for a row whose valid columns are the
+// box [f0,e0) x [f1,e1) x [f2,e2) (box coordinates).  ci = chunk index per axis,
+// bit j <-> column 32*pc + j of the chunk; columns run (j0, j1, j2) row-major over cb.
+__device__ __forceinline__ uint32_t piece_word(const TcParams& P, const int (&ci)[3], int pc,
+                                               const int (&f)[3], const int (&e)[3])
+{
+    const int seg = P.cb[2] < 32 ? P.cb[2] : 32;
+    const int nseg = 32 / seg;
+    uint32_t w = 0;
+    for (int sg = 0; sg < nseg; ++sg) {
+        const int jj = 32 * pc + sg * seg;
+        const int j2 = jj & (P.cb[2] - 1);
+        const int j1 = (jj >> P.cb2_log) & (P.cb[1] - 1);
+        const int j0 = jj >> (P.cb2_log + P.cb1_log);
+        const int i0 = ci[0] * P.cb[0] + j0, i1 = ci[1] * P.cb[1] + j1;
+        const int base2 = ci[2] * P.cb[2] + j2;
+        int lo2 = f[2] - base2, hi2 = e[2] - base2;
+        lo2 = lo2 > 0 ? lo2 : 0;
+        hi2 = hi2 < seg ? hi2 : seg;
+        if (i0 >= f[0] && i0 < e[0] && i1 >= f[1] && i1 < e[1] && hi2 > lo2) {
+            const uint32_t run = (hi2 - lo2 >= 32) ? 0xffffffffu : ((1u << (hi2 - lo2)) - 1u);
+            w |= (run << lo2) << (sg * seg);
+        }
+    }
+    return w;
+}
+
+__device__ __forceinline__ uint32_t pack16(float a, float b, bool bf16)
+{
+    if (bf16) {
+        __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&t);
+    }
+    __half2 t = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeFn get_encode()
+{
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+    });
+    return fn;
+}
+
+inline int ilog2(int x) { int l = 0; while ((1 << l) < x) ++l; return l; }
+inline int pow2ceil(int x) { return 1 << ilog2(x); }
+
+// Internal geometry always has three axes; lower ranks get leading axes of size 1.
+struct Plan {
+    TcParams p;
+    int box_q[3], box_kv[3];
+};
+
+// Pick the query-tile shape whose key box needs the fewest 128-key chunks.
+inline bool make_plan(const Geo& g, Plan& plan)
+{
+    TcParams& p = plan.p;
+    const int pad = 3 - g.rank;
+    for (int a = 0; a < 3; ++a) {
+        const int s = a - pad;
+        p.L[a] = s >= 0 ? g.L[s] : 1;
+        p.K[a] = s >= 0 ? g.K[s] : 1;
+        p.dil[a] = s >= 0 ? g.dil[s] : 1;
+        p.causal[a] = s >= 0 ? g.causal[s] : 0;
+    }
+    long long best = -1;
+    for (int t2 = 1; t2 <= 128; t2 *= 2)
+        for (int t1 = 1; t1 * t2 <= 128; t1 *= 2) {
+            const int t0 = 128 / (t1 * t2);
+            const int t[3] = {t0, t1, t2};
+            bool fits = true;
+            for (int a = 0; a < 3; ++a)
+                if (p.L[a] == 1 && t[a] != 1) fits = false;      // unused axis
+            if (!fits) continue;
+            const int E2 = t2 + p.K[2] - 1;
+            int cb2 = pow2ceil(E2);
+            if (cb2 > 128) cb2 = 128;
+            if (cb2 * p.dil[2] > 256) continue;                  // TMA box limit
+            const int E1 = t1 + p.K[1] - 1;
+            int cb1 = 128 / cb2;
+            if (p.L[1] == 1) cb1 = 1;
+            if (cb1 > pow2ceil(E1)) cb1 = pow2ceil(E1);
+            if (cb1 * p.dil[1] > 256) continue;
+            int cb0 = 128 / (cb2 * cb1);
+            if (p.L[0] == 1 && cb0 != 1) continue;               // would leave the chunk short of 128 keys
+            if (cb0 * p.dil[0] > 256) continue;
+            const int E0 = t0 + p.K[0] - 1;
+            const long long n = (long long)((E0 + cb0 - 1) / cb0) * ((E1 + cb1 - 1) / cb1) * ((E2 + cb2 - 1) / cb2);
+            // prefer fewer chunks, then wider innermost tiles
+            if (best < 0 || n < best) {
+                best = n;
+                for (int a = 0; a < 3; ++a) p.tile[a] = t[a];
+                p.cb[0] = cb0; p.cb[1] = cb1; p.cb[2] = cb2;
+                p.nchunk[0] = (E0 + cb0 - 1) / cb0; p.nchunk[1] = (E1 + cb1 - 1) / cb1; p.nchunk[2] = (E2 + cb2 - 1) / cb2;
+            }
+        }
+    if (best < 0) return false;
+    p.cb1_log = ilog2(p.cb[1]); p.cb2_log = ilog2(p.cb[2]);
+    p.nchunks = (int)best;
+    p.ntiles = 1;
+    for (int a = 0; a < 3; ++a) {
+        const int lp = (p.L[a] + p.dil[a] - 1) / p.dil[a];
+        p.ntile[a] = (lp + p.tile[a] - 1) / p.tile[a];
+        p.ntiles *= p.ntile[a];
+        plan.box_q[a] = p.tile[a] * p.dil[a];
+        plan.box_kv[a] = p.cb[a] * p.dil[a];
+        if (plan.box_q[a] > 256) return false;
+    }
+    p.rank = g.rank; p.B = g.B; p.Hq = g.Hq; p.Hkv = g.Hkv; p.group = g.group;
+    p.scale_log2 = (float)(g.scale * 1.4426950408889634);
+    p.scale = (float)g.scale;
+    p.extents = g.extents;
+    p.ltot = g.ltot;
+    return true;
+}
+
+// 5-D map over [B, X0, X1, X2, heads*D] (innermost first in the arrays below).
+inline bool encode_map(CUtensorMap* map, const void* base, bool bf16, const TcParams& p, int heads, int dh,
+                const long long strides[3], const int box[3])
+{
+    EncodeFn enc = get_encode();
+    if (!enc) return false;
+    const cuuint64_t tok = (cuuint64_t)strides[1] * 2;
+    cuuint64_t dims[5] = {(cuuint64_t)heads * dh, (cuuint64_t)p.L[2], (cuuint64_t)p.L[1], (cuuint64_t)p.L[0], (cuuint64_t)p.B};
+    cuuint64_t gstr[4] = {tok, tok * p.L[2], tok * p.L[2] * p.L[1], (cuuint64_t)strides[0] * 2};
+    cuuint32_t bx[5] = {64, (cuuint32_t)box[2], (cuuint32_t)box[1], (cuuint32_t)box[0], 1};
+    cuuint32_t es[5] = {1, (cuuint32_t)p.dil[2], (cuuint32_t)p.dil[1], (cuuint32_t)p.dil[0], 1};
+    if (dims[4] == 0) return false;
+    const CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
+                           const_cast<void*>(base), dims, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, const void* v)
+{
+    if (dtype != 1 && dtype != 2) return false;                 // f16 / bf16
+    if (g.D != 64 || g.Dv != 64) return false;
+    if (g.n_extra != 0) return false;
+    if (!(g.scale > 0.0)) return false;
+    for (int a = 0; a < g.rank; ++a) {
+        if (g.st[a] != 1) return false;
+        if ((g.K[a] & 1) == 0) return false;                    // even kernels: SIMT path
+        if (g.extents && g.dil[a] != 1) return false;
+    }
+    // heads must be adjacent so that (head, channel) folds into one map dimension
+    if (g.qs[2] != g.D || g.ks[2] != g.D || g.vs[2] != g.Dv) return false;
+    const long long strs[6] = {g.qs[0], g.qs[1], g.ks[0], g.ks[1], g.vs[0], g.vs[1]};
+    for (long long s : strs)
+        if (s % 8 != 0) return false;                           // 16-byte global strides
+    const void* ptrs[3] = {q, k, v};
+    for (const void* p : ptrs)
+        if (reinterpret_cast<uintptr_t>(p) & 15u) return false;
+    return true;
+}
+
+int* status_ptr();   // device address of the library's status word (defined in tc_fwd.cu)
+
+
+} // namespace tcplan
+} // namespace natten
