@@ -327,7 +327,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             ok = ok && mbar_wait(bar_s, cc & 1, abort_flag);
             tc_fence_after();
             uint32_t pk_p[16], pk_ds[16];
-            if (any && ok) {
+            if (any) {
                 uint32_t s[32], dp[32];
                 tmem_ld32(trow + kColS + 32 * piece, s);
                 tmem_ld32(trow + kColDP + 32 * piece, dp);
@@ -351,7 +351,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                     pk_ds[i] = pack16(dsv[0], dsv[1], BF16);
                 }
             } else {
-                if (kKeySide && !any) ok = ok && mbar_wait(bar_stats + 8 * (cc % kStages), (cc / kStages) & 1, abort_flag);
+                if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (cc % kStages), (cc / kStages) & 1, abort_flag);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) { pk_p[i] = 0u; pk_ds[i] = 0u; }
             }
@@ -367,14 +367,15 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         // ---- accumulators -> global: this warp owns 16 of the 64 channels ----
         ok = ok && mbar_wait(bar_acc, (total - 1) & 1, abort_flag);
         tc_fence_after();
-        if (in_tensor) {
-            const bool live = valid_row && ok;
+        // The TMEM loads are warp-collective: every lane takes part, only the stores are per row.
+        const bool live = valid_row && ok;
 #pragma unroll
-            for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
-                uint32_t a[32];
-                // 32x32b.x32 reads 32 columns; only the 16 owned by this warp are used
-                tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + 32 * (piece >> 1), a);
-                tmem_ld_wait();
+        for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
+            uint32_t a[32];
+            // 32x32b.x32 reads 32 columns; only the 16 owned by this warp are used
+            tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + 32 * (piece >> 1), a);
+            tmem_ld_wait();
+            if (in_tensor) {
                 uint32_t w[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
