@@ -1,23 +1,29 @@
 // Fused neighbourhood-attention backward on tcgen05 tensor cores (sm_100a).
 //
 // Two launches of one kernel template, neither materialises P or dS in memory:
-//   * query side (kQuerySide): rows = a box of 128 queries, columns = chunks of the
-//     key box.  S = Q K^T, dP = dO V^T (tensor cores, TMEM); threads turn them into
+//   * query side: rows = a box of 128 queries, columns = chunks of the key box.
+//     S = Q K^T, dP = dO V^T (tensor cores, TMEM); threads turn them into
 //     dS = P (dP - delta) * scale with P = exp2(S*scale*log2e - lse*log2e); dQ += dS K.
-//   * key side (kKeySide): rows = a box of 128 keys, columns = chunks of the box of
-//     queries that attend to them (the inverse neighbourhood, a contiguous range per
-//     axis for odd kernels), for every query head of the GQA group.  S^T = K Q^T,
-//     dP^T = V dO^T; dV += P^T dO, dK += dS^T Q.  Per-column lse / delta are staged in
-//     shared memory by a helper warp.
+//   * key side: rows = a box of 128 keys, columns = chunks of the box of queries that
+//     attend to them (the inverse neighbourhood, a contiguous range per axis for odd
+//     kernels), for every query head of the GQA group.  S^T = K Q^T, dP^T = V dO^T;
+//     dV += P^T dO, dK += dS^T Q.  Per-column lse / delta are staged in shared memory
+//     by a helper warp.
 // The row accumulators live in TMEM for the whole CTA, so dK/dV are reduced in a
 // fixed order: results are bit-reproducible, no atomics.
 //
-// Warps: 16 compute warps (four per TMEM lane quadrant, each owns one 32-column piece
-// of the chunk), one TMA + MMA issuing warp, one column-statistics warp.
-// TMEM (512 columns): S [0,128) dP [128,256) P [256,320) dS [320,384) acc1 [384,448) acc2 [448,512).
+// Chunks are 64 columns wide so that a CTA needs only 256 TMEM columns and 98 KB of
+// shared memory: two CTAs share an SM and one computes while the other waits for its
+// MMAs or loads.  Warps: 8 compute warps (two per TMEM lane quadrant, each owns one
+// 32-column piece of the chunk), one TMA + MMA issuing warp, one column-statistics warp.
+// TMEM: S [0,64)  dP [64,128)  acc1 [128,192)  acc2 [192,256).  The 16-bit P and dS that
+// feed the accumulating MMAs overwrite the first half of the S / dP columns of the piece
+// they were computed from (same warp, after it has read them).
 #include "tc_kernels.cuh"
 
 #include "tc_plan.cuh"
+
+#include <type_traits>
 
 namespace natten {
 
@@ -26,20 +32,22 @@ using namespace tcplan;
 
 namespace {
 
+constexpr int kCols = 64;                   // columns per chunk
 constexpr int kStages = 4;
-constexpr int kComputeWarps = 16;
+constexpr int kComputeWarps = 8;
 constexpr int kThreads = (kComputeWarps + 2) * 32;
-constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColDP = 128, kColP = 256, kColDS = 320, kColA1 = 384, kColA2 = 448;
-constexpr int kTile = kTileRows * 128;      // bytes of one [128 x 64] 16-bit tile
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0, kColDP = 64, kColA1 = 128, kColA2 = 192;
+constexpr int kTile = kTileRows * 128;      // bytes of one [128 x 64] 16-bit row tile
+constexpr int kColTile = kCols * 128;       // bytes of one [64 x 64] 16-bit column tile
 
 struct Smem {
     static constexpr int kR1 = 0;
     static constexpr int kR2 = kR1 + kTile;
     static constexpr int kC1 = kR2 + kTile;                     // [kStages]
-    static constexpr int kC2 = kC1 + kStages * kTile;           // [kStages]
-    static constexpr int kStats = kC2 + kStages * kTile;        // [kStages][2][128] float
-    static constexpr int kBar = kStats + kStages * 1024;
+    static constexpr int kC2 = kC1 + kStages * kColTile;        // [kStages]
+    static constexpr int kStats = kC2 + kStages * kColTile;     // [kStages][2][64] float
+    static constexpr int kBar = kStats + kStages * 512;
     static constexpr int kTotal = kBar + 256;
 };
 
@@ -57,8 +65,10 @@ __device__ __forceinline__ void inverse_range(int n, int L, int K, int causal, i
     }
 }
 
-template <bool BF16, bool kKeySide>
-__global__ void __launch_bounds__(kThreads, 1)
+// kInner: innermost chunk extent when it is 16 or 32 (separable row / column masks, packed
+// 16-bit arithmetic), 0 = any geometry (per-column validity words).
+template <bool BF16, bool kKeySide, int kInner>
+__global__ void __launch_bounds__(kThreads, 2)
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
               const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2,
               const __grid_constant__ TcParams P, const float* __restrict__ lse,
@@ -75,16 +85,18 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     int gidx = blockIdx.x / P.ntiles, tidx = blockIdx.x % P.ntiles;
     int rg[3], origin[3], Lp[3], boxlo[3], nc[3];
     bool cta_active = true;
-    for (int a = 2; a >= 0; --a) {
+    auto axis_setup = [&](const int a) {
         rg[a] = gidx % P.dil[a]; gidx /= P.dil[a];
         origin[a] = (tidx % P.ntile[a]) * P.tile[a]; tidx /= P.ntile[a];
         const int ea = a - (3 - P.rank);
         const int Ls = (P.extents && ea >= 0) ? P.extents[b * P.rank + ea] : P.L[a];
         Lp[a] = rg[a] < Ls ? (Ls - rg[a] + P.dil[a] - 1) / P.dil[a] : 0;
         if (origin[a] >= Lp[a]) cta_active = false;
-    }
+    };
+    axis_setup(2); axis_setup(1); axis_setup(0);
     int nchunks = 1;
-    if (cta_active)
+    if (cta_active) {
+#pragma unroll
         for (int a = 0; a < 3; ++a) {
             const int last = origin[a] + P.tile[a] - 1 < Lp[a] - 1 ? origin[a] + P.tile[a] - 1 : Lp[a] - 1;
             int hi;
@@ -99,6 +111,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             nc[a] = (hi - boxlo[a] + P.cb[a]) / P.cb[a];
             nchunks *= nc[a];
         }
+    }
 
     // ---- per-thread row ------------------------------------------------------
     int f[3] = {0, 0, 0}, e[3] = {0, 0, 0};
@@ -114,6 +127,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         ri[0] = r;
         valid_row = true; in_tensor = true;
         long long pflat = 0;
+#pragma unroll
         for (int a = 0; a < 3; ++a) {
             const int xa = origin[a] + ri[a];
             const int pa = rg[a] + P.dil[a] * xa;
@@ -135,19 +149,19 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         }
         if (!valid_row) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
         out_row = ((long long)b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + hy;
-        if (!kKeySide && valid_row && cta_active) {
-            row_lse2 = lse[out_row] * 1.4426950408889634f;
-            row_delta = delta[out_row];
+        if (!kKeySide && valid_row && cta_active) {          // negated, pre-scaled addends
+            row_lse2 = -lse[out_row] * 1.4426950408889634f;
+            row_delta = -delta[out_row] * P.scale;
         }
     }
 
     if (!cta_active) {                       // padding rows get zero gradients
         if (warp < kComputeWarps && in_tensor) {
-            uint4* o1 = reinterpret_cast<uint4*>(out1 + out_row * DH + piece * 16);
-            o1[0] = make_uint4(0, 0, 0, 0); o1[1] = make_uint4(0, 0, 0, 0);
-            if (kKeySide) {
-                uint4* o2 = reinterpret_cast<uint4*>(out2 + out_row * DH + piece * 16);
-                o2[0] = make_uint4(0, 0, 0, 0); o2[1] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
+                uint4* o = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * DH + piece * 32);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[i] = make_uint4(0, 0, 0, 0);
             }
         }
         return;
@@ -203,14 +217,15 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 int ci[3], hc;
                 chunk_index(cc, ci, hc);
                 int X[3];
+#pragma unroll
                 for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (boxlo[a] + ci[a] * P.cb[a]);
                 const int s = cc % kStages;
                 const uint32_t bar = bar_col + 8 * s;
                 // query side: columns are keys (kv head); key side: columns are queries (query head)
                 const int hx = (kKeySide ? hc : head_kv) * DH;
-                mbar_expect_tx(bar, 2 * kTile);
-                tma_load_5d(sbase + Smem::kC1 + s * kTile, &tmC1, bar, hx, X[2], X[1], X[0], b);
-                tma_load_5d(sbase + Smem::kC2 + s * kTile, &tmC2, bar, hx, X[2], X[1], X[0], b);
+                mbar_expect_tx(bar, 2 * kColTile);
+                tma_load_5d(sbase + Smem::kC1 + s * kColTile, &tmC1, bar, hx, X[2], X[1], X[0], b);
+                tma_load_5d(sbase + Smem::kC2 + s * kColTile, &tmC2, bar, hx, X[2], X[1], X[0], b);
             };
             {
                 const int hx = (kKeySide ? head_kv : head_row) * DH;
@@ -222,7 +237,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             }
             for (int cc = 0; cc < total && cc < kStages; ++cc) issue_cols(cc);
 
-            constexpr uint32_t idesc_kk = instr_desc(BF16 ? 1 : 0, kChunk, 0, 0);   // both operands K-major
+            constexpr uint32_t idesc_kk = instr_desc(BF16 ? 1 : 0, kCols, 0, 0);    // both operands K-major
             constexpr uint32_t idesc_acc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A from TMEM, B MN-major
             auto issue_s_dp = [&](int cc) {
                 const int s = cc % kStages;
@@ -230,26 +245,28 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
 #pragma unroll
                 for (int ks = 0; ks < DH / 16; ++ks)
                     mma_ss(tmem + kColS, smem_desc(sbase + Smem::kR1 + ks * 32, 16, 1024),
-                           smem_desc(sbase + Smem::kC1 + s * kTile + ks * 32, 16, 1024), idesc_kk, ks > 0);
+                           smem_desc(sbase + Smem::kC1 + s * kColTile + ks * 32, 16, 1024), idesc_kk, ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < DH / 16; ++ks)
                     mma_ss(tmem + kColDP, smem_desc(sbase + Smem::kR2 + ks * 32, 16, 1024),
-                           smem_desc(sbase + Smem::kC2 + s * kTile + ks * 32, 16, 1024), idesc_kk, ks > 0);
+                           smem_desc(sbase + Smem::kC2 + s * kColTile + ks * 32, 16, 1024), idesc_kk, ks > 0);
                 mma_commit(bar_s);
             };
+            // k-step ks covers columns 16*ks..16*ks+15 of the chunk; their 16-bit pairs sit in the
+            // first 16 TMEM columns of the 32-column piece they came from.
             auto issue_acc = [&](int cc) {
                 const int s = cc % kStages;
                 tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < kChunk / 16; ++ks)
-                    mma_ts(tmem + kColA1, tmem + kColDS + 8 * ks,
-                           smem_desc(sbase + Smem::kC1 + s * kTile + ks * 2048, kTile, 1024), idesc_acc,
+                for (int ks = 0; ks < kCols / 16; ++ks)
+                    mma_ts(tmem + kColA1, tmem + kColDP + 32 * (ks / 2) + 8 * (ks % 2),
+                           smem_desc(sbase + Smem::kC1 + s * kColTile + ks * 2048, kColTile, 1024), idesc_acc,
                            (cc > 0 || ks > 0) ? 1u : 0u);
                 if (kKeySide) {
 #pragma unroll
-                    for (int ks = 0; ks < kChunk / 16; ++ks)
-                        mma_ts(tmem + kColA2, tmem + kColP + 8 * ks,
-                               smem_desc(sbase + Smem::kC2 + s * kTile + ks * 2048, kTile, 1024), idesc_acc,
+                    for (int ks = 0; ks < kCols / 16; ++ks)
+                        mma_ts(tmem + kColA2, tmem + kColS + 32 * (ks / 2) + 8 * (ks % 2),
+                               smem_desc(sbase + Smem::kC2 + s * kColTile + ks * 2048, kColTile, 1024), idesc_acc,
                                (cc > 0 || ks > 0) ? 1u : 0u);
                 }
                 mma_commit(bar_acc);
@@ -261,12 +278,12 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             for (int cc = 0; cc < total && ok; ++cc) {
                 ok = mbar_wait(bar_sp, cc & 1, abort_flag);              // S/dP consumed, P/dS stored
                 if (!ok) break;
+                issue_acc(cc);                                           // reads P/dS ...
                 if (cc + 1 < total) {
                     ok = mbar_wait(bar_col + 8 * ((cc + 1) % kStages), ((cc + 1) / kStages) & 1, abort_flag);
                     if (!ok) break;
-                    issue_s_dp(cc + 1);                                  // next chunk's S/dP first ...
+                    issue_s_dp(cc + 1);                                  // ... before the next S/dP overwrite them
                 }
-                issue_acc(cc);                                           // ... then this chunk's accumulation
                 if (cc + kStages < total) {
                     ok = mbar_wait(bar_acc, cc & 1, abort_flag);         // stage cc % kStages is free again
                     if (!ok) break;
@@ -285,29 +302,27 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 if (cc >= kStages) ok = ok && mbar_wait(bar_acc, (cc - kStages) & 1, abort_flag);
                 int ci[3], hc;
                 chunk_index(cc, ci, hc);
-                float* st = stats + s * 256;
+                float* st = stats + s * 128;
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
+                for (int k = 0; k < kCols / 32; ++k) {
                     const int j = lane + 32 * k;
                     const int j2 = j & (P.cb[2] - 1);
                     const int j1 = (j >> P.cb2_log) & (P.cb[1] - 1);
                     const int j0 = j >> (P.cb2_log + P.cb1_log);
-                    const int jj[3] = {j0, j1, j2};
-                    bool inside = ok;
-                    long long pflat = 0;
-                    for (int a = 0; a < 3; ++a) {
-                        const int qa = boxlo[a] + ci[a] * P.cb[a] + jj[a];
-                        if (qa < 0 || qa >= Lp[a]) inside = false;
-                        pflat = pflat * P.L[a] + (rg[a] + P.dil[a] * qa);
-                    }
+                    const int q0 = boxlo[0] + ci[0] * P.cb[0] + j0;
+                    const int q1 = boxlo[1] + ci[1] * P.cb[1] + j1;
+                    const int q2 = boxlo[2] + ci[2] * P.cb[2] + j2;
+                    const bool inside = ok && q0 >= 0 && q0 < Lp[0] && q1 >= 0 && q1 < Lp[1] && q2 >= 0 && q2 < Lp[2];
                     float l2 = 0.f, dl = 0.f;
                     if (inside) {
+                        const long long pflat = ((long long)(rg[0] + P.dil[0] * q0) * P.L[1] + (rg[1] + P.dil[1] * q1)) * P.L[2]
+                                                + (rg[2] + P.dil[2] * q2);
                         const long long row = ((long long)b * P.ltot + pflat) * P.Hq + hc;
-                        l2 = lse[row] * 1.4426950408889634f;
-                        dl = delta[row];
+                        l2 = -lse[row] * 1.4426950408889634f;        // negated, pre-scaled addends
+                        dl = -delta[row] * P.scale;
                     }
                     st[j] = l2;
-                    st[128 + j] = dl;
+                    st[kCols + j] = dl;
                 }
                 mbar_arrive(bar_stats + 8 * s);
             }
@@ -318,53 +333,122 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         // =====================================================================
         const uint32_t trow = tmem + (static_cast<uint32_t>(quad * 32) << 16);
         bool ok = true;
+        constexpr int kPairs = kInner > 0 ? kInner / 2 : 1;
+        constexpr int kRows = kInner > 0 ? 32 / kInner : 1;
         for (int cc = 0; cc < total; ++cc) {
             int ci[3], hc;
             chunk_index(cc, ci, hc);
-            const uint32_t word = piece_word(P, ci, piece, f, e);
-            const bool any = __any_sync(0xffffffffu, word != 0u);
 
-            ok = ok && mbar_wait(bar_s, cc & 1, abort_flag);
-            tc_fence_after();
-            uint32_t pk_p[16], pk_ds[16];
-            if (any) {
-                uint32_t s[32], dp[32];
-                tmem_ld32(trow + kColS + 32 * piece, s);
-                tmem_ld32(trow + kColDP + 32 * piece, dp);
-                const float* st = stats + (cc % kStages) * 256 + 32 * piece;
-                if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (cc % kStages), (cc / kStages) & 1, abort_flag);
-                tmem_ld_wait();
+            // ---- validity of this warp's 32 columns for this thread's row ----
+            uint32_t word = 0u;                  // generic geometry: one bit per column
+            uint32_t colmask[kPairs];            // separable geometry: 16-bit lane masks per column pair
+            uint32_t rowmask[kRows];             //                      all-ones / zero per inner row
+            bool mine = false;
+            if (kInner > 0) {
+                const int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float pv[2], dsv[2];
+                for (int i = 0; i < kPairs; ++i)
+                    colmask[i] = ((2 * i >= lo2 && 2 * i < hi2) ? 0x0000FFFFu : 0u) |
+                                 ((2 * i + 1 >= lo2 && 2 * i + 1 < hi2) ? 0xFFFF0000u : 0u);
+                const bool cols_any = hi2 > 0 && lo2 < kInner && hi2 > lo2;
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int j = 2 * i + u;
-                        const float l2 = kKeySide ? st[j] : row_lse2;
-                        const float dl = kKeySide ? st[128 + j] : row_delta;
-                        const bool on = (word >> j) & 1u;
-                        const float p = on ? fast_exp2(__uint_as_float(s[j]) * P.scale_log2 - l2) : 0.f;
-                        pv[u] = p;
-                        dsv[u] = p * (__uint_as_float(dp[j]) - dl) * P.scale;
-                    }
-                    pk_p[i] = pack16(pv[0], pv[1], BF16);
-                    pk_ds[i] = pack16(dsv[0], dsv[1], BF16);
+                for (int t = 0; t < kRows; ++t) {
+                    const int jj = 32 * piece + t * kInner;
+                    const int j1 = (jj >> P.cb2_log) & (P.cb[1] - 1);
+                    const int j0 = jj >> (P.cb2_log + P.cb1_log);
+                    const int i0 = ci[0] * P.cb[0] + j0, i1 = ci[1] * P.cb[1] + j1;
+                    const bool rok = i0 >= f[0] && i0 < e[0] && i1 >= f[1] && i1 < e[1];
+                    rowmask[t] = rok ? 0xFFFFFFFFu : 0u;
+                    mine = mine || (rok && cols_any);
                 }
             } else {
-                if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (cc % kStages), (cc / kStages) & 1, abort_flag);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) { pk_p[i] = 0u; pk_ds[i] = 0u; }
+                word = piece_word(P, ci, piece, f, e);
+                mine = word != 0u;
             }
-            if (cc > 0) ok = ok && mbar_wait(bar_acc, (cc - 1) & 1, abort_flag);   // previous P/dS consumed
+            const bool any = __any_sync(0xffffffffu, mine);
+            const bool full = kInner == 0 && __all_sync(0xffffffffu, word == 0xffffffffu);
+
+            ok = ok && mbar_wait(bar_s, cc & 1, abort_flag);     // also: the previous chunk's P/dS were consumed
+            if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (cc % kStages), (cc / kStages) & 1, abort_flag);
             tc_fence_after();
-            tmem_st16(trow + kColDS + 16 * piece, pk_ds);
-            if (kKeySide) tmem_st16(trow + kColP + 16 * piece, pk_p);
+            if (any) {
+                const float* stp = stats + (cc % kStages) * 128 + 32 * piece;
+                const float4* st4 = reinterpret_cast<const float4*>(stp);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {               // 16 columns at a time
+                    uint32_t s[16], dp[16], pk_p[8], pk_ds[8];
+                    tmem_ld16(trow + kColS + 32 * piece + 16 * half, s);
+                    tmem_ld16(trow + kColDP + 32 * piece + 16 * half, dp);
+                    tmem_ld_wait();
+                    if (kInner > 0 || full) {
+                        // P = 2^(s*c - lse2), dS = P * (dP*scale - delta*scale); fp32, rounded once each
+#pragma unroll
+                        for (int g4 = 0; g4 < 4; ++g4) {             // four columns at a time
+                            float nl[4], nd[4];
+                            if (kKeySide) {
+                                const float4 a = st4[4 * half + g4], d = st4[kCols / 4 + 4 * half + g4];
+                                nl[0] = a.x; nl[1] = a.y; nl[2] = a.z; nl[3] = a.w;
+                                nd[0] = d.x; nd[1] = d.y; nd[2] = d.z; nd[3] = d.w;
+                            } else {
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) { nl[u] = row_lse2; nd[u] = row_delta; }
+                            }
+#pragma unroll
+                            for (int h2 = 0; h2 < 2; ++h2) {
+                                const int pl = 2 * g4 + h2, j = 2 * pl;      // pair / column inside the half
+                                const int pi = 8 * half + pl;                // pair inside the piece
+                                const float x0 = fmaf(__uint_as_float(s[j]), P.scale_log2, nl[2 * h2]);
+                                const float x1 = fmaf(__uint_as_float(s[j + 1]), P.scale_log2, nl[2 * h2 + 1]);
+                                const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                                const float g0 = fmaf(__uint_as_float(dp[j]), P.scale, nd[2 * h2]);
+                                const float g1 = fmaf(__uint_as_float(dp[j + 1]), P.scale, nd[2 * h2 + 1]);
+                                uint32_t pp = cvt_pack<BF16>(p0, p1);
+                                uint32_t dd = cvt_pack<BF16>(p0 * g0, p1 * g1);
+                                if (kInner > 0) {
+                                    const uint32_t m = colmask[pi % kPairs] & rowmask[pi / kPairs];
+                                    pp &= m;
+                                    dd &= m;
+                                }
+                                pk_p[pl] = pp;
+                                pk_ds[pl] = dd;
+                            }
+                        }
+                    } else {
+                        const float* st = stp + 16 * half;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float pv[2], dsv[2];
+#pragma unroll
+                            for (int u = 0; u < 2; ++u) {
+                                const int j = 2 * i + u;
+                                const float nl = kKeySide ? st[j] : row_lse2;
+                                const float nd = kKeySide ? st[kCols + j] : row_delta;
+                                const bool on = (word >> (16 * half + j)) & 1u;
+                                const float p = on ? fast_exp2(fmaf(__uint_as_float(s[j]), P.scale_log2, nl)) : 0.f;
+                                pv[u] = p;
+                                dsv[u] = p * fmaf(__uint_as_float(dp[j]), P.scale, nd);
+                            }
+                            pk_p[i] = pack16(pv[0], pv[1], BF16);
+                            pk_ds[i] = pack16(dsv[0], dsv[1], BF16);
+                        }
+                    }
+                    // the pairs overwrite columns this warp has already read
+                    tmem_st8(trow + kColDP + 32 * piece + 8 * half, pk_ds);
+                    if (kKeySide) tmem_st8(trow + kColS + 32 * piece + 8 * half, pk_p);
+                }
+            } else {                             // nothing valid here: the MMA must read zeros
+                uint32_t z[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) z[i] = 0u;
+                tmem_st16(trow + kColDP + 32 * piece, z);
+                if (kKeySide) tmem_st16(trow + kColS + 32 * piece, z);
+            }
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(bar_sp);
         }
 
-        // ---- accumulators -> global: this warp owns 16 of the 64 channels ----
+        // ---- accumulators -> global: this warp owns 32 of the 64 channels ----
         ok = ok && mbar_wait(bar_acc, (total - 1) & 1, abort_flag);
         tc_fence_after();
         // The TMEM loads are warp-collective: every lane takes part, only the stores are per row.
@@ -372,20 +456,18 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
 #pragma unroll
         for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
             uint32_t a[32];
-            // 32x32b.x32 reads 32 columns; only the 16 owned by this warp are used
-            tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + 32 * (piece >> 1), a);
+            tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + 32 * piece, a);
             tmem_ld_wait();
             if (in_tensor) {
-                uint32_t w[8];
+                uint4* d4 = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * DH + piece * 32);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int c0 = 16 * (piece & 1) + 2 * i;
-                    w[i] = live ? pack16(__uint_as_float(a[c0]), __uint_as_float(a[c0 + 1]), BF16) : 0u;
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        w[j] = live ? pack16(__uint_as_float(a[8 * i + 2 * j]), __uint_as_float(a[8 * i + 2 * j + 1]), BF16) : 0u;
+                    d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                uint16_t* dst = (which == 0 ? out1 : out2) + out_row * DH + piece * 16;
-                uint4* d4 = reinterpret_cast<uint4*>(dst);
-                d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
         }
     }
@@ -457,20 +539,26 @@ int launch_bwd(const Geo& g, const Plan& plan, const void* q, const void* k, con
         return -2;
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= p.dil[a];
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(tc_bwd_kernel<BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
-        cudaFuncSetAttribute(tc_bwd_kernel<BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
-        attr_done = true;
-    }
     const dim3 grid_q((unsigned)(p.ntiles * ngroups), (unsigned)g.Hq, (unsigned)g.B);
     const dim3 grid_k((unsigned)(p.ntiles * ngroups), (unsigned)g.Hkv, (unsigned)g.B);
-    tc_bwd_kernel<BF16, false><<<grid_q, kThreads, Smem::kTotal, s>>>(
-        q_tile, do_tile, k_chunk, v_chunk, p, (const float*)lse, delta, (uint16_t*)dq, nullptr);
-    tc_count_launch();
-    tc_bwd_kernel<BF16, true><<<grid_k, kThreads, Smem::kTotal, s>>>(
-        k_tile, v_tile, q_chunk, do_chunk, p, (const float*)lse, delta, (uint16_t*)dk, (uint16_t*)dv);
-    tc_count_launch();
+    auto launch = [&](auto inner) {
+        constexpr int kInner = decltype(inner)::value;
+        static bool attr_done = false;
+        if (!attr_done) {
+            cudaFuncSetAttribute(tc_bwd_kernel<BF16, false, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+            cudaFuncSetAttribute(tc_bwd_kernel<BF16, true, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+            attr_done = true;
+        }
+        tc_bwd_kernel<BF16, false, kInner><<<grid_q, kThreads, Smem::kTotal, s>>>(
+            q_tile, do_tile, k_chunk, v_chunk, p, (const float*)lse, delta, (uint16_t*)dq, nullptr);
+        tc_count_launch();
+        tc_bwd_kernel<BF16, true, kInner><<<grid_k, kThreads, Smem::kTotal, s>>>(
+            k_tile, v_tile, q_chunk, do_chunk, p, (const float*)lse, delta, (uint16_t*)dk, (uint16_t*)dv);
+        tc_count_launch();
+    };
+    if (p.cb[2] == 16) launch(std::integral_constant<int, 16>{});
+    else if (p.cb[2] == 32) launch(std::integral_constant<int, 32>{});
+    else launch(std::integral_constant<int, 0>{});
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? 0 : (int)err;
 }
@@ -485,7 +573,7 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     if (!tc_eligible(dtype, g, q, k, v)) return -2;
     if (reinterpret_cast<uintptr_t>(dout) & 15u) return -2;
     Plan plan;
-    if (!make_plan(g, plan)) return -2;
+    if (!make_plan(g, plan, kCols)) return -2;
     plan.p.status = status_ptr();
     if (!plan.p.status) return -2;
     if (g.B == 0) return 0;

@@ -62,6 +62,29 @@ __device__ __forceinline__ uint32_t piece_word(const TcParams& P, const int (&ci
     return w;
 }
 
+// Packed 16-bit pair arithmetic (element 0 in the low half).
+template <bool BF16> __device__ __forceinline__ uint32_t cvt_pack(float lo, float hi)
+{
+    uint32_t d;
+    if (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+template <bool BF16> __device__ __forceinline__ uint32_t ex2_x2(uint32_t x)
+{
+    uint32_t d;
+    if (BF16) asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(d) : "r"(x));
+    else asm("ex2.approx.f16x2 %0, %1;" : "=r"(d) : "r"(x));
+    return d;
+}
+template <bool BF16> __device__ __forceinline__ uint32_t mul_x2(uint32_t a, uint32_t b)
+{
+    uint32_t d;
+    if (BF16) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    else asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t pack16(float a, float b, bool bf16)
 {
     if (bf16) {
@@ -102,8 +125,8 @@ struct Plan {
     int box_q[3], box_kv[3];
 };
 
-// Pick the query-tile shape whose key box needs the fewest 128-key chunks.
-inline bool make_plan(const Geo& g, Plan& plan)
+// Pick the row-tile shape (128 rows) whose column box needs the fewest chunks of `chunk` columns.
+inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk)
 {
     TcParams& p = plan.p;
     const int pad = 3 - g.rank;
@@ -125,15 +148,15 @@ inline bool make_plan(const Geo& g, Plan& plan)
             if (!fits) continue;
             const int E2 = t2 + p.K[2] - 1;
             int cb2 = pow2ceil(E2);
-            if (cb2 > 128) cb2 = 128;
+            if (cb2 > chunk) cb2 = chunk;
             if (cb2 * p.dil[2] > 256) continue;                  // TMA box limit
             const int E1 = t1 + p.K[1] - 1;
-            int cb1 = 128 / cb2;
+            int cb1 = chunk / cb2;
             if (p.L[1] == 1) cb1 = 1;
             if (cb1 > pow2ceil(E1)) cb1 = pow2ceil(E1);
             if (cb1 * p.dil[1] > 256) continue;
-            int cb0 = 128 / (cb2 * cb1);
-            if (p.L[0] == 1 && cb0 != 1) continue;               // would leave the chunk short of 128 keys
+            int cb0 = chunk / (cb2 * cb1);
+            if (p.L[0] == 1 && cb0 != 1) continue;               // would leave the chunk short of columns
             if (cb0 * p.dil[0] > 256) continue;
             const int E0 = t0 + p.K[0] - 1;
             const long long n = (long long)((E0 + cb0 - 1) / cb0) * ((E1 + cb1 - 1) / cb1) * ((E2 + cb2 - 1) / cb2);

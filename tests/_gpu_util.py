@@ -25,7 +25,10 @@ def rounded(a, dtype):
     return torch.as_tensor(np.asarray(a)).to(dtype).double().numpy()
 
 
-def check(name, got, want, dtype, scale_rel=True):
+def check(name, got, want, dtype, scale_rel=False):
+    """``scale_rel``: measure 16-bit results relative to the tensor's magnitude.  Used for the
+    split ops, whose raw (unscaled) logits reach |q||k| ~ 10: one bf16 ulp there is 0.03, so the
+    output format alone exceeds an absolute 2e-2."""
     got = got.detach().double().cpu().numpy()
     want = np.asarray(want, dtype=np.float64)
     assert got.shape == want.shape, (name, got.shape, want.shape)
@@ -36,7 +39,7 @@ def check(name, got, want, dtype, scale_rel=True):
         return 0.0
     err = float(np.abs(got[fg] - want[fw]).max())
     tol = TOL[dtype]
-    if dtype in (torch.float32, torch.float64):
+    if dtype in (torch.float32, torch.float64) or scale_rel:
         tol = tol * max(1.0, float(np.abs(want[fw]).max()))     # relative to the tensor's scale
     assert err <= tol, f"{name}: max abs err {err:.3e} > {tol:.3e} ({dtype})"
     return err
