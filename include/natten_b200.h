@@ -120,6 +120,9 @@ unsigned long long natten_launch_count(void); /* kernels launched by this librar
 /* Synchronises the device and reports whether any kernel of this library gave up
  * on a bounded wait since the library was loaded (NATTEN_OK or NATTEN_E_DEVICE). */
 int natten_device_status(void);
+/* Debug aid: a device buffer of >= 256 int64 that one CTA of each tensor-core kernel
+ * fills with clock64() stamps of its pipeline events (NULL switches it off).           */
+void natten_debug_trace(void* device_buffer);
 
 #ifdef __cplusplus
 }

@@ -23,6 +23,7 @@ EXPORTS = (
     "natten_fused_fwd", "natten_fused_bwd", "natten_workspace_bytes", "natten_qk_fwd",
     "natten_qk_bwd", "natten_av_fwd", "natten_av_bwd", "natten_strerror",
     "natten_abi_version", "natten_last_path", "natten_launch_count", "natten_device_status",
+    "natten_debug_trace",
 )
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.float64: F64}

@@ -208,6 +208,7 @@ const char* natten_strerror(int code)
 int natten_abi_version(void) { return 1; }
 int natten_last_path(void) { return t_last_path; }
 unsigned long long natten_launch_count(void) { return simt_launch_count() + tc_launch_count(); }
+void natten_debug_trace(void* device_buffer) { tc_set_trace(device_buffer); }
 int natten_device_status(void) { return tc_device_status() == 0 ? NATTEN_OK : NATTEN_E_DEVICE; }
 
 } // extern "C"

@@ -197,6 +197,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const int total = nchunks * n_heads_col;                 // column passes of this CTA
+    // debug clock stamps: CTA (5, 0, 0); key side uses the upper half of the buffer
+    long long* tr = (P.trace && blockIdx.x == 5 && blockIdx.y == 0 && blockIdx.z == 0) ? P.trace + (kKeySide ? 128 : 0) : nullptr;
+    int tn = 0;
+    auto stamp = [&](int base) { if (tr && tn < 60) tr[base + tn++] = clock64(); };
 
     auto chunk_index = [&](int cc, int (&ci)[3], int& head_col) {
         head_col = kKeySide ? hy * P.group + cc / nchunks : hy;
@@ -272,18 +276,23 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 mma_commit(bar_acc);
             };
 
+            stamp(0);
             bool ok = mbar_wait(bar_row, 0, abort_flag);
             ok = ok && mbar_wait(bar_col, 0, abort_flag);
+            stamp(0);
             if (ok) issue_s_dp(0);
+            stamp(0);
             for (int cc = 0; cc < total && ok; ++cc) {
                 ok = mbar_wait(bar_sp, cc & 1, abort_flag);              // S/dP consumed, P/dS stored
                 if (!ok) break;
+                stamp(0);
                 issue_acc(cc);                                           // reads P/dS ...
                 if (cc + 1 < total) {
                     ok = mbar_wait(bar_col + 8 * ((cc + 1) % kStages), ((cc + 1) / kStages) & 1, abort_flag);
                     if (!ok) break;
                     issue_s_dp(cc + 1);                                  // ... before the next S/dP overwrite them
                 }
+                stamp(0);
                 if (cc + kStages < total) {
                     ok = mbar_wait(bar_acc, cc & 1, abort_flag);         // stage cc % kStages is free again
                     if (!ok) break;
@@ -335,22 +344,25 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         bool ok = true;
         constexpr int kPairs = kInner > 0 ? kInner / 2 : 1;
         constexpr int kRows = kInner > 0 ? 32 / kInner : 1;
+        int ci[3] = {0, 0, 0};                   // chunk index per axis, advanced without divisions
+        uint32_t colmask[kPairs];                // separable geometry: 16-bit lane masks per column pair
+        bool cols_any = false;
+        int cached_c2 = -1;
         for (int cc = 0; cc < total; ++cc) {
-            int ci[3], hc;
-            chunk_index(cc, ci, hc);
-
             // ---- validity of this warp's 32 columns for this thread's row ----
             uint32_t word = 0u;                  // generic geometry: one bit per column
-            uint32_t colmask[kPairs];            // separable geometry: 16-bit lane masks per column pair
-            uint32_t rowmask[kRows];             //                      all-ones / zero per inner row
+            uint32_t rowmask[kRows];             // separable geometry: all-ones / zero per inner row
             bool mine = false;
             if (kInner > 0) {
-                const int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
+                if (ci[2] != cached_c2) {        // the column masks only change with the innermost chunk index
+                    cached_c2 = ci[2];
+                    const int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
 #pragma unroll
-                for (int i = 0; i < kPairs; ++i)
-                    colmask[i] = ((2 * i >= lo2 && 2 * i < hi2) ? 0x0000FFFFu : 0u) |
-                                 ((2 * i + 1 >= lo2 && 2 * i + 1 < hi2) ? 0xFFFF0000u : 0u);
-                const bool cols_any = hi2 > 0 && lo2 < kInner && hi2 > lo2;
+                    for (int i = 0; i < kPairs; ++i)
+                        colmask[i] = ((2 * i >= lo2 && 2 * i < hi2) ? 0x0000FFFFu : 0u) |
+                                     ((2 * i + 1 >= lo2 && 2 * i + 1 < hi2) ? 0xFFFF0000u : 0u);
+                    cols_any = hi2 > 0 && lo2 < kInner && hi2 > lo2;
+                }
 #pragma unroll
                 for (int t = 0; t < kRows; ++t) {
                     const int jj = 32 * piece + t * kInner;
@@ -368,9 +380,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             const bool any = __any_sync(0xffffffffu, mine);
             const bool full = kInner == 0 && __all_sync(0xffffffffu, word == 0xffffffffu);
 
+            if (warp == 0 && lane == 0) stamp(64);
             ok = ok && mbar_wait(bar_s, cc & 1, abort_flag);     // also: the previous chunk's P/dS were consumed
             if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (cc % kStages), (cc / kStages) & 1, abort_flag);
             tc_fence_after();
+            if (warp == 0 && lane == 0) stamp(64);
             if (any) {
                 const float* stp = stats + (cc % kStages) * 128 + 32 * piece;
                 const float4* st4 = reinterpret_cast<const float4*>(stp);
@@ -402,15 +416,14 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                                 const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                                 const float g0 = fmaf(__uint_as_float(dp[j]), P.scale, nd[2 * h2]);
                                 const float g1 = fmaf(__uint_as_float(dp[j + 1]), P.scale, nd[2 * h2 + 1]);
-                                uint32_t pp = cvt_pack<BF16>(p0, p1);
                                 uint32_t dd = cvt_pack<BF16>(p0 * g0, p1 * g1);
-                                if (kInner > 0) {
-                                    const uint32_t m = colmask[pi % kPairs] & rowmask[pi / kPairs];
-                                    pp &= m;
-                                    dd &= m;
-                                }
-                                pk_p[pl] = pp;
+                                if (kInner > 0) dd = dd & colmask[pi % kPairs] & rowmask[pi / kPairs];
                                 pk_ds[pl] = dd;
+                                if (kKeySide) {
+                                    uint32_t pp = cvt_pack<BF16>(p0, p1);
+                                    if (kInner > 0) pp = pp & colmask[pi % kPairs] & rowmask[pi / kPairs];
+                                    pk_p[pl] = pp;
+                                }
                             }
                         }
                     } else {
@@ -446,6 +459,15 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(bar_sp);
+            if (warp == 0 && lane == 0) stamp(64);
+            // next chunk (innermost axis fastest; wraps to the next query head on the key side)
+            if (++ci[2] == nc[2]) {
+                ci[2] = 0;
+                if (++ci[1] == nc[1]) {
+                    ci[1] = 0;
+                    if (++ci[0] == nc[0]) ci[0] = 0;
+                }
+            }
         }
 
         // ---- accumulators -> global: this warp owns 32 of the 64 channels ----
@@ -575,6 +597,7 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     Plan plan;
     if (!make_plan(g, plan, kCols)) return -2;
     plan.p.status = status_ptr();
+    plan.p.trace = trace_ptr();
     if (!plan.p.status) return -2;
     if (g.B == 0) return 0;
     if (g.Hq > 65535 || g.B > 65535) return -2;

@@ -25,7 +25,11 @@ using namespace tcplan;
 
 __device__ int g_tc_status = 0;
 
+static long long* g_trace = nullptr;
+void tc_set_trace(void* p) { g_trace = reinterpret_cast<long long*>(p); }
+
 namespace tcplan {
+long long* trace_ptr() { return g_trace; }
 int* status_ptr()
 {
     int* p = nullptr;
@@ -402,6 +406,7 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
         !encode_map(&mv, v, bf16, plan.p, g.Hkv, g.Dv, g.vs, plan.box_kv))
         return -2;
     plan.p.status = status_ptr();
+    plan.p.trace = trace_ptr();
     if (!plan.p.status) return -2;
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= plan.p.dil[a];

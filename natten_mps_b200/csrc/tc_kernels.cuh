@@ -17,5 +17,7 @@ void tc_count_launch();
 unsigned long long tc_launch_count();
 // 0 = clean; 1 = some kernel gave up on a bounded wait (synchronises the device).
 int tc_device_status();
+// Debug: device buffer (>= 256 long long) that one CTA of each tensor-core kernel fills with clock stamps.
+void tc_set_trace(void* device_buffer);
 
 } // namespace natten

@@ -26,6 +26,7 @@ struct TcParams {
     const int* extents;
     long long ltot;
     int* status;
+    long long* trace;      // optional device buffer for clock stamps of one CTA (nullptr = off)
 };
 
 __device__ __forceinline__ float fast_exp2(float x)
@@ -230,6 +231,7 @@ inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, c
 }
 
 int* status_ptr();   // device address of the library's status word (defined in tc_fwd.cu)
+long long* trace_ptr();   // debug clock-stamp buffer set through natten_debug_trace (or nullptr)
 
 
 } // namespace tcplan
