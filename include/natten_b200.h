@@ -39,7 +39,8 @@ enum {
     NATTEN_E_INVALID = -1,      /* malformed params (rank, sizes, null pointers)   */
     NATTEN_E_UNSUPPORTED = -2,  /* legal but outside what the kernels cover        */
     NATTEN_E_WORKSPACE = -3,    /* workspace missing or too small                  */
-    NATTEN_E_DEVICE = -4        /* a kernel reported a bounded-wait timeout        */
+    NATTEN_E_DEVICE = -4,       /* a kernel reported a bounded-wait timeout        */
+    NATTEN_E_TOO_LARGE = -5     /* exceeds the built-in scratch of the *_static entry */
 };
 
 enum {
@@ -95,6 +96,19 @@ int natten_fused_bwd(const natten_params_t* params, const void* q, const void* k
 
 /* Scratch bytes an op needs (0 when none). */
 size_t natten_workspace_bytes(const natten_params_t* params, int op);
+
+/* natten_fused_bwd for callers that cannot allocate device memory (no counterpart in
+ * the reference, which always allocates through PyTorch).  Same arguments without the
+ * workspace: the scratch is a fixed 4 MiB array inside the library, enough for
+ * batch * queries * heads_q <= 1 048 576; larger problems return NATTEN_E_TOO_LARGE.
+ * The first call on each device queries the array's device address (no allocation):
+ * make it before any stream capture.  All calls on a device share the array, so calls
+ * whose kernels can overlap (different streams) race; keep them on one stream.        */
+int natten_fused_bwd_static(const natten_params_t* params, const void* q, const void* k, const void* v,
+                            const void* extra_k, const void* extra_v, const void* out, const void* lse,
+                            const void* dout, const void* dlse, void* dq, void* dk, void* dv,
+                            void* dextra_k, void* dextra_v, void* stream);
+size_t natten_static_scratch_bytes(void);
 
 /* Split QK forward / backward: na{R}d_qk_forward / na{R}d_qk_backward
  * (src/natten_mps/_core/ops.py:98-110, 126-138; oracle _core/pure.py:223-254,

@@ -23,7 +23,7 @@ EXPORTS = (
     "natten_fused_fwd", "natten_fused_bwd", "natten_workspace_bytes", "natten_qk_fwd",
     "natten_qk_bwd", "natten_av_fwd", "natten_av_bwd", "natten_strerror",
     "natten_abi_version", "natten_last_path", "natten_launch_count", "natten_device_status",
-    "natten_debug_trace",
+    "natten_debug_trace", "natten_fused_bwd_static", "natten_static_scratch_bytes",
 )
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.float64: F64}
@@ -63,6 +63,8 @@ def lib():
         pp = ctypes.POINTER(Params)
         L.natten_fused_fwd.argtypes = [pp] + [vp] * 8
         L.natten_fused_bwd.argtypes = [pp] + [vp] * 15 + [ctypes.c_size_t, vp]
+        L.natten_fused_bwd_static.argtypes = [pp] + [vp] * 15
+        L.natten_static_scratch_bytes.restype = ctypes.c_size_t
         L.natten_workspace_bytes.argtypes = [pp, ctypes.c_int]
         L.natten_workspace_bytes.restype = ctypes.c_size_t
         L.natten_qk_fwd.argtypes = [pp] + [vp] * 4

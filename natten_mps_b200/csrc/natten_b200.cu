@@ -200,6 +200,7 @@ const char* natten_strerror(int code)
         case NATTEN_E_UNSUPPORTED: return "unsupported configuration";
         case NATTEN_E_WORKSPACE: return "workspace missing or too small";
         case NATTEN_E_DEVICE: return "device-side wait timed out";
+        case NATTEN_E_TOO_LARGE: return "problem exceeds the built-in scratch of the no-allocation entry point";
     }
     if (code > 0) return cudaGetErrorString((cudaError_t)code);
     return "unknown error";
