@@ -161,6 +161,8 @@ def run_reference(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())
     steps = max(1, min(args.steps, 20))
     cb, sec = cpu_port_run(w, steps, max(1, min(args.warmup, 2)), sample_batch=w["B"])
     line = {
@@ -206,9 +208,39 @@ def run_ours(args, w):
     geo = dict(kernel_size=w["kernel"], stride=w["stride"], dilation=w["dilation"], is_causal=w["causal"],
                scale=w["D"] ** -0.5)
 
+    # The timed step calls the C ABI directly on preallocated buffers (the library never
+    # allocates), so the host does little more than two foreign calls per step.
+    import ctypes
+    L = _cabi.lib()
+    rank_sp = w["rank"]
+    strides = lambda t: _cabi.token_strides(t, rank_sp)
+    params = _cabi.make_params(rank_sp, tdt, B, w["Hq"], w["Hkv"], w["D"], w["D"], w["spatial"], w["kernel"],
+                               w["stride"], w["dilation"], w["causal"], w["D"] ** -0.5, 0,
+                               strides(q), strides(k), strides(v))
+    out_b = torch.empty(shp_q, dtype=tdt, device=dev)
+    lse_b = torch.empty(shp_q[:-1], dtype=torch.float32, device=dev)
+    dq_b, dk_b, dv_b = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ws_bytes = int(L.natten_workspace_bytes(params, _cabi.OP_FUSED_BWD))
+    ws_b = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    fwd_args = (params, P(q), P(k), P(v), None, None, P(out_b), P(lse_b), stream)
+    bwd_args = (params, P(q), P(k), P(v), None, None, P(out_b), P(lse_b), P(go), None, P(dq_b), P(dk_b),
+                P(dv_b), None, None, P(ws_b), ws_b.numel(), stream)
+
+    def fwd_call():
+        rc = L.natten_fused_fwd(*fwd_args)
+        if rc:
+            _cabi.check(rc, "natten_fused_fwd")
+
+    def bwd_call():
+        rc = L.natten_fused_bwd(*bwd_args)
+        if rc:
+            _cabi.check(rc, "natten_fused_bwd")
+
     def step():
-        out, lse = _backend.fused_forward(q, k, v, **geo)
-        return _backend.fused_backward(q, k, v, out, lse, go, **geo)
+        fwd_call()
+        bwd_call()
 
     def sync_all():
         torch.cuda.synchronize()
@@ -245,9 +277,9 @@ def run_ours(args, w):
     fwd_ms, bwd_ms = [], []
     for _ in range(max(5, min(args.steps, 20))):
         fe[0].record()
-        out, lse = _backend.fused_forward(q, k, v, **geo)
+        fwd_call()
         fe[1].record()
-        _backend.fused_backward(q, k, v, out, lse, go, **geo)
+        bwd_call()
         fe[2].record()
         torch.cuda.synchronize()
         fwd_ms.append(fe[0].elapsed_time(fe[1]))

@@ -80,20 +80,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     // query side: blockIdx.y = query head.  key side: blockIdx.y = kv head.
     const int hy = blockIdx.y, b = blockIdx.z;
     const int n_heads_col = kKeySide ? P.group : 1;          // column passes (query heads of the group)
+    const int prior_abort = *reinterpret_cast<volatile int*>(P.status);   // loaded early, used at barrier set-up
 
     // ---- CTA geometry -------------------------------------------------------
-    int gidx = blockIdx.x / P.ntiles, tidx = blockIdx.x % P.ntiles;
     int rg[3], origin[3], Lp[3], boxlo[3], nc[3];
-    bool cta_active = true;
-    auto axis_setup = [&](const int a) {
-        rg[a] = gidx % P.dil[a]; gidx /= P.dil[a];
-        origin[a] = (tidx % P.ntile[a]) * P.tile[a]; tidx /= P.ntile[a];
-        const int ea = a - (3 - P.rank);
-        const int Ls = (P.extents && ea >= 0) ? P.extents[b * P.rank + ea] : P.L[a];
-        Lp[a] = rg[a] < Ls ? (Ls - rg[a] + P.dil[a] - 1) / P.dil[a] : 0;
-        if (origin[a] >= Lp[a]) cta_active = false;
-    };
-    axis_setup(2); axis_setup(1); axis_setup(0);
+    const bool cta_active = cta_geometry(P, blockIdx.x, b, rg, origin, Lp);
     int nchunks = 1;
     if (cta_active) {
 #pragma unroll
@@ -108,23 +99,101 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 boxlo[a] = P.causal[a] ? origin[a] - (P.K[a] - 1) : ws1(origin[a], Lp[a], P.K[a]);
                 hi = P.causal[a] ? last : ws1(last, Lp[a], P.K[a]) + P.K[a] - 1;
             }
-            nc[a] = (hi - boxlo[a] + P.cb[a]) / P.cb[a];
+            nc[a] = chunks_along(P, a, hi - boxlo[a] + 1);
             nchunks *= nc[a];
         }
     }
 
+    const int quad = warp & 3, piece = (warp >> 2) & 1;      // compute warps: TMEM lane quadrant, 32-column piece
+    if (!cta_active) {                       // padding rows get zero gradients
+        if (warp < kComputeWarps) {
+            int ri[3];
+            row_offsets(P, quad * 32 + lane, ri);
+            bool inside = true;
+            long long pflat = 0;
+#pragma unroll
+            for (int a = 0; a < 3; ++a) {
+                const int pa = rg[a] + P.dil[a] * (origin[a] + ri[a]);
+                if (pa >= P.L[a]) inside = false;
+                pflat = pflat * P.L[a] + pa;
+            }
+            if (inside) {
+                const long long orow = ((long long)b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + hy;
+#pragma unroll
+                for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
+                    uint4* o = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + orow * DH + piece * 32);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[i] = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- shared memory, barriers, TMEM --------------------------------------
+    const uint32_t sbase = smem_u32(smem);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kBar + 128);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Smem::kBar + 136);
+    const uint32_t bar_row = sbase + Smem::kBar + 0;
+    const uint32_t bar_col = sbase + Smem::kBar + 8;          // [kStages] C1, C2 landed
+    const uint32_t bar_stats = sbase + Smem::kBar + 40;       // [kStages] column lse / delta staged
+    const uint32_t bar_s = sbase + Smem::kBar + 72;           // S and dP of the chunk are in TMEM
+    const uint32_t bar_sp = sbase + Smem::kBar + 80;          // threads consumed S/dP, wrote P/dS
+    const uint32_t bar_acc = sbase + Smem::kBar + 88;         // accumulating MMAs of the chunk finished
+    float* stats = reinterpret_cast<float*>(smem + Smem::kStats);
+
+    const int total = nchunks * n_heads_col;                 // column passes of this CTA
+    const int head_row = hy;                                  // head coordinate of the row tensors
+    const int head_kv = kKeySide ? hy : hy / P.group;
+    // Column loads are issued in order; counters avoid divisions.
+    int ld[3] = {0, 0, 0}, ld_head = 0, loaded = 0;
+    auto issue_cols = [&]() {
+        int X[3];
+#pragma unroll
+        for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (boxlo[a] + ld[a] * P.cb[a]);
+        const int s = loaded % kStages;
+        const uint32_t bar = bar_col + 8 * s;
+        // query side: columns are keys (kv head); key side: columns are queries (query head)
+        const int hx = (kKeySide ? hy * P.group + ld_head : head_kv) * DH;
+        mbar_expect_tx(bar, 2 * kColTile);
+        tma_load_5d(sbase + Smem::kC1 + s * kColTile, &tmC1, bar, hx, X[2], X[1], X[0], b);
+        tma_load_5d(sbase + Smem::kC2 + s * kColTile, &tmC2, bar, hx, X[2], X[1], X[0], b);
+        ++loaded;
+        if (++ld[2] == nc[2]) { ld[2] = 0; if (++ld[1] == nc[1]) { ld[1] = 0; if (++ld[0] == nc[0]) { ld[0] = 0; ++ld_head; } } }
+    };
+    // The issuing warp sets up the barriers, allocates TMEM and starts the first loads right away,
+    // so they are in flight while the compute warps are still working out their row geometry.
+    if (warp == kComputeWarps) {
+        if (lane == 0) {
+            *abort_flag = ((sbase & 1023u) || prior_abort) ? 1 : 0;
+            mbar_init(bar_row, 1);
+            for (int s = 0; s < kStages; ++s) { mbar_init(bar_col + 8 * s, 1); mbar_init(bar_stats + 8 * s, 32); }
+            mbar_init(bar_s, 1);
+            mbar_init(bar_sp, kComputeWarps * 32);
+            mbar_init(bar_acc, 1);
+            mbar_init_fence();
+            fence_async_smem();
+            if (!*abort_flag) {
+                const int hx = (kKeySide ? head_kv : head_row) * DH;
+                mbar_expect_tx(bar_row, 2 * kTile);
+                tma_load_5d(sbase + Smem::kR1, &tmR1, bar_row, hx, rg[2] + P.dil[2] * origin[2],
+                            rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
+                tma_load_5d(sbase + Smem::kR2, &tmR2, bar_row, hx, rg[2] + P.dil[2] * origin[2],
+                            rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
+                for (int cc = 0; cc < total && cc < kStages; ++cc) issue_cols();
+            }
+        }
+        __syncwarp();
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    }
     // ---- per-thread row ------------------------------------------------------
     int f[3] = {0, 0, 0}, e[3] = {0, 0, 0};
     bool valid_row = false, in_tensor = false;
     long long out_row = 0;
     float row_lse2 = 0.f, row_delta = 0.f;
-    const int quad = warp & 3, piece = warp >> 2;            // compute warps only
     if (warp < kComputeWarps) {
-        int r = quad * 32 + lane;
         int ri[3];
-        ri[2] = r % P.tile[2]; r /= P.tile[2];
-        ri[1] = r % P.tile[1]; r /= P.tile[1];
-        ri[0] = r;
+        row_offsets(P, quad * 32 + lane, ri);
         valid_row = true; in_tensor = true;
         long long pflat = 0;
 #pragma unroll
@@ -155,48 +224,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         }
     }
 
-    if (!cta_active) {                       // padding rows get zero gradients
-        if (warp < kComputeWarps && in_tensor) {
-#pragma unroll
-            for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
-                uint4* o = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * DH + piece * 32);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) o[i] = make_uint4(0, 0, 0, 0);
-            }
-        }
-        return;
-    }
-
-    // ---- shared memory, barriers, TMEM --------------------------------------
-    const uint32_t sbase = smem_u32(smem);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kBar + 128);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Smem::kBar + 136);
-    const uint32_t bar_row = sbase + Smem::kBar + 0;
-    const uint32_t bar_col = sbase + Smem::kBar + 8;          // [kStages] C1, C2 landed
-    const uint32_t bar_stats = sbase + Smem::kBar + 40;       // [kStages] column lse / delta staged
-    const uint32_t bar_s = sbase + Smem::kBar + 72;           // S and dP of the chunk are in TMEM
-    const uint32_t bar_sp = sbase + Smem::kBar + 80;          // threads consumed S/dP, wrote P/dS
-    const uint32_t bar_acc = sbase + Smem::kBar + 88;         // accumulating MMAs of the chunk finished
-    float* stats = reinterpret_cast<float*>(smem + Smem::kStats);
-
-    if (tid == 0) {
-        *abort_flag = ((sbase & 1023u) || *reinterpret_cast<volatile int*>(P.status)) ? 1 : 0;
-        mbar_init(bar_row, 1);
-        for (int s = 0; s < kStages; ++s) { mbar_init(bar_col + 8 * s, 1); mbar_init(bar_stats + 8 * s, 32); }
-        mbar_init(bar_s, 1);
-        mbar_init(bar_sp, kComputeWarps * 32);
-        mbar_init(bar_acc, 1);
-        mbar_init_fence();
-    }
-    if (warp == kComputeWarps) {
-        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-        if (lane == 0) { tma_prefetch_desc(&tmR1); tma_prefetch_desc(&tmR2); tma_prefetch_desc(&tmC1); tma_prefetch_desc(&tmC2); }
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const int total = nchunks * n_heads_col;                 // column passes of this CTA
     // debug clock stamps: CTA (5, 0, 0); key side uses the upper half of the buffer
     long long* tr = (P.trace && blockIdx.x == 5 && blockIdx.y == 0 && blockIdx.z == 0) ? P.trace + (kKeySide ? 128 : 0) : nullptr;
     int tn = 0;
@@ -209,38 +240,12 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         ci[1] = c % nc[1]; c /= nc[1];
         ci[0] = c;
     };
-    const int head_row = hy;                                  // head coordinate of the row tensors
-    const int head_kv = kKeySide ? hy : hy / P.group;
 
     if (warp == kComputeWarps) {
         // =====================================================================
         // TMA + MMA issue (one thread)
         // =====================================================================
         if (lane == 0 && !*abort_flag) {
-            auto issue_cols = [&](int cc) {
-                int ci[3], hc;
-                chunk_index(cc, ci, hc);
-                int X[3];
-#pragma unroll
-                for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (boxlo[a] + ci[a] * P.cb[a]);
-                const int s = cc % kStages;
-                const uint32_t bar = bar_col + 8 * s;
-                // query side: columns are keys (kv head); key side: columns are queries (query head)
-                const int hx = (kKeySide ? hc : head_kv) * DH;
-                mbar_expect_tx(bar, 2 * kColTile);
-                tma_load_5d(sbase + Smem::kC1 + s * kColTile, &tmC1, bar, hx, X[2], X[1], X[0], b);
-                tma_load_5d(sbase + Smem::kC2 + s * kColTile, &tmC2, bar, hx, X[2], X[1], X[0], b);
-            };
-            {
-                const int hx = (kKeySide ? head_kv : head_row) * DH;
-                mbar_expect_tx(bar_row, 2 * kTile);
-                tma_load_5d(sbase + Smem::kR1, &tmR1, bar_row, hx, rg[2] + P.dil[2] * origin[2],
-                            rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
-                tma_load_5d(sbase + Smem::kR2, &tmR2, bar_row, hx, rg[2] + P.dil[2] * origin[2],
-                            rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
-            }
-            for (int cc = 0; cc < total && cc < kStages; ++cc) issue_cols(cc);
-
             constexpr uint32_t idesc_kk = instr_desc(BF16 ? 1 : 0, kCols, 0, 0);    // both operands K-major
             constexpr uint32_t idesc_acc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A from TMEM, B MN-major
             auto issue_s_dp = [&](int cc) {
@@ -296,7 +301,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 if (cc + kStages < total) {
                     ok = mbar_wait(bar_acc, cc & 1, abort_flag);         // stage cc % kStages is free again
                     if (!ok) break;
-                    issue_cols(cc + kStages);
+                    issue_cols();
                 }
             }
         }

@@ -18,6 +18,8 @@
 
 #include "tc_plan.cuh"
 
+#include <type_traits>
+
 namespace natten {
 
 using namespace tc;
@@ -41,7 +43,7 @@ int* status_ptr()
 namespace {
 
 constexpr int kStages = 3;
-constexpr int kThreads = 160;            // 4 softmax warps + 1 TMA/MMA warp
+constexpr int kThreads = 288;            // 8 softmax warps + 1 TMA/MMA warp
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColP = 128, kColO = 192;
 
@@ -54,336 +56,374 @@ struct SmemMap {
     static constexpr int kK = kQ + kTile;
     static constexpr int kV = kK + kStages * kTile;
     static constexpr int kBar = kV + kStages * kTile;
-    // barriers: q, kv_full[3], s_full, sp_ready, o_full  (8 bytes each) + tmem ptr + abort flag
-    static constexpr int kTotal = kBar + 128;
+    // barriers: q, kv_full[3], s_full, sp_ready, o_full  (8 bytes each) + tmem ptr + abort flag,
+    // then 512 bytes for the two column halves to exchange their row maxima
+    static constexpr int kTotal = kBar + 128 + 512;
 };
 
 __device__ __forceinline__ int tc_window_start(int p, int L, int K) { return window_start(p, L, K, 1); }
 
-template <int DH, bool BF16>
-__global__ void __launch_bounds__(kThreads, (DH == 64 ? 2 : 1))
+// kInner: innermost chunk extent when it is 16 or 32 (separable row / column masks),
+// 0 = any geometry (per-column validity words from piece_word).
+template <bool BF16, int kInner>
+__global__ void __launch_bounds__(kThreads, 2)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ TcParams P,
               uint16_t* __restrict__ out, float* __restrict__ lse)
 {
+    constexpr int DH = 64;
     using SM = SmemMap<DH>;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y, b = blockIdx.z, hk = h / P.group;
+    const int quad = warp & 3, team = (warp >> 2) & 1;        // softmax warps: TMEM lane quadrant, column half
+    const long long t_begin = clock64();
+    const int prior_abort = *reinterpret_cast<volatile int*>(P.status);   // loaded early, used at barrier set-up
 
     // ---- CTA geometry -------------------------------------------------------
-    int gidx = blockIdx.x / P.ntiles, tidx = blockIdx.x % P.ntiles;
-    int rg[3], origin[3], Ls[3], Lp[3], lo[3];
-    bool cta_active = true;
-    for (int a = 2; a >= 0; --a) {
-        rg[a] = gidx % P.dil[a]; gidx /= P.dil[a];
-        origin[a] = (tidx % P.ntile[a]) * P.tile[a]; tidx /= P.ntile[a];
-        const int ea = a - (3 - P.rank);
-        Ls[a] = (P.extents && ea >= 0) ? P.extents[b * P.rank + ea] : P.L[a];
-        Lp[a] = rg[a] < Ls[a] ? (Ls[a] - rg[a] + P.dil[a] - 1) / P.dil[a] : 0;
-        if (origin[a] >= Lp[a]) cta_active = false;
-        lo[a] = P.causal[a] ? origin[a] - (P.K[a] - 1) : tc_window_start(origin[a], Lp[a] > 0 ? Lp[a] : 1, P.K[a]);
-    }
-
-    // ---- per-thread query row (softmax warps) -------------------------------
-    int f[3] = {0, 0, 0}, e[3] = {0, 0, 0};
-    bool valid_q = false, in_tensor = false;
-    long long out_row = 0;
-    if (warp < 4) {
-        int r = tid, pflat_ok = 1;
-        int qi[3], pa[3];
-        qi[2] = r % P.tile[2]; r /= P.tile[2];
-        qi[1] = r % P.tile[1]; r /= P.tile[1];
-        qi[0] = r;
-        valid_q = true; in_tensor = true;
-        long long pflat = 0;
+    int rg[3], origin[3], Lp[3], lo[3], nc[3];
+    const bool cta_active = cta_geometry(P, blockIdx.x, b, rg, origin, Lp);
+    int nch = 1;
+    if (cta_active) {
+#pragma unroll
         for (int a = 0; a < 3; ++a) {
-            const int qa = origin[a] + qi[a];
-            pa[a] = rg[a] + P.dil[a] * qa;
-            if (qa >= Lp[a]) valid_q = false;
-            if (pa[a] >= P.L[a]) in_tensor = false;
-            pflat = pflat * P.L[a] + pa[a];
-            if (cta_active) {
-                const int first = P.causal[a] ? qa - (P.K[a] - 1) : tc_window_start(qa, Lp[a], P.K[a]);
-                const int fa = first > 0 ? first : 0;
-                const int la = first + P.K[a] < Lp[a] ? first + P.K[a] : Lp[a];
-                f[a] = fa - lo[a];
-                e[a] = la - lo[a];
-            }
+            const int last = origin[a] + P.tile[a] - 1 < Lp[a] - 1 ? origin[a] + P.tile[a] - 1 : Lp[a] - 1;
+            lo[a] = P.causal[a] ? origin[a] - (P.K[a] - 1) : tc_window_start(origin[a], Lp[a], P.K[a]);
+            const int hi = P.causal[a] ? last : tc_window_start(last, Lp[a], P.K[a]) + P.K[a] - 1;
+            nc[a] = chunks_along(P, a, hi - lo[a] + 1);       // chunks this tile really needs
+            nch *= nc[a];
         }
-        (void)pflat_ok;
-        if (!valid_q) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
-        out_row = (((long long)b * P.ltot + pflat) * P.Hq + h);
     }
 
     if (!cta_active) {                       // nothing to attend: padding rows are zero
-        if (warp < 4 && in_tensor) {
-            uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH);
+        if (warp < 8) {
+            int qi[3];
+            row_offsets(P, quad * 32 + lane, qi);
+            bool inside = true;
+            long long pflat = 0;
 #pragma unroll
-            for (int i = 0; i < DH / 8; ++i) o4[i] = make_uint4(0, 0, 0, 0);
-            lse[out_row] = 0.f;
+            for (int a = 0; a < 3; ++a) {
+                const int pa = rg[a] + P.dil[a] * (origin[a] + qi[a]);
+                if (pa >= P.L[a]) inside = false;
+                pflat = pflat * P.L[a] + pa;
+            }
+            if (inside) {
+                const long long orow = ((long long)b * P.ltot + pflat) * P.Hq + h;
+                uint4* o4 = reinterpret_cast<uint4*>(out + orow * DH + team * 32);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o4[i] = make_uint4(0, 0, 0, 0);
+                if (team == 0) lse[orow] = 0.f;
+            }
         }
         return;
     }
 
     // ---- shared memory, barriers, TMEM --------------------------------------
+    const long long t_geom = clock64();
     const uint32_t sbase = smem_u32(smem);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::kBar + 64);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::kBar + 72);
+    uint16_t* xmax = reinterpret_cast<uint16_t*>(smem + SM::kBar + 128);      // [2][128] partial row maxima (bf16 bits)
     const uint32_t bar_q = sbase + SM::kBar + 0;
     const uint32_t bar_kv = sbase + SM::kBar + 8;       // [3]
     const uint32_t bar_s = sbase + SM::kBar + 32;
     const uint32_t bar_sp = sbase + SM::kBar + 40;
     const uint32_t bar_o = sbase + SM::kBar + 48;
 
-    if (tid == 0) {
-        // swizzled tiles need a 1024-byte aligned base; once any CTA has given up, the rest bail out
-        *abort_flag = ((sbase & 1023u) || *reinterpret_cast<volatile int*>(P.status)) ? 1 : 0;
-        mbar_init(bar_q, 1);
-        for (int s = 0; s < kStages; ++s) mbar_init(bar_kv + 8 * s, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_sp, 128);
-        mbar_init(bar_o, 1);
-        mbar_init_fence();
-    }
-    if (warp == 4) {
+    // The issuing warp sets up the barriers, allocates TMEM and starts the first loads right away,
+    // so they are in flight while the softmax warps are still working out their row geometry.
+    int ld[3] = {0, 0, 0};                       // chunk counters of the next load
+    int loaded = 0;
+    auto issue_kv = [&]() {
+        int X[3];
+#pragma unroll
+        for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (lo[a] + ld[a] * P.cb[a]);
+        const int s = loaded % kStages;
+        const uint32_t bar = bar_kv + 8 * s;
+        mbar_expect_tx(bar, 2 * SM::kTile);
+        tma_load_5d(sbase + SM::kK + s * SM::kTile, &tmK, bar, hk * DH, X[2], X[1], X[0], b);
+        tma_load_5d(sbase + SM::kV + s * SM::kTile, &tmV, bar, hk * DH, X[2], X[1], X[0], b);
+        ++loaded;
+        if (++ld[2] == nc[2]) { ld[2] = 0; if (++ld[1] == nc[1]) { ld[1] = 0; ++ld[0]; } }
+    };
+    long long tw0 = 0, tw1 = 0, tw2 = 0, tw3 = 0;
+    if (warp == 8) {
+        tw0 = clock64();
+        if (lane == 0) {
+            // swizzled tiles need a 1024-byte aligned base; once any CTA has given up, the rest bail out
+            *abort_flag = ((sbase & 1023u) || prior_abort) ? 1 : 0;
+            mbar_init(bar_q, 1);
+            for (int s = 0; s < kStages; ++s) mbar_init(bar_kv + 8 * s, 1);
+            mbar_init(bar_s, 1);
+            mbar_init(bar_sp, 256);
+            mbar_init(bar_o, 1);
+            mbar_init_fence();
+            fence_async_smem();
+            tw1 = clock64();
+            if (!*abort_flag) {
+                mbar_expect_tx(bar_q, SM::kTile);
+                tma_load_5d(sbase + SM::kQ, &tmQ, bar_q, h * DH, rg[2] + P.dil[2] * origin[2],
+                            rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
+                for (int c = 0; c < nch && c < kStages; ++c) issue_kv();
+            }
+        }
+        tw2 = clock64();
+        __syncwarp();
         tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-        if (lane == 0) { tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); }
+        tw3 = clock64();
     }
+    const long long t_init = clock64();
+    // ---- per-thread query row (softmax warps) -------------------------------
+    int f[3] = {0, 0, 0}, e[3] = {0, 0, 0};
+    bool valid_q = false, in_tensor = false;
+    long long out_row = 0;
+    if (warp < 8) {
+        int qi[3];
+        row_offsets(P, quad * 32 + lane, qi);
+        valid_q = true; in_tensor = true;
+        long long pflat = 0;
+#pragma unroll
+        for (int a = 0; a < 3; ++a) {
+            const int qa = origin[a] + qi[a];
+            const int pa = rg[a] + P.dil[a] * qa;
+            if (qa >= Lp[a]) valid_q = false;
+            if (pa >= P.L[a]) in_tensor = false;
+            pflat = pflat * P.L[a] + pa;
+            if (cta_active) {
+                const int first = P.causal[a] ? qa - (P.K[a] - 1) : tc_window_start(qa, Lp[a], P.K[a]);
+                f[a] = (first > 0 ? first : 0) - lo[a];
+                e[a] = (first + P.K[a] < Lp[a] ? first + P.K[a] : Lp[a]) - lo[a];
+            }
+        }
+        if (!valid_q) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
+        out_row = (((long long)b * P.ltot + pflat) * P.Hq + h);
+    }
+
+    const long long t_alloc = clock64();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    const long long t_sync = clock64();
     const uint32_t tmem = *tmem_slot;
-    const int nch = P.nchunks;
+    // debug clock stamps of CTA (5, 0, 0): forward uses entries [256, 384)
+    long long* tr = (P.trace && blockIdx.x == 5 && blockIdx.y == 0 && blockIdx.z == 0) ? P.trace + 256 : nullptr;
+    int tn = 0;
+    auto stamp = [&](int base) { if (tr && tn < 60) tr[base + tn++] = clock64(); };
 
-    if (warp == 4) {
+    if (warp == 8) {
         // =====================================================================
         // TMA + MMA issue (one thread)
         // =====================================================================
         if (lane == 0 && !*abort_flag) {
-            auto issue_kv = [&](int c) {
-                int cc = c, ci[3];
-                ci[2] = cc % P.nchunk[2]; cc /= P.nchunk[2];
-                ci[1] = cc % P.nchunk[1]; cc /= P.nchunk[1];
-                ci[0] = cc;
-                int X[3];
-                for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (lo[a] + ci[a] * P.cb[a]);
-                const int s = c % kStages;
-                const uint32_t bar = bar_kv + 8 * s;
-                mbar_expect_tx(bar, 2 * SM::kTile);
-                for (int hf = 0; hf < SM::kHalves; ++hf) {
-                    tma_load_5d(sbase + SM::kK + s * SM::kTile + hf * (kChunk * 128), &tmK, bar,
-                                hk * DH + 64 * hf, X[2], X[1], X[0], b);
-                    tma_load_5d(sbase + SM::kV + s * SM::kTile + hf * (kChunk * 128), &tmV, bar,
-                                hk * DH + 64 * hf, X[2], X[1], X[0], b);
-                }
-            };
-            mbar_expect_tx(bar_q, SM::kTile);
-            for (int hf = 0; hf < SM::kHalves; ++hf)
-                tma_load_5d(sbase + SM::kQ + hf * (kTileRows * 128), &tmQ, bar_q, h * DH + 64 * hf,
-                            rg[2] + P.dil[2] * origin[2], rg[1] + P.dil[1] * origin[1],
-                            rg[0] + P.dil[0] * origin[0], b);
-            for (int c = 0; c < nch && c < kStages; ++c) issue_kv(c);
-
             constexpr uint32_t idesc_qk = instr_desc(BF16 ? 1 : 0, kChunk, 0, 0);
             constexpr uint32_t idesc_pv = instr_desc(BF16 ? 1 : 0, DH, 0, 1);
+            const uint64_t dq0 = smem_desc(sbase + SM::kQ, 16, 1024);
             auto issue_qk = [&](int c) {
-                const int s = c % kStages;
+                const uint64_t dk0 = smem_desc(sbase + SM::kK + (c % kStages) * SM::kTile, 16, 1024);
                 tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < DH / 16; ++ks) {
-                    const uint32_t off = (ks / 4) * (kTileRows * 128) + (ks % 4) * 32;
-                    mma_ss(tmem + kColS, smem_desc(sbase + SM::kQ + off, 16, 1024),
-                           smem_desc(sbase + SM::kK + s * SM::kTile + off, 16, 1024), idesc_qk, ks > 0);
-                }
+                for (int ks = 0; ks < DH / 16; ++ks)
+                    mma_ss(tmem + kColS, dq0 + 2 * ks, dk0 + 2 * ks, idesc_qk, ks > 0);
                 mma_commit(bar_s);
             };
             auto issue_pv = [&](int c) {
-                const int s = c % kStages;
+                const uint64_t dv0 = smem_desc(sbase + SM::kV + (c % kStages) * SM::kTile, SM::kTile, 1024);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kChunk / 16; ++ks)
-                    mma_ts(tmem + kColO, tmem + kColP + 8 * ks,
-                           smem_desc(sbase + SM::kV + s * SM::kTile + ks * 2048, kChunk * 128, 1024),
-                           idesc_pv, ks > 0);
+                    mma_ts(tmem + kColO, tmem + kColP + 8 * ks, dv0 + 128 * ks, idesc_pv, ks > 0);
                 mma_commit(bar_o);
             };
 
+            stamp(0);
             bool ok = mbar_wait(bar_q, 0, abort_flag);
+            ok = ok && mbar_wait(bar_kv, 0, abort_flag);
+            stamp(0);
+            if (ok) issue_qk(0);
+            stamp(0);
             for (int c = 0; c < nch && ok; ++c) {
-                if (c == 0) {
-                    ok = mbar_wait(bar_kv, 0, abort_flag);
-                    if (ok) issue_qk(0);
-                }
-                ok = ok && mbar_wait(bar_sp, c & 1, abort_flag);     // S(c) consumed, P(c) stored
+                ok = mbar_wait(bar_sp, c & 1, abort_flag);           // S(c) consumed, P(c) stored
                 if (!ok) break;
-                issue_pv(c);
-                if (c + 1 < nch) {
+                stamp(0);
+                if (c + 1 < nch) {                                   // next scores first: the threads wait for them
                     ok = mbar_wait(bar_kv + 8 * ((c + 1) % kStages), ((c + 1) / kStages) & 1, abort_flag);
                     if (!ok) break;
                     issue_qk(c + 1);
                 }
+                issue_pv(c);
+                stamp(0);
                 if (c + kStages < nch) {
                     ok = mbar_wait(bar_o, c & 1, abort_flag);        // stage c % kStages is free again
                     if (!ok) break;
-                    issue_kv(c + kStages);
+                    issue_kv();
                 }
             }
         }
     } else {
         // =====================================================================
-        // softmax warps: thread = query row
+        // softmax warps: thread = (query row, 64-column half of the chunk, 32 output channels)
         // =====================================================================
-        const uint32_t trow = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        const uint32_t trow = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+        const int row = quad * 32 + lane;
         float m = -INFINITY, l = 0.f;
-        float acc[DH];
+        float acc[32];
 #pragma unroll
-        for (int i = 0; i < DH; ++i) acc[i] = 0.f;
-        const int seg = P.cb[2] < 32 ? P.cb[2] : 32;
-        const int nseg = 32 / seg;
+        for (int i = 0; i < 32; ++i) acc[i] = 0.f;
         bool ok = true;
+        int ci[3] = {0, 0, 0};
+        uint32_t colbits = 0u;                   // separable geometry: valid columns of one inner row
+        int cached_c2 = -1;
 
         for (int c = 0; c < nch; ++c) {
-            // ---- validity words of this chunk (bit j of word pc <-> column 32*pc + j) ----
-            int cc = c, ci[3];
-            ci[2] = cc % P.nchunk[2]; cc /= P.nchunk[2];
-            ci[1] = cc % P.nchunk[1]; cc /= P.nchunk[1];
-            ci[0] = cc;
-            uint32_t words[4];
-#pragma unroll
-            for (int pc = 0; pc < 4; ++pc) {
-                uint32_t w = 0;
-                for (int sg = 0; sg < nseg; ++sg) {
-                    const int jj = 32 * pc + sg * seg;
-                    const int j2 = jj & (P.cb[2] - 1);
-                    const int j1 = (jj >> P.cb2_log) & (P.cb[1] - 1);
-                    const int j0 = jj >> (P.cb2_log + P.cb1_log);
-                    const int i0 = ci[0] * P.cb[0] + j0, i1 = ci[1] * P.cb[1] + j1;
-                    const int base2 = ci[2] * P.cb[2] + j2;
-                    int lo2 = f[2] - base2, hi2 = e[2] - base2;
+            // ---- validity words of this thread's two 32-column pieces ----
+            uint32_t words[2];
+            if (kInner > 0) {
+                if (ci[2] != cached_c2) {
+                    cached_c2 = ci[2];
+                    int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
                     lo2 = lo2 > 0 ? lo2 : 0;
-                    hi2 = hi2 < seg ? hi2 : seg;
-                    if (i0 >= f[0] && i0 < e[0] && i1 >= f[1] && i1 < e[1] && hi2 > lo2) {
-                        const uint32_t run = (hi2 - lo2 >= 32) ? 0xffffffffu : ((1u << (hi2 - lo2)) - 1u);
-                        w |= (run << lo2) << (sg * seg);
-                    }
+                    hi2 = hi2 < kInner ? hi2 : kInner;
+                    colbits = hi2 > lo2 ? (((hi2 - lo2 >= 32) ? 0xffffffffu : ((1u << (hi2 - lo2)) - 1u)) << lo2) : 0u;
                 }
-                words[pc] = w;
+#pragma unroll
+                for (int pc = 0; pc < 2; ++pc) {
+                    uint32_t w = 0u;
+#pragma unroll
+                    for (int t = 0; t < 32 / kInner; ++t) {
+                        const int jj = 64 * team + 32 * pc + t * kInner;
+                        const int j1 = (jj >> P.cb2_log) & (P.cb[1] - 1);
+                        const int j0 = jj >> (P.cb2_log + P.cb1_log);
+                        const int i0 = ci[0] * P.cb[0] + j0, i1 = ci[1] * P.cb[1] + j1;
+                        if (i0 >= f[0] && i0 < e[0] && i1 >= f[1] && i1 < e[1]) w |= colbits << (t * kInner);
+                    }
+                    words[pc] = w;
+                }
+            } else {
+#pragma unroll
+                for (int pc = 0; pc < 2; ++pc) words[pc] = piece_word(P, ci, 2 * team + pc, f, e);
             }
 
+            if (warp == 0 && lane == 0) stamp(64);
             ok = ok && mbar_wait(bar_s, c & 1, abort_flag);
             tc_fence_after();
+            if (warp == 0 && lane == 0) stamp(64);
 
-            // ---- pass 1: row maximum over the valid columns ----
+            // ---- pass 1: maximum over the valid columns of this half, then agree with the other half ----
             float mc = -INFINITY;
 #pragma unroll
-            for (int pc = 0; pc < 4; ++pc) {
+            for (int pc = 0; pc < 2; ++pc) {
                 if (!__any_sync(0xffffffffu, words[pc] != 0u)) continue;
                 uint32_t s[32];
-                tmem_ld32(trow + kColS + 32 * pc, s);
+                tmem_ld32(trow + kColS + 64 * team + 32 * pc, s);
                 tmem_ld_wait();
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    mc = fmaxf(mc, ((words[pc] >> i) & 1u) ? __uint_as_float(s[i]) : -INFINITY);
+                for (int i = 0; i < 32; i += 4) {
+                    m0 = fmaxf(m0, ((words[pc] >> i) & 1u) ? __uint_as_float(s[i]) : -INFINITY);
+                    m1 = fmaxf(m1, ((words[pc] >> (i + 1)) & 1u) ? __uint_as_float(s[i + 1]) : -INFINITY);
+                    m2 = fmaxf(m2, ((words[pc] >> (i + 2)) & 1u) ? __uint_as_float(s[i + 2]) : -INFINITY);
+                    m3 = fmaxf(m3, ((words[pc] >> (i + 3)) & 1u) ? __uint_as_float(s[i + 3]) : -INFINITY);
+                }
+                mc = fmaxf(mc, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
             }
             if (!ok) mc = -INFINITY;
+            {
+                // Both halves must use one maximum.  Each publishes its own rounded up to bf16
+                // (any value >= the true maximum works as the stabiliser) and takes the larger.
+                uint32_t bits = __float_as_uint(mc);
+                bits = (mc >= 0.f) ? ((bits + 0xFFFFu) & 0xFFFF0000u) : (bits & 0xFFFF0000u);
+                xmax[team * 128 + row] = static_cast<uint16_t>(bits >> 16);
+                asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+                const uint32_t other = static_cast<uint32_t>(xmax[(1 - team) * 128 + row]) << 16;
+                mc = fmaxf(__uint_as_float(bits), __uint_as_float(other));
+            }
+            if (warp == 0 && lane == 0) stamp(64);
             const float m_new = fmaxf(m, mc);
             const float alpha = (m == -INFINITY) ? 0.f : fast_exp2((m - m_new) * P.scale_log2);
             const float mb = (m_new == -INFINITY) ? 0.f : m_new * P.scale_log2;
 
-            // ---- fold the previous chunk's P V into the accumulators ----
+            // ---- fold the previous chunk's P V (this team's 32 channels) ----
             if (c > 0) {
                 ok = ok && mbar_wait(bar_o, (c - 1) & 1, abort_flag);
                 tc_fence_after();
+                uint32_t o[32];
+                tmem_ld32(trow + kColO + 32 * team, o);
+                tmem_ld_wait();
 #pragma unroll
-                for (int part = 0; part < DH / 32; ++part) {
-                    uint32_t o[32];
-                    tmem_ld32(trow + kColO + 32 * part, o);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        acc[32 * part + i] = (acc[32 * part + i] + __uint_as_float(o[i])) * alpha;
-                }
+                for (int i = 0; i < 32; ++i) acc[i] = (acc[i] + __uint_as_float(o[i])) * alpha;
             }
 
-            // ---- pass 2: probabilities -> TMEM (16-bit pairs), row sum ----
-            float rowsum = 0.f;
+            if (warp == 0 && lane == 0) stamp(64);
+            // ---- pass 2: probabilities -> TMEM (16-bit pairs), row sum of this half ----
+            float r0 = 0.f, r1 = 0.f;
 #pragma unroll
-            for (int pc = 0; pc < 4; ++pc) {
+            for (int pc = 0; pc < 2; ++pc) {
                 uint32_t packed[16];
                 if (__any_sync(0xffffffffu, words[pc] != 0u)) {
                     uint32_t s[32];
-                    tmem_ld32(trow + kColS + 32 * pc, s);
+                    tmem_ld32(trow + kColS + 64 * team + 32 * pc, s);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float p0 = ((words[pc] >> (2 * i)) & 1u)
-                                             ? fast_exp2(__uint_as_float(s[2 * i]) * P.scale_log2 - mb) : 0.f;
-                        const float p1 = ((words[pc] >> (2 * i + 1)) & 1u)
-                                             ? fast_exp2(__uint_as_float(s[2 * i + 1]) * P.scale_log2 - mb) : 0.f;
-                        rowsum += p0 + p1;
-                        if (BF16) {
-                            __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-                            packed[i] = *reinterpret_cast<uint32_t*>(&t);
-                        } else {
-                            __half2 t = __floats2half2_rn(p0, p1);
-                            packed[i] = *reinterpret_cast<uint32_t*>(&t);
-                        }
+                        const float x0 = ((words[pc] >> (2 * i)) & 1u) ? fmaf(__uint_as_float(s[2 * i]), P.scale_log2, -mb) : -INFINITY;
+                        const float x1 = ((words[pc] >> (2 * i + 1)) & 1u) ? fmaf(__uint_as_float(s[2 * i + 1]), P.scale_log2, -mb) : -INFINITY;
+                        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                        r0 += p0;
+                        r1 += p1;
+                        packed[i] = cvt_pack<BF16>(p0, p1);
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) packed[i] = 0u;
                 }
-                tmem_st16(trow + kColP + 16 * pc, packed);
+                tmem_st16(trow + kColP + 32 * team + 16 * pc, packed);
             }
-            if (!ok) rowsum = 0.f;
-            l = l * alpha + rowsum;
+            l = l * alpha + (ok ? r0 + r1 : 0.f);
             m = m_new;
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(bar_sp);
+            if (warp == 0 && lane == 0) stamp(64);
+            if (++ci[2] == nc[2]) { ci[2] = 0; if (++ci[1] == nc[1]) { ci[1] = 0; ++ci[0]; } }
         }
 
-        // ---- last chunk's P V, normalise, write out ----
+        // ---- last chunk's P V, combine the two halves' sums, normalise, write out ----
         ok = ok && mbar_wait(bar_o, (nch - 1) & 1, abort_flag);
         tc_fence_after();
-#pragma unroll
-        for (int part = 0; part < DH / 32; ++part) {
+        {
             uint32_t o[32];
-            tmem_ld32(trow + kColO + 32 * part, o);
+            tmem_ld32(trow + kColO + 32 * team, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[32 * part + i] += __uint_as_float(o[i]);
+            for (int i = 0; i < 32; ++i) acc[i] += __uint_as_float(o[i]);
         }
+        // every MMA has finished, so the first K stage can carry the partial row sums
+        float* xsum = reinterpret_cast<float*>(smem + SM::kK);
+        xsum[team * 128 + row] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+        l += xsum[(1 - team) * 128 + row];
         if (in_tensor) {
             const bool live = valid_q && l > 0.f && ok;
             const float inv = live ? 1.f / l : 0.f;
-            uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH);
+            uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH + team * 32);
 #pragma unroll
-            for (int i = 0; i < DH / 8; ++i) {
+            for (int i = 0; i < 4; ++i) {
                 uint32_t w[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float a0 = live ? acc[8 * i + 2 * j] * inv : 0.f;
-                    const float a1 = live ? acc[8 * i + 2 * j + 1] * inv : 0.f;
-                    if (BF16) {
-                        __nv_bfloat162 t = __floats2bfloat162_rn(a0, a1);
-                        w[j] = *reinterpret_cast<uint32_t*>(&t);
-                    } else {
-                        __half2 t = __floats2half2_rn(a0, a1);
-                        w[j] = *reinterpret_cast<uint32_t*>(&t);
-                    }
-                }
+                for (int j = 0; j < 4; ++j)
+                    w[j] = live ? cvt_pack<BF16>(acc[8 * i + 2 * j] * inv, acc[8 * i + 2 * j + 1] * inv) : 0u;
                 o4[i] = make_uint4(w[0], w[1], w[2], w[3]);
             }
             // natural-log lse of scale * logits
-            lse[out_row] = live ? (m * P.scale_log2 + log2f(l)) * 0.6931471805599453f : 0.f;
+            if (team == 0) lse[out_row] = live ? (m * P.scale_log2 + log2f(l)) * 0.6931471805599453f : 0.f;
         }
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (tr && tid == 0) { tr[120] = t_begin; tr[121] = clock64(); tr[122] = t_geom; tr[123] = t_init; tr[125] = t_sync; }
+    if (tr && tid == 256) { tr[124] = t_alloc; tr[110] = tw0; tr[111] = tw1; tr[112] = tw2; tr[113] = tw3; }
+    if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
         if (lane == 0 && *abort_flag) atomicExch(P.status, 1);
@@ -415,15 +455,23 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     if (g.Hq > 65535 || g.B > 65535) return -2;
     using SM = SmemMap<64>;
     cudaError_t err;
-    if (bf16) {
+    auto launch = [&](auto bf, auto inner) {
+        constexpr bool kBf = decltype(bf)::value;
+        constexpr int kInner = decltype(inner)::value;
         static bool once = false;
-        if (!once) { cudaFuncSetAttribute(tc_fwd_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal); once = true; }
-        tc_fwd_kernel<64, true><<<grid, kThreads, SM::kTotal, s>>>(mq, mk, mv, plan.p, (uint16_t*)out, (float*)lse);
-    } else {
-        static bool once = false;
-        if (!once) { cudaFuncSetAttribute(tc_fwd_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal); once = true; }
-        tc_fwd_kernel<64, false><<<grid, kThreads, SM::kTotal, s>>>(mq, mk, mv, plan.p, (uint16_t*)out, (float*)lse);
-    }
+        if (!once) {
+            cudaFuncSetAttribute(tc_fwd_kernel<kBf, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
+            once = true;
+        }
+        tc_fwd_kernel<kBf, kInner><<<grid, kThreads, SM::kTotal, s>>>(mq, mk, mv, plan.p, (uint16_t*)out, (float*)lse);
+    };
+    auto by_inner = [&](auto bf) {
+        if (plan.p.cb[2] == 16) launch(bf, std::integral_constant<int, 16>{});
+        else if (plan.p.cb[2] == 32) launch(bf, std::integral_constant<int, 32>{});
+        else launch(bf, std::integral_constant<int, 0>{});
+    };
+    if (bf16) by_inner(std::true_type{});
+    else by_inner(std::false_type{});
     err = cudaGetLastError();
     tc_count_launch();
     return err == cudaSuccess ? 0 : (int)err;

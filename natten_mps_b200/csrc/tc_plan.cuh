@@ -20,7 +20,9 @@ constexpr int kChunk = 128;              // columns per chunk (MMA N of S, K of 
 struct TcParams {
     int L[3], K[3], dil[3], causal[3];
     int tile[3], cb[3], nchunk[3], ntile[3];
-    int cb1_log, cb2_log;
+    int cb0_log, cb1_log, cb2_log;
+    int tile1_log, tile2_log;            // tile extents are powers of two
+    unsigned ntile_mul[3], dil_mul[3];   // ceil(2^32 / d) for d >= 2, 0 for d == 1 (see fast_div)
     int rank, B, Hq, Hkv, group, ntiles, nchunks;
     float scale_log2, scale;
     const int* extents;
@@ -28,6 +30,50 @@ struct TcParams {
     int* status;
     long long* trace;      // optional device buffer for clock stamps of one CTA (nullptr = off)
 };
+
+// n / d with a precomputed multiplier; exact while n * d < 2^32 (checked on the host).
+__device__ __forceinline__ unsigned fast_div(unsigned n, unsigned mul) { return mul ? __umulhi(n, mul) : n; }
+
+// Block index -> dilation residues rg, tile origin, sub-grid extents Lp (innermost axis fastest,
+// dilation group slowest); returns whether the tile holds any row of this sample.
+__device__ __forceinline__ bool cta_geometry(const TcParams& P, unsigned bx, int b, int (&rg)[3],
+                                             int (&origin)[3], int (&Lp)[3])
+{
+    unsigned x = bx;
+#pragma unroll
+    for (int a = 2; a >= 0; --a) {
+        const unsigned q = fast_div(x, P.ntile_mul[a]);
+        origin[a] = static_cast<int>(x - q * P.ntile[a]) * P.tile[a];
+        x = q;
+    }
+    bool active = true;
+#pragma unroll
+    for (int a = 2; a >= 0; --a) {
+        const unsigned q = fast_div(x, P.dil_mul[a]);
+        rg[a] = static_cast<int>(x - q * P.dil[a]);
+        x = q;
+        const int ea = a - (3 - P.rank);
+        const int Ls = (P.extents && ea >= 0) ? P.extents[b * P.rank + ea] : P.L[a];
+        Lp[a] = rg[a] < Ls ? static_cast<int>(fast_div(Ls - rg[a] + P.dil[a] - 1, P.dil_mul[a])) : 0;
+        if (origin[a] >= Lp[a]) active = false;
+    }
+    return active;
+}
+
+// Chunks needed to cover `extent` columns along axis a (chunk extents are powers of two).
+__device__ __forceinline__ int chunks_along(const TcParams& P, int a, int extent)
+{
+    const int lg = a == 0 ? P.cb0_log : (a == 1 ? P.cb1_log : P.cb2_log);
+    return (extent + P.cb[a] - 1) >> lg;
+}
+
+// Row r (0..127) of the tile -> offsets along the three axes.
+__device__ __forceinline__ void row_offsets(const TcParams& P, int r, int (&ri)[3])
+{
+    ri[2] = r & (P.tile[2] - 1);
+    ri[1] = (r >> P.tile2_log) & (P.tile[1] - 1);
+    ri[0] = r >> (P.tile2_log + P.tile1_log);
+}
 
 __device__ __forceinline__ float fast_exp2(float x)
 {
@@ -170,16 +216,25 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk)
             }
         }
     if (best < 0) return false;
-    p.cb1_log = ilog2(p.cb[1]); p.cb2_log = ilog2(p.cb[2]);
+    p.cb0_log = ilog2(p.cb[0]); p.cb1_log = ilog2(p.cb[1]); p.cb2_log = ilog2(p.cb[2]);
+    p.tile1_log = ilog2(p.tile[1]); p.tile2_log = ilog2(p.tile[2]);
     p.nchunks = (int)best;
     p.ntiles = 1;
     for (int a = 0; a < 3; ++a) {
         const int lp = (p.L[a] + p.dil[a] - 1) / p.dil[a];
         p.ntile[a] = (lp + p.tile[a] - 1) / p.tile[a];
         p.ntiles *= p.ntile[a];
+        p.ntile_mul[a] = p.ntile[a] >= 2 ? (unsigned)((0x100000000ull + p.ntile[a] - 1) / p.ntile[a]) : 0u;
+        p.dil_mul[a] = p.dil[a] >= 2 ? (unsigned)((0x100000000ull + p.dil[a] - 1) / p.dil[a]) : 0u;
         plan.box_q[a] = p.tile[a] * p.dil[a];
         plan.box_kv[a] = p.cb[a] * p.dil[a];
         if (plan.box_q[a] > 256) return false;
+    }
+    {
+        long long blocks = p.ntiles;
+        int dmax = 1;
+        for (int a = 0; a < 3; ++a) { blocks *= p.dil[a]; dmax = p.dil[a] > dmax ? p.dil[a] : dmax; dmax = p.ntile[a] > dmax ? p.ntile[a] : dmax; }
+        if (blocks * dmax >= (1ll << 32) || (long long)(p.L[0] + p.L[1] + p.L[2] + dmax) * dmax >= (1ll << 32)) return false;
     }
     p.rank = g.rank; p.B = g.B; p.Hq = g.Hq; p.Hkv = g.Hkv; p.group = g.group;
     p.scale_log2 = (float)(g.scale * 1.4426950408889634);
