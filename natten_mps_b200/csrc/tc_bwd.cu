@@ -36,12 +36,15 @@ constexpr int kCols = 64;                   // columns per chunk
 constexpr int kStages = 4;
 constexpr int kComputeWarps = 8;
 constexpr int kThreads = (kComputeWarps + 2) * 32;
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColDP = 64, kColA1 = 128, kColA2 = 192;
-constexpr int kTile = kTileRows * 128;      // bytes of one [128 x 64] 16-bit row tile
-constexpr int kColTile = kCols * 128;       // bytes of one [64 x 64] 16-bit column tile
+constexpr uint32_t kColS = 0, kColDP = 64, kColA1 = 128;   // acc2 follows acc1 (64 or 128 columns each)
+constexpr int kRowHalf = kTileRows * 128;   // bytes of one [128 x 64] 16-bit block of a row tile
+constexpr int kColHalf = kCols * 128;       // bytes of one [64 x 64] 16-bit block of a column tile
 
-struct Smem {
+template <int DH>
+struct SmemB {
+    static constexpr int kHalves = DH / 64;
+    static constexpr int kTile = kRowHalf * kHalves;             // row tile  [128 x DH]
+    static constexpr int kColTile = kColHalf * kHalves;          // column tile [64 x DH]
     static constexpr int kR1 = 0;
     static constexpr int kR2 = kR1 + kTile;
     static constexpr int kC1 = kR2 + kTile;                     // [kStages]
@@ -49,6 +52,8 @@ struct Smem {
     static constexpr int kStats = kC2 + kStages * kColTile;     // [kStages][2][64] float
     static constexpr int kBar = kStats + kStages * 512;
     static constexpr int kTotal = kBar + 256;
+    static constexpr uint32_t kTmemCols = DH == 64 ? 256 : 512;
+    static constexpr uint32_t kColA2 = kColA1 + DH;
 };
 
 __device__ __forceinline__ int ws1(int p, int L, int K) { return window_start(p, L, K, 1); }
@@ -67,14 +72,16 @@ __device__ __forceinline__ void inverse_range(int n, int L, int K, int causal, i
 
 // kInner: innermost chunk extent when it is 16 or 32 (separable row / column masks, packed
 // 16-bit arithmetic), 0 = any geometry (per-column validity words).
-template <bool BF16, bool kKeySide, int kInner>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int DH, bool BF16, bool kKeySide, int kInner>
+__global__ void __launch_bounds__(kThreads, (DH == 64 ? 2 : 1))
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
               const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2,
               const __grid_constant__ TcParams P, const float* __restrict__ lse,
               const float* __restrict__ delta, uint16_t* __restrict__ out1, uint16_t* __restrict__ out2)
 {
-    constexpr int DH = 64;
+    using Smem = SmemB<DH>;
+    constexpr int kTile = Smem::kTile, kColTile = Smem::kColTile, CH = DH / 2;
+    constexpr uint32_t kTmemCols = Smem::kTmemCols, kColA2 = Smem::kColA2;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // query side: blockIdx.y = query head.  key side: blockIdx.y = kv head.
@@ -121,9 +128,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 const long long orow = ((long long)b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + hy;
 #pragma unroll
                 for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
-                    uint4* o = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + orow * DH + piece * 32);
+                    uint4* o = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + orow * DH + piece * CH);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) o[i] = make_uint4(0, 0, 0, 0);
+                    for (int i = 0; i < CH / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
                 }
             }
         }
@@ -156,8 +163,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         // query side: columns are keys (kv head); key side: columns are queries (query head)
         const int hx = (kKeySide ? hy * P.group + ld_head : head_kv) * DH;
         mbar_expect_tx(bar, 2 * kColTile);
-        tma_load_5d(sbase + Smem::kC1 + s * kColTile, &tmC1, bar, hx, X[2], X[1], X[0], b);
-        tma_load_5d(sbase + Smem::kC2 + s * kColTile, &tmC2, bar, hx, X[2], X[1], X[0], b);
+#pragma unroll
+        for (int hf = 0; hf < Smem::kHalves; ++hf) {
+            tma_load_5d(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmC1, bar, hx + 64 * hf, X[2], X[1], X[0], b);
+            tma_load_5d(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmC2, bar, hx + 64 * hf, X[2], X[1], X[0], b);
+        }
         ++loaded;
         if (++ld[2] == nc[2]) { ld[2] = 0; if (++ld[1] == nc[1]) { ld[1] = 0; if (++ld[0] == nc[0]) { ld[0] = 0; ++ld_head; } } }
     };
@@ -176,10 +186,13 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             if (!*abort_flag) {
                 const int hx = (kKeySide ? head_kv : head_row) * DH;
                 mbar_expect_tx(bar_row, 2 * kTile);
-                tma_load_5d(sbase + Smem::kR1, &tmR1, bar_row, hx, rg[2] + P.dil[2] * origin[2],
-                            rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
-                tma_load_5d(sbase + Smem::kR2, &tmR2, bar_row, hx, rg[2] + P.dil[2] * origin[2],
-                            rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
+#pragma unroll
+                for (int hf = 0; hf < Smem::kHalves; ++hf) {
+                    tma_load_5d(sbase + Smem::kR1 + hf * kRowHalf, &tmR1, bar_row, hx + 64 * hf, rg[2] + P.dil[2] * origin[2],
+                                rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
+                    tma_load_5d(sbase + Smem::kR2 + hf * kRowHalf, &tmR2, bar_row, hx + 64 * hf, rg[2] + P.dil[2] * origin[2],
+                                rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
+                }
                 for (int cc = 0; cc < total && cc < kStages; ++cc) issue_cols();
             }
         }
@@ -248,34 +261,39 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         if (lane == 0 && !*abort_flag) {
             constexpr uint32_t idesc_kk = instr_desc(BF16 ? 1 : 0, kCols, 0, 0);    // both operands K-major
             constexpr uint32_t idesc_acc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A from TMEM, B MN-major
+            const uint64_t dR1 = smem_desc(sbase + Smem::kR1, 16, 1024), dR2 = smem_desc(sbase + Smem::kR2, 16, 1024);
             auto issue_s_dp = [&](int cc) {
                 const int s = cc % kStages;
+                const uint64_t dC1 = smem_desc(sbase + Smem::kC1 + s * kColTile, 16, 1024);
+                const uint64_t dC2 = smem_desc(sbase + Smem::kC2 + s * kColTile, 16, 1024);
                 tc_fence_after();
+                // 32 bytes per k-step inside a 64-channel block; blocks are kRowHalf / kColHalf apart
 #pragma unroll
                 for (int ks = 0; ks < DH / 16; ++ks)
-                    mma_ss(tmem + kColS, smem_desc(sbase + Smem::kR1 + ks * 32, 16, 1024),
-                           smem_desc(sbase + Smem::kC1 + s * kColTile + ks * 32, 16, 1024), idesc_kk, ks > 0);
+                    mma_ss(tmem + kColS, dR1 + (((ks / 4) * kRowHalf + (ks % 4) * 32) >> 4),
+                           dC1 + (((ks / 4) * kColHalf + (ks % 4) * 32) >> 4), idesc_kk, ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < DH / 16; ++ks)
-                    mma_ss(tmem + kColDP, smem_desc(sbase + Smem::kR2 + ks * 32, 16, 1024),
-                           smem_desc(sbase + Smem::kC2 + s * kColTile + ks * 32, 16, 1024), idesc_kk, ks > 0);
+                    mma_ss(tmem + kColDP, dR2 + (((ks / 4) * kRowHalf + (ks % 4) * 32) >> 4),
+                           dC2 + (((ks / 4) * kColHalf + (ks % 4) * 32) >> 4), idesc_kk, ks > 0);
                 mma_commit(bar_s);
             };
             // k-step ks covers columns 16*ks..16*ks+15 of the chunk; their 16-bit pairs sit in the
-            // first 16 TMEM columns of the 32-column piece they came from.
+            // first 16 TMEM columns of the 32-column piece they came from.  The column tile is read
+            // MN-major: 16 rows (2048 bytes) per k-step, the second 64-channel block kColHalf further.
             auto issue_acc = [&](int cc) {
                 const int s = cc % kStages;
+                const uint64_t dC1 = smem_desc(sbase + Smem::kC1 + s * kColTile, kColHalf, 1024);
+                const uint64_t dC2 = smem_desc(sbase + Smem::kC2 + s * kColTile, kColHalf, 1024);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kCols / 16; ++ks)
-                    mma_ts(tmem + kColA1, tmem + kColDP + 32 * (ks / 2) + 8 * (ks % 2),
-                           smem_desc(sbase + Smem::kC1 + s * kColTile + ks * 2048, kColTile, 1024), idesc_acc,
+                    mma_ts(tmem + kColA1, tmem + kColDP + 32 * (ks / 2) + 8 * (ks % 2), dC1 + 128 * ks, idesc_acc,
                            (cc > 0 || ks > 0) ? 1u : 0u);
                 if (kKeySide) {
 #pragma unroll
                     for (int ks = 0; ks < kCols / 16; ++ks)
-                        mma_ts(tmem + kColA2, tmem + kColS + 32 * (ks / 2) + 8 * (ks % 2),
-                               smem_desc(sbase + Smem::kC2 + s * kColTile + ks * 2048, kColTile, 1024), idesc_acc,
+                        mma_ts(tmem + kColA2, tmem + kColS + 32 * (ks / 2) + 8 * (ks % 2), dC2 + 128 * ks, idesc_acc,
                                (cc > 0 || ks > 0) ? 1u : 0u);
                 }
                 mma_commit(bar_acc);
@@ -482,18 +500,21 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         const bool live = valid_row && ok;
 #pragma unroll
         for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
-            uint32_t a[32];
-            tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + 32 * piece, a);
-            tmem_ld_wait();
-            if (in_tensor) {
-                uint4* d4 = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * DH + piece * 32);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint32_t w[4];
+            for (int part = 0; part < CH / 32; ++part) {
+                uint32_t a[32];
+                tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + CH * piece + 32 * part, a);
+                tmem_ld_wait();
+                if (in_tensor) {
+                    uint4* d4 = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * DH + piece * CH + 32 * part);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        w[j] = live ? pack16(__uint_as_float(a[8 * i + 2 * j]), __uint_as_float(a[8 * i + 2 * j + 1]), BF16) : 0u;
-                    d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            w[j] = live ? pack16(__uint_as_float(a[8 * i + 2 * j]), __uint_as_float(a[8 * i + 2 * j + 1]), BF16) : 0u;
+                        d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
             }
         }
@@ -508,19 +529,19 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     }
 }
 
-// delta[row] = sum_d out[row,d]*dout[row,d] - dlse[row]
-template <bool BF16>
+// delta[row] = sum_d out[row,d]*dout[row,d] - dlse[row]      (DH/8 threads per row, 16 bytes each)
+template <int DH, bool BF16>
 __global__ void tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ dout,
                                 const float* __restrict__ dlse, float* __restrict__ delta, long long rows)
 {
-    // 8 threads per 64-channel row, 16 bytes each
+    constexpr int kPer = DH / 8;
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long row = t >> 3;
-    const int part = (int)(t & 7);
+    const long long row = t / kPer;
+    const int part = (int)(t % kPer);
     float acc = 0.f;
     if (row < rows) {
-        const uint4 a = reinterpret_cast<const uint4*>(out + row * 64)[part];
-        const uint4 g = reinterpret_cast<const uint4*>(dout + row * 64)[part];
+        const uint4 a = reinterpret_cast<const uint4*>(out + row * DH)[part];
+        const uint4 g = reinterpret_cast<const uint4*>(dout + row * DH)[part];
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -535,34 +556,34 @@ __global__ void tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t
             acc += x.x * y.x + x.y * y.y;
         }
     }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+#pragma unroll
+    for (int o = 1; o < kPer; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (row < rows && part == 0) delta[row] = acc - (dlse ? dlse[row] : 0.f);
 }
 
-template <bool BF16>
+template <int DH, bool BF16>
 int launch_bwd(const Geo& g, const Plan& plan, const void* q, const void* k, const void* v,
                const void* out, const void* lse, const void* dout, const void* dlse, void* dq, void* dk,
                void* dv, float* delta, cudaStream_t s)
 {
     const TcParams& p = plan.p;
     const long long qrows = (long long)g.B * g.ltot * g.Hq;
-    tc_delta_kernel<BF16><<<(unsigned)((qrows * 8 + 255) / 256), 256, 0, s>>>(
+    tc_delta_kernel<DH, BF16><<<(unsigned)((qrows * (DH / 8) + 255) / 256), 256, 0, s>>>(
         (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, qrows);
     tc_count_launch();
 
     const long long dos[3] = {g.ltot * g.Hq * g.Dv, (long long)g.Hq * g.Dv, g.Dv};   // dout is contiguous
     CUtensorMap q_tile, do_tile, k_chunk, v_chunk, k_tile, v_tile, q_chunk, do_chunk;
     const bool bf = BF16;
-    if (!encode_map(&q_tile, q, bf, p, g.Hq, 64, g.qs, plan.box_q) ||
-        !encode_map(&do_tile, dout, bf, p, g.Hq, 64, dos, plan.box_q) ||
-        !encode_map(&k_chunk, k, bf, p, g.Hkv, 64, g.ks, plan.box_kv) ||
-        !encode_map(&v_chunk, v, bf, p, g.Hkv, 64, g.vs, plan.box_kv) ||
-        !encode_map(&k_tile, k, bf, p, g.Hkv, 64, g.ks, plan.box_q) ||
-        !encode_map(&v_tile, v, bf, p, g.Hkv, 64, g.vs, plan.box_q) ||
-        !encode_map(&q_chunk, q, bf, p, g.Hq, 64, g.qs, plan.box_kv) ||
-        !encode_map(&do_chunk, dout, bf, p, g.Hq, 64, dos, plan.box_kv))
+    using Smem = SmemB<DH>;
+    if (!encode_map(&q_tile, q, bf, p, g.Hq, DH, g.qs, plan.box_q) ||
+        !encode_map(&do_tile, dout, bf, p, g.Hq, DH, dos, plan.box_q) ||
+        !encode_map(&k_chunk, k, bf, p, g.Hkv, DH, g.ks, plan.box_kv) ||
+        !encode_map(&v_chunk, v, bf, p, g.Hkv, DH, g.vs, plan.box_kv) ||
+        !encode_map(&k_tile, k, bf, p, g.Hkv, DH, g.ks, plan.box_q) ||
+        !encode_map(&v_tile, v, bf, p, g.Hkv, DH, g.vs, plan.box_q) ||
+        !encode_map(&q_chunk, q, bf, p, g.Hq, DH, g.qs, plan.box_kv) ||
+        !encode_map(&do_chunk, dout, bf, p, g.Hq, DH, dos, plan.box_kv))
         return -2;
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= p.dil[a];
@@ -572,14 +593,14 @@ int launch_bwd(const Geo& g, const Plan& plan, const void* q, const void* k, con
         constexpr int kInner = decltype(inner)::value;
         static bool attr_done = false;
         if (!attr_done) {
-            cudaFuncSetAttribute(tc_bwd_kernel<BF16, false, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
-            cudaFuncSetAttribute(tc_bwd_kernel<BF16, true, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+            cudaFuncSetAttribute(tc_bwd_kernel<DH, BF16, false, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+            cudaFuncSetAttribute(tc_bwd_kernel<DH, BF16, true, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
             attr_done = true;
         }
-        tc_bwd_kernel<BF16, false, kInner><<<grid_q, kThreads, Smem::kTotal, s>>>(
+        tc_bwd_kernel<DH, BF16, false, kInner><<<grid_q, kThreads, Smem::kTotal, s>>>(
             q_tile, do_tile, k_chunk, v_chunk, p, (const float*)lse, delta, (uint16_t*)dq, nullptr);
         tc_count_launch();
-        tc_bwd_kernel<BF16, true, kInner><<<grid_k, kThreads, Smem::kTotal, s>>>(
+        tc_bwd_kernel<DH, BF16, true, kInner><<<grid_k, kThreads, Smem::kTotal, s>>>(
             k_tile, v_tile, q_chunk, do_chunk, p, (const float*)lse, delta, (uint16_t*)dk, (uint16_t*)dv);
         tc_count_launch();
     };
@@ -607,8 +628,11 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     if (g.B == 0) return 0;
     if (g.Hq > 65535 || g.B > 65535) return -2;
     float* delta = reinterpret_cast<float*>(workspace);
-    return dtype == 2 ? launch_bwd<true>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s)
-                      : launch_bwd<false>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s);
+    if (g.D == 64)
+        return dtype == 2 ? launch_bwd<64, true>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s)
+                          : launch_bwd<64, false>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s);
+    return dtype == 2 ? launch_bwd<128, true>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s)
+                      : launch_bwd<128, false>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s);
 }
 
 size_t tc_bwd_workspace_bytes(int, const Geo&) { return 0; }

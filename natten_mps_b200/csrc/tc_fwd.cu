@@ -42,16 +42,16 @@ int* status_ptr()
 
 namespace {
 
-constexpr int kStages = 3;
 constexpr int kThreads = 288;            // 8 softmax warps + 1 TMA/MMA warp
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColP = 128, kColO = 192;
+constexpr uint32_t kColS = 0, kColP = 128;      // S: 128 columns, P: 64; O follows (64 or 128 columns)
 
 // Shared-memory map (dynamic, base must be 1024-byte aligned).
 template <int DH>
 struct SmemMap {
-    static constexpr int kHalves = DH / 64;
-    static constexpr int kTile = kTileRows * 128 * kHalves;       // bytes of one [128 x DH] 16-bit tile
+    static constexpr int kHalves = DH / 64;                       // 64-channel blocks (one swizzle row each)
+    static constexpr int kStages = DH == 64 ? 3 : 2;
+    static constexpr int kHalf = kTileRows * 128;                 // bytes of one [128 x 64] 16-bit block
+    static constexpr int kTile = kHalf * kHalves;                 // bytes of one [128 x DH] 16-bit tile
     static constexpr int kQ = 0;
     static constexpr int kK = kQ + kTile;
     static constexpr int kV = kK + kStages * kTile;
@@ -59,20 +59,24 @@ struct SmemMap {
     // barriers: q, kv_full[3], s_full, sp_ready, o_full  (8 bytes each) + tmem ptr + abort flag,
     // then 512 bytes for the two column halves to exchange their row maxima
     static constexpr int kTotal = kBar + 128 + 512;
+    static constexpr uint32_t kTmemCols = DH == 64 ? 256 : 512;
+    static constexpr uint32_t kColO = DH == 64 ? 192 : 256;
 };
 
 __device__ __forceinline__ int tc_window_start(int p, int L, int K) { return window_start(p, L, K, 1); }
 
 // kInner: innermost chunk extent when it is 16 or 32 (separable row / column masks),
 // 0 = any geometry (per-column validity words from piece_word).
-template <bool BF16, int kInner>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int DH, bool BF16, int kInner>
+__global__ void __launch_bounds__(kThreads, (DH == 64 ? 2 : 1))
 tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ TcParams P,
               uint16_t* __restrict__ out, float* __restrict__ lse)
 {
-    constexpr int DH = 64;
     using SM = SmemMap<DH>;
+    constexpr int kStages = SM::kStages;
+    constexpr int CH = DH / 2;                 // output channels per softmax thread
+    constexpr uint32_t kColO = SM::kColO, kTmemCols = SM::kTmemCols;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y, b = blockIdx.z, hk = h / P.group;
@@ -109,9 +113,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
             if (inside) {
                 const long long orow = ((long long)b * P.ltot + pflat) * P.Hq + h;
-                uint4* o4 = reinterpret_cast<uint4*>(out + orow * DH + team * 32);
+                uint4* o4 = reinterpret_cast<uint4*>(out + orow * DH + team * CH);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) o4[i] = make_uint4(0, 0, 0, 0);
+                for (int i = 0; i < CH / 8; ++i) o4[i] = make_uint4(0, 0, 0, 0);
                 if (team == 0) lse[orow] = 0.f;
             }
         }
@@ -141,8 +145,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const int s = loaded % kStages;
         const uint32_t bar = bar_kv + 8 * s;
         mbar_expect_tx(bar, 2 * SM::kTile);
-        tma_load_5d(sbase + SM::kK + s * SM::kTile, &tmK, bar, hk * DH, X[2], X[1], X[0], b);
-        tma_load_5d(sbase + SM::kV + s * SM::kTile, &tmV, bar, hk * DH, X[2], X[1], X[0], b);
+#pragma unroll
+        for (int hf = 0; hf < SM::kHalves; ++hf) {
+            tma_load_5d(sbase + SM::kK + s * SM::kTile + hf * SM::kHalf, &tmK, bar, hk * DH + 64 * hf, X[2], X[1], X[0], b);
+            tma_load_5d(sbase + SM::kV + s * SM::kTile + hf * SM::kHalf, &tmV, bar, hk * DH + 64 * hf, X[2], X[1], X[0], b);
+        }
         ++loaded;
         if (++ld[2] == nc[2]) { ld[2] = 0; if (++ld[1] == nc[1]) { ld[1] = 0; ++ld[0]; } }
     };
@@ -162,8 +169,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             tw1 = clock64();
             if (!*abort_flag) {
                 mbar_expect_tx(bar_q, SM::kTile);
-                tma_load_5d(sbase + SM::kQ, &tmQ, bar_q, h * DH, rg[2] + P.dil[2] * origin[2],
-                            rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
+#pragma unroll
+                for (int hf = 0; hf < SM::kHalves; ++hf)
+                    tma_load_5d(sbase + SM::kQ + hf * SM::kHalf, &tmQ, bar_q, h * DH + 64 * hf,
+                                rg[2] + P.dil[2] * origin[2], rg[1] + P.dil[1] * origin[1],
+                                rg[0] + P.dil[0] * origin[0], b);
                 for (int c = 0; c < nch && c < kStages; ++c) issue_kv();
             }
         }
@@ -222,12 +232,15 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 const uint64_t dk0 = smem_desc(sbase + SM::kK + (c % kStages) * SM::kTile, 16, 1024);
                 tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < DH / 16; ++ks)
-                    mma_ss(tmem + kColS, dq0 + 2 * ks, dk0 + 2 * ks, idesc_qk, ks > 0);
+                for (int ks = 0; ks < DH / 16; ++ks) {       // 32 bytes per k-step inside a 64-channel block
+                    const uint32_t off = ((ks / 4) * SM::kHalf + (ks % 4) * 32) >> 4;
+                    mma_ss(tmem + kColS, dq0 + off, dk0 + off, idesc_qk, ks > 0);
+                }
                 mma_commit(bar_s);
             };
             auto issue_pv = [&](int c) {
-                const uint64_t dv0 = smem_desc(sbase + SM::kV + (c % kStages) * SM::kTile, SM::kTile, 1024);
+                // V read MN-major: 16 key rows per k-step, the second 64-channel block sits kHalf bytes further
+                const uint64_t dv0 = smem_desc(sbase + SM::kV + (c % kStages) * SM::kTile, SM::kHalf, 1024);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kChunk / 16; ++ks)
@@ -266,9 +279,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const uint32_t trow = tmem + (static_cast<uint32_t>(quad * 32) << 16);
         const int row = quad * 32 + lane;
         float m = -INFINITY, l = 0.f;
-        float acc[32];
+        float acc[CH];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+        for (int i = 0; i < CH; ++i) acc[i] = 0.f;
         bool ok = true;
         int ci[3] = {0, 0, 0};
         uint32_t colbits = 0u;                   // separable geometry: valid columns of one inner row
@@ -346,11 +359,14 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             if (c > 0) {
                 ok = ok && mbar_wait(bar_o, (c - 1) & 1, abort_flag);
                 tc_fence_after();
-                uint32_t o[32];
-                tmem_ld32(trow + kColO + 32 * team, o);
-                tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) acc[i] = (acc[i] + __uint_as_float(o[i])) * alpha;
+                for (int part = 0; part < CH / 32; ++part) {
+                    uint32_t o[32];
+                    tmem_ld32(trow + kColO + CH * team + 32 * part, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[32 * part + i] = (acc[32 * part + i] + __uint_as_float(o[i])) * alpha;
+                }
             }
 
             if (warp == 0 && lane == 0) stamp(64);
@@ -390,12 +406,13 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         // ---- last chunk's P V, combine the two halves' sums, normalise, write out ----
         ok = ok && mbar_wait(bar_o, (nch - 1) & 1, abort_flag);
         tc_fence_after();
-        {
+#pragma unroll
+        for (int part = 0; part < CH / 32; ++part) {
             uint32_t o[32];
-            tmem_ld32(trow + kColO + 32 * team, o);
+            tmem_ld32(trow + kColO + CH * team + 32 * part, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] += __uint_as_float(o[i]);
+            for (int i = 0; i < 32; ++i) acc[32 * part + i] += __uint_as_float(o[i]);
         }
         // every MMA has finished, so the first K stage can carry the partial row sums
         float* xsum = reinterpret_cast<float*>(smem + SM::kK);
@@ -405,9 +422,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (in_tensor) {
             const bool live = valid_q && l > 0.f && ok;
             const float inv = live ? 1.f / l : 0.f;
-            uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH + team * 32);
+            uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH + team * CH);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < CH / 8; ++i) {
                 uint32_t w[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
@@ -453,25 +470,30 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     const dim3 grid((unsigned)(plan.p.ntiles * ngroups), (unsigned)g.Hq, (unsigned)g.B);
     if (grid.x == 0 || g.B == 0) return 0;
     if (g.Hq > 65535 || g.B > 65535) return -2;
-    using SM = SmemMap<64>;
     cudaError_t err;
-    auto launch = [&](auto bf, auto inner) {
+    auto launch = [&](auto dh, auto bf, auto inner) {
+        constexpr int kDh = decltype(dh)::value;
         constexpr bool kBf = decltype(bf)::value;
         constexpr int kInner = decltype(inner)::value;
+        using SM = SmemMap<kDh>;
         static bool once = false;
         if (!once) {
-            cudaFuncSetAttribute(tc_fwd_kernel<kBf, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
+            cudaFuncSetAttribute(tc_fwd_kernel<kDh, kBf, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
             once = true;
         }
-        tc_fwd_kernel<kBf, kInner><<<grid, kThreads, SM::kTotal, s>>>(mq, mk, mv, plan.p, (uint16_t*)out, (float*)lse);
+        tc_fwd_kernel<kDh, kBf, kInner><<<grid, kThreads, SM::kTotal, s>>>(mq, mk, mv, plan.p, (uint16_t*)out, (float*)lse);
     };
-    auto by_inner = [&](auto bf) {
-        if (plan.p.cb[2] == 16) launch(bf, std::integral_constant<int, 16>{});
-        else if (plan.p.cb[2] == 32) launch(bf, std::integral_constant<int, 32>{});
-        else launch(bf, std::integral_constant<int, 0>{});
+    auto by_inner = [&](auto dh, auto bf) {
+        if (plan.p.cb[2] == 16) launch(dh, bf, std::integral_constant<int, 16>{});
+        else if (plan.p.cb[2] == 32) launch(dh, bf, std::integral_constant<int, 32>{});
+        else launch(dh, bf, std::integral_constant<int, 0>{});
     };
-    if (bf16) by_inner(std::true_type{});
-    else by_inner(std::false_type{});
+    auto by_type = [&](auto dh) {
+        if (bf16) by_inner(dh, std::true_type{});
+        else by_inner(dh, std::false_type{});
+    };
+    if (g.D == 64) by_type(std::integral_constant<int, 64>{});
+    else by_type(std::integral_constant<int, 128>{});
     err = cudaGetLastError();
     tc_count_launch();
     return err == cudaSuccess ? 0 : (int)err;

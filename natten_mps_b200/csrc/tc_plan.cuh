@@ -266,7 +266,7 @@ inline bool encode_map(CUtensorMap* map, const void* base, bool bf16, const TcPa
 inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, const void* v)
 {
     if (dtype != 1 && dtype != 2) return false;                 // f16 / bf16
-    if (g.D != 64 || g.Dv != 64) return false;
+    if ((g.D != 64 && g.D != 128) || g.Dv != g.D) return false;
     if (g.n_extra != 0) return false;
     if (!(g.scale > 0.0)) return false;
     for (int a = 0; a < g.rank; ++a) {

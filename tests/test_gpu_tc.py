@@ -24,20 +24,34 @@ CASES = [
     ((6, 20, 18), 1, 2, 2, (3, 7, 7), (1, 1, 1), (True, False, False), None),
     ((5, 9, 11), 1, 2, 1, (3, 3, 5), (1, 2, 1), (False, False, False), None),
     ((8, 12, 12), 2, 1, 1, (3, 5, 5), (1, 1, 1), (False, False, False), [[8, 12, 12], [4, 7, 9]]),
+    # head dim 128 (ninth field)
+    ((40, 24), 1, 2, 1, (7, 7), (1, 1), (False, False), None, 128),
+    ((600,), 2, 4, 1, (255,), (1,), (False,), [[600], [300]], 128),
+    ((5, 9, 17), 1, 2, 2, (3, 5, 7), (1, 1, 1), (True, False, False), None, 128),
+    ((26, 30), 1, 2, 2, (5, 5), (2, 2), (False, False), None, 128),
 ]
 
 
+def _dim(case):
+    return case[8] if len(case) > 8 else 64
+
+
+def _id(c):
+    return "x".join(map(str, c[0])) + f"_k{c[4][0]}_d{c[5][0]}_h{_dim(c)}"
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
-@pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c[0])) + f"_k{c[4][0]}_d{c[5][0]}")
+@pytest.mark.parametrize("case", CASES, ids=_id)
 def test_tc_forward_matches_simt(case, dtype):
-    spatial, B, Hq, Hkv, ks, dil, causal, extents = case
+    spatial, B, Hq, Hkv, ks, dil, causal, extents = case[:8]
+    D = _dim(case)
     rank = len(spatial)
     g = torch.Generator(device="cpu").manual_seed(7)
-    q = torch.randn((B, *spatial, Hq, 64), generator=g).to(dtype).cuda()
-    k = torch.randn((B, *spatial, Hkv, 64), generator=g).to(dtype).cuda()
-    v = torch.randn((B, *spatial, Hkv, 64), generator=g).to(dtype).cuda()
+    q = torch.randn((B, *spatial, Hq, D), generator=g).to(dtype).cuda()
+    k = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    v = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
     ext = None if extents is None else torch.tensor(extents, dtype=torch.int32).cuda()
-    args = (q, k, v, ks, (1,) * rank, dil, causal, 0.125)
+    args = (q, k, v, ks, (1,) * rank, dil, causal, D ** -0.5)
     try:
         _cabi.set_force("simt")
         ref_out, ref_lse = _backend.fused_forward(*args, extents=ext)
@@ -55,18 +69,19 @@ def test_tc_forward_matches_simt(case, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
-@pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c[0])) + f"_k{c[4][0]}_d{c[5][0]}")
+@pytest.mark.parametrize("case", CASES, ids=_id)
 def test_tc_backward_matches_simt(case, dtype):
-    spatial, B, Hq, Hkv, ks, dil, causal, extents = case
+    spatial, B, Hq, Hkv, ks, dil, causal, extents = case[:8]
+    D = _dim(case)
     rank = len(spatial)
     g = torch.Generator(device="cpu").manual_seed(11)
-    q = torch.randn((B, *spatial, Hq, 64), generator=g).to(dtype).cuda()
-    k = torch.randn((B, *spatial, Hkv, 64), generator=g).to(dtype).cuda()
-    v = torch.randn((B, *spatial, Hkv, 64), generator=g).to(dtype).cuda()
-    go = torch.randn((B, *spatial, Hq, 64), generator=g).to(dtype).cuda()
+    q = torch.randn((B, *spatial, Hq, D), generator=g).to(dtype).cuda()
+    k = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    v = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    go = torch.randn((B, *spatial, Hq, D), generator=g).to(dtype).cuda()
     glse = torch.randn((B, *spatial, Hq), generator=g).cuda()
     ext = None if extents is None else torch.tensor(extents, dtype=torch.int32).cuda()
-    geo = (ks, (1,) * rank, dil, causal, 0.125)
+    geo = (ks, (1,) * rank, dil, causal, D ** -0.5)
     try:
         _cabi.set_force("simt")
         out, lse = _backend.fused_forward(q, k, v, *geo, extents=ext)
