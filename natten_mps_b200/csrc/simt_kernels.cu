@@ -896,6 +896,32 @@ cudaError_t simt_fused_bwd(int dtype, const Geo& g, const void* q, const void* k
                                           workspace, s));
 }
 
+// Gradients of the additional tokens only (used next to the tensor-core backward, which
+// covers dq/dk/dv).  `delta` must already hold rowsum(out*dout) - dlse.
+template <typename T>
+cudaError_t fused_bwd_extra_t(const Geo& g, const void* q, const void* ek, const void* ev, const void* lse,
+                              const void* delta, const void* dout, void* dek, void* dev, cudaStream_t s)
+{
+    using A = typename AccOf<T>::type;
+    if (g.n_extra <= 0 || g.B <= 0) return cudaSuccess;
+    const size_t smem = (size_t)(kWarps + 1) * (g.D + g.Dv) * sizeof(A);
+    const int dmax = g.D > g.Dv ? g.D : g.Dv;
+    const unsigned blocks = (unsigned)((long long)g.B * g.n_extra * g.Hkv);
+    NATTEN_DISPATCH_N(dmax, ND,
+        fused_bwd_extra_kernel<T, ND, ND><<<blocks, kWarps * 32, smem, s>>>(
+            g, (const T*)q, (const T*)ek, (const T*)ev, (const A*)lse, (const A*)delta, (const T*)dout,
+            (const A*)nullptr, (T*)dek, (T*)dev));
+    ++g_launches;
+    return cudaGetLastError();
+}
+
+cudaError_t simt_fused_bwd_extra(int dtype, const Geo& g, const void* q, const void* ek, const void* ev,
+                                 const void* lse, const void* delta, const void* dout, void* dek, void* dev,
+                                 cudaStream_t s)
+{
+    NATTEN_BY_DTYPE(dtype, fused_bwd_extra_t<T>(g, q, ek, ev, lse, delta, dout, dek, dev, s));
+}
+
 cudaError_t simt_qk_fwd(int dtype, const Geo& g, const void* q, const void* k, void* logits, cudaStream_t s)
 {
     NATTEN_BY_DTYPE(dtype, qk_fwd_t<T>(g, q, k, logits, s));

@@ -10,6 +10,9 @@ cudaError_t simt_fused_bwd(int dtype, const Geo& g, const void* q, const void* k
                            const void* ek, const void* ev, const void* out, const void* lse,
                            const void* dout, const void* dlse, void* dq, void* dk, void* dv,
                            void* dek, void* dev, void* workspace, cudaStream_t s);
+cudaError_t simt_fused_bwd_extra(int dtype, const Geo& g, const void* q, const void* ek, const void* ev,
+                                 const void* lse, const void* delta, const void* dout, void* dek, void* dev,
+                                 cudaStream_t s);
 cudaError_t simt_qk_fwd(int dtype, const Geo& g, const void* q, const void* k, void* logits, cudaStream_t s);
 cudaError_t simt_qk_bwd(int dtype, const Geo& g, const void* q, const void* k, const void* dlogits,
                         void* dq, void* dk, cudaStream_t s);

@@ -21,6 +21,7 @@
 // they were computed from (same warp, after it has read them).
 #include "tc_kernels.cuh"
 
+#include "simt_kernels.cuh"
 #include "tc_plan.cuh"
 
 #include <type_traits>
@@ -76,6 +77,7 @@ template <int DH, bool BF16, bool kKeySide, int kInner>
 __global__ void __launch_bounds__(kThreads, (DH == 64 ? 2 : 1))
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
               const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2,
+              const __grid_constant__ CUtensorMap tmE1, const __grid_constant__ CUtensorMap tmE2,
               const __grid_constant__ TcParams P, const float* __restrict__ lse,
               const float* __restrict__ delta, uint16_t* __restrict__ out1, uint16_t* __restrict__ out2)
 {
@@ -149,27 +151,38 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     const uint32_t bar_acc = sbase + Smem::kBar + 88;         // accumulating MMAs of the chunk finished
     float* stats = reinterpret_cast<float*>(smem + Smem::kStats);
 
-    const int total = nchunks * n_heads_col;                 // column passes of this CTA
+    // column passes of this CTA; on the query side the additional tokens follow, 64 per pass
+    const int nbox = nchunks * n_heads_col;
+    const int total = nbox + (kKeySide ? 0 : ((P.n_extra + kCols - 1) >> 6));
     const int head_row = hy;                                  // head coordinate of the row tensors
     const int head_kv = kKeySide ? hy : hy / P.group;
     // Column loads are issued in order; counters avoid divisions.
     int ld[3] = {0, 0, 0}, ld_head = 0, loaded = 0;
     auto issue_cols = [&]() {
-        int X[3];
-#pragma unroll
-        for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (boxlo[a] + ld[a] * P.cb[a]);
         const int s = loaded % kStages;
         const uint32_t bar = bar_col + 8 * s;
-        // query side: columns are keys (kv head); key side: columns are queries (query head)
-        const int hx = (kKeySide ? hy * P.group + ld_head : head_kv) * DH;
         mbar_expect_tx(bar, 2 * kColTile);
+        if (loaded < nbox) {
+            int X[3];
 #pragma unroll
-        for (int hf = 0; hf < Smem::kHalves; ++hf) {
-            tma_load_5d(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmC1, bar, hx + 64 * hf, X[2], X[1], X[0], b);
-            tma_load_5d(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmC2, bar, hx + 64 * hf, X[2], X[1], X[0], b);
+            for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (boxlo[a] + ld[a] * P.cb[a]);
+            // query side: columns are keys (kv head); key side: columns are queries (query head)
+            const int hx = (kKeySide ? hy * P.group + ld_head : head_kv) * DH;
+#pragma unroll
+            for (int hf = 0; hf < Smem::kHalves; ++hf) {
+                tma_load_5d(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmC1, bar, hx + 64 * hf, X[2], X[1], X[0], b);
+                tma_load_5d(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmC2, bar, hx + 64 * hf, X[2], X[1], X[0], b);
+            }
+            if (++ld[2] == nc[2]) { ld[2] = 0; if (++ld[1] == nc[1]) { ld[1] = 0; if (++ld[0] == nc[0]) { ld[0] = 0; ++ld_head; } } }
+        } else {                                 // additional tokens (rows past n_extra are zero-filled)
+            const int e0 = (loaded - nbox) * kCols;
+#pragma unroll
+            for (int hf = 0; hf < Smem::kHalves; ++hf) {
+                tma_load_5d(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmE1, bar, head_kv * DH + 64 * hf, e0, 0, 0, b);
+                tma_load_5d(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmE2, bar, head_kv * DH + 64 * hf, e0, 0, 0, b);
+            }
         }
         ++loaded;
-        if (++ld[2] == nc[2]) { ld[2] = 0; if (++ld[1] == nc[1]) { ld[1] = 0; if (++ld[0] == nc[0]) { ld[0] = 0; ++ld_head; } } }
     };
     // The issuing warp sets up the barriers, allocates TMEM and starts the first loads right away,
     // so they are in flight while the compute warps are still working out their row geometry.
@@ -376,7 +389,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             uint32_t word = 0u;                  // generic geometry: one bit per column
             uint32_t rowmask[kRows];             // separable geometry: all-ones / zero per inner row
             bool mine = false;
-            if (kInner > 0) {
+            const bool extra = !kKeySide && cc >= nbox;      // additional tokens: first n_extra columns, every live row
+            if (extra) {
+                word = valid_row ? low_bits(P.n_extra - ((cc - nbox) * kCols + 32 * piece)) : 0u;
+                mine = word != 0u;
+            } else if (kInner > 0) {
                 if (ci[2] != cached_c2) {        // the column masks only change with the innermost chunk index
                     cached_c2 = ci[2];
                     const int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
@@ -401,7 +418,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 mine = word != 0u;
             }
             const bool any = __any_sync(0xffffffffu, mine);
-            const bool full = kInner == 0 && __all_sync(0xffffffffu, word == 0xffffffffu);
+            const bool separable = kInner > 0 && !extra;
+            const bool full = !separable && __all_sync(0xffffffffu, word == 0xffffffffu);
 
             if (warp == 0 && lane == 0) stamp(64);
             ok = ok && mbar_wait(bar_s, cc & 1, abort_flag);     // also: the previous chunk's P/dS were consumed
@@ -417,7 +435,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                     tmem_ld16(trow + kColS + 32 * piece + 16 * half, s);
                     tmem_ld16(trow + kColDP + 32 * piece + 16 * half, dp);
                     tmem_ld_wait();
-                    if (kInner > 0 || full) {
+                    if (separable || full) {
                         // P = 2^(s*c - lse2), dS = P * (dP*scale - delta*scale); fp32, rounded once each
 #pragma unroll
                         for (int g4 = 0; g4 < 4; ++g4) {             // four columns at a time
@@ -440,11 +458,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                                 const float g0 = fmaf(__uint_as_float(dp[j]), P.scale, nd[2 * h2]);
                                 const float g1 = fmaf(__uint_as_float(dp[j + 1]), P.scale, nd[2 * h2 + 1]);
                                 uint32_t dd = cvt_pack<BF16>(p0 * g0, p1 * g1);
-                                if (kInner > 0) dd = dd & colmask[pi % kPairs] & rowmask[pi / kPairs];
+                                if (separable) dd = dd & colmask[pi % kPairs] & rowmask[pi / kPairs];
                                 pk_ds[pl] = dd;
                                 if (kKeySide) {
                                     uint32_t pp = cvt_pack<BF16>(p0, p1);
-                                    if (kInner > 0) pp = pp & colmask[pi % kPairs] & rowmask[pi / kPairs];
+                                    if (separable) pp = pp & colmask[pi % kPairs] & rowmask[pi / kPairs];
                                     pk_p[pl] = pp;
                                 }
                             }
@@ -562,8 +580,8 @@ __global__ void tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t
 }
 
 template <int DH, bool BF16>
-int launch_bwd(const Geo& g, const Plan& plan, const void* q, const void* k, const void* v,
-               const void* out, const void* lse, const void* dout, const void* dlse, void* dq, void* dk,
+int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const void* k, const void* v,
+               const void* ek, const void* ev, void* dek, void* dev, const void* out, const void* lse, const void* dout, const void* dlse, void* dq, void* dk,
                void* dv, float* delta, cudaStream_t s)
 {
     const TcParams& p = plan.p;
@@ -573,7 +591,7 @@ int launch_bwd(const Geo& g, const Plan& plan, const void* q, const void* k, con
     tc_count_launch();
 
     const long long dos[3] = {g.ltot * g.Hq * g.Dv, (long long)g.Hq * g.Dv, g.Dv};   // dout is contiguous
-    CUtensorMap q_tile, do_tile, k_chunk, v_chunk, k_tile, v_tile, q_chunk, do_chunk;
+    CUtensorMap q_tile, do_tile, k_chunk, v_chunk, k_tile, v_tile, q_chunk, do_chunk, ek_chunk, ev_chunk;
     const bool bf = BF16;
     using Smem = SmemB<DH>;
     if (!encode_map(&q_tile, q, bf, p, g.Hq, DH, g.qs, plan.box_q) ||
@@ -584,6 +602,10 @@ int launch_bwd(const Geo& g, const Plan& plan, const void* q, const void* k, con
         !encode_map(&v_tile, v, bf, p, g.Hkv, DH, g.vs, plan.box_q) ||
         !encode_map(&q_chunk, q, bf, p, g.Hq, DH, g.qs, plan.box_kv) ||
         !encode_map(&do_chunk, dout, bf, p, g.Hq, DH, dos, plan.box_kv))
+        return -2;
+    ek_chunk = k_chunk; ev_chunk = v_chunk;      // placeholders when there are no additional tokens
+    if (g.n_extra > 0 && (!encode_extra_map(&ek_chunk, ek, bf, g.B, g.n_extra, g.Hkv, DH, kCols) ||
+                          !encode_extra_map(&ev_chunk, ev, bf, g.B, g.n_extra, g.Hkv, DH, kCols)))
         return -2;
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= p.dil[a];
@@ -598,16 +620,19 @@ int launch_bwd(const Geo& g, const Plan& plan, const void* q, const void* k, con
             attr_done = true;
         }
         tc_bwd_kernel<DH, BF16, false, kInner><<<grid_q, kThreads, Smem::kTotal, s>>>(
-            q_tile, do_tile, k_chunk, v_chunk, p, (const float*)lse, delta, (uint16_t*)dq, nullptr);
+            q_tile, do_tile, k_chunk, v_chunk, ek_chunk, ev_chunk, p, (const float*)lse, delta, (uint16_t*)dq, nullptr);
         tc_count_launch();
         tc_bwd_kernel<DH, BF16, true, kInner><<<grid_k, kThreads, Smem::kTotal, s>>>(
-            k_tile, v_tile, q_chunk, do_chunk, p, (const float*)lse, delta, (uint16_t*)dk, (uint16_t*)dv);
+            k_tile, v_tile, q_chunk, do_chunk, ek_chunk, ev_chunk, p, (const float*)lse, delta, (uint16_t*)dk, (uint16_t*)dv);
         tc_count_launch();
     };
     if (p.cb[2] == 16) launch(std::integral_constant<int, 16>{});
     else if (p.cb[2] == 32) launch(std::integral_constant<int, 32>{});
     else launch(std::integral_constant<int, 0>{});
-    const cudaError_t err = cudaGetLastError();
+    cudaError_t err = cudaGetLastError();
+    // The additional tokens' own gradients sum over every query of the sample: SIMT kernel.
+    if (err == cudaSuccess && g.n_extra > 0)
+        err = simt_fused_bwd_extra(dtype, g, q, ek, ev, lse, delta, dout, dek, dev, s);
     return err == cudaSuccess ? 0 : (int)err;
 }
 
@@ -617,8 +642,8 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
                  const void* ev, const void* out, const void* lse, const void* dout, const void* dlse,
                  void* dq, void* dk, void* dv, void* dek, void* dev, void* workspace, cudaStream_t s)
 {
-    (void)ek; (void)ev; (void)dek; (void)dev;
     if (!tc_eligible(dtype, g, q, k, v)) return -2;
+    if (g.n_extra > 0 && ((reinterpret_cast<uintptr_t>(ek) | reinterpret_cast<uintptr_t>(ev)) & 15u)) return -2;
     if (reinterpret_cast<uintptr_t>(dout) & 15u) return -2;
     Plan plan;
     if (!make_plan(g, plan, kCols)) return -2;
@@ -629,10 +654,10 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     if (g.Hq > 65535 || g.B > 65535) return -2;
     float* delta = reinterpret_cast<float*>(workspace);
     if (g.D == 64)
-        return dtype == 2 ? launch_bwd<64, true>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s)
-                          : launch_bwd<64, false>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s);
-    return dtype == 2 ? launch_bwd<128, true>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s)
-                      : launch_bwd<128, false>(g, plan, q, k, v, out, lse, dout, dlse, dq, dk, dv, delta, s);
+        return dtype == 2 ? launch_bwd<64, true>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s)
+                          : launch_bwd<64, false>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s);
+    return dtype == 2 ? launch_bwd<128, true>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s)
+                      : launch_bwd<128, false>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s);
 }
 
 size_t tc_bwd_workspace_bytes(int, const Geo&) { return 0; }

@@ -70,7 +70,8 @@ __device__ __forceinline__ int tc_window_start(int p, int L, int K) { return win
 template <int DH, bool BF16, int kInner>
 __global__ void __launch_bounds__(kThreads, (DH == 64 ? 2 : 1))
 tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ TcParams P,
+              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmEK,
+              const __grid_constant__ CUtensorMap tmEV, const __grid_constant__ TcParams P,
               uint16_t* __restrict__ out, float* __restrict__ lse)
 {
     using SM = SmemMap<DH>;
@@ -87,7 +88,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     // ---- CTA geometry -------------------------------------------------------
     int rg[3], origin[3], Lp[3], lo[3], nc[3];
     const bool cta_active = cta_geometry(P, blockIdx.x, b, rg, origin, Lp);
-    int nch = 1;
+    int nnb = 1;                             // chunks of the neighbourhood box
     if (cta_active) {
 #pragma unroll
         for (int a = 0; a < 3; ++a) {
@@ -95,9 +96,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             lo[a] = P.causal[a] ? origin[a] - (P.K[a] - 1) : tc_window_start(origin[a], Lp[a], P.K[a]);
             const int hi = P.causal[a] ? last : tc_window_start(last, Lp[a], P.K[a]) + P.K[a] - 1;
             nc[a] = chunks_along(P, a, hi - lo[a] + 1);       // chunks this tile really needs
-            nch *= nc[a];
+            nnb *= nc[a];
         }
     }
+    const int nch = nnb + ((P.n_extra + kChunk - 1) >> 7);   // then the additional tokens, 128 per chunk
 
     if (!cta_active) {                       // nothing to attend: padding rows are zero
         if (warp < 8) {
@@ -139,19 +141,28 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     int ld[3] = {0, 0, 0};                       // chunk counters of the next load
     int loaded = 0;
     auto issue_kv = [&]() {
-        int X[3];
-#pragma unroll
-        for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (lo[a] + ld[a] * P.cb[a]);
         const int s = loaded % kStages;
         const uint32_t bar = bar_kv + 8 * s;
         mbar_expect_tx(bar, 2 * SM::kTile);
+        if (loaded < nnb) {
+            int X[3];
 #pragma unroll
-        for (int hf = 0; hf < SM::kHalves; ++hf) {
-            tma_load_5d(sbase + SM::kK + s * SM::kTile + hf * SM::kHalf, &tmK, bar, hk * DH + 64 * hf, X[2], X[1], X[0], b);
-            tma_load_5d(sbase + SM::kV + s * SM::kTile + hf * SM::kHalf, &tmV, bar, hk * DH + 64 * hf, X[2], X[1], X[0], b);
+            for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (lo[a] + ld[a] * P.cb[a]);
+#pragma unroll
+            for (int hf = 0; hf < SM::kHalves; ++hf) {
+                tma_load_5d(sbase + SM::kK + s * SM::kTile + hf * SM::kHalf, &tmK, bar, hk * DH + 64 * hf, X[2], X[1], X[0], b);
+                tma_load_5d(sbase + SM::kV + s * SM::kTile + hf * SM::kHalf, &tmV, bar, hk * DH + 64 * hf, X[2], X[1], X[0], b);
+            }
+            if (++ld[2] == nc[2]) { ld[2] = 0; if (++ld[1] == nc[1]) { ld[1] = 0; ++ld[0]; } }
+        } else {                                 // additional tokens (rows past n_extra are zero-filled)
+            const int e0 = (loaded - nnb) * kChunk;
+#pragma unroll
+            for (int hf = 0; hf < SM::kHalves; ++hf) {
+                tma_load_5d(sbase + SM::kK + s * SM::kTile + hf * SM::kHalf, &tmEK, bar, hk * DH + 64 * hf, e0, 0, 0, b);
+                tma_load_5d(sbase + SM::kV + s * SM::kTile + hf * SM::kHalf, &tmEV, bar, hk * DH + 64 * hf, e0, 0, 0, b);
+            }
         }
         ++loaded;
-        if (++ld[2] == nc[2]) { ld[2] = 0; if (++ld[1] == nc[1]) { ld[1] = 0; ++ld[0]; } }
     };
     long long tw0 = 0, tw1 = 0, tw2 = 0, tw3 = 0;
     if (warp == 8) {
@@ -290,7 +301,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         for (int c = 0; c < nch; ++c) {
             // ---- validity words of this thread's two 32-column pieces ----
             uint32_t words[2];
-            if (kInner > 0) {
+            if (c >= nnb) {                       // additional tokens: every live row sees the first n_extra columns
+#pragma unroll
+                for (int pc = 0; pc < 2; ++pc)
+                    words[pc] = valid_q ? low_bits(P.n_extra - ((c - nnb) * kChunk + 64 * team + 32 * pc)) : 0u;
+            } else if (kInner > 0) {
                 if (ci[2] != cached_c2) {
                     cached_c2 = ci[2];
                     int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
@@ -452,15 +467,19 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const void* v, const void* ek,
                  const void* ev, void* out, void* lse, cudaStream_t s)
 {
-    (void)ek; (void)ev;
     if (!tc_eligible(dtype, g, q, k, v)) return -2;
+    if (g.n_extra > 0 && ((reinterpret_cast<uintptr_t>(ek) | reinterpret_cast<uintptr_t>(ev)) & 15u)) return -2;
     Plan plan;
     if (!make_plan(g, plan)) return -2;
     const bool bf16 = dtype == 2;
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mek, mev;
     if (!encode_map(&mq, q, bf16, plan.p, g.Hq, g.D, g.qs, plan.box_q) ||
         !encode_map(&mk, k, bf16, plan.p, g.Hkv, g.D, g.ks, plan.box_kv) ||
         !encode_map(&mv, v, bf16, plan.p, g.Hkv, g.Dv, g.vs, plan.box_kv))
+        return -2;
+    mek = mk; mev = mv;                      // placeholders when there are no additional tokens
+    if (g.n_extra > 0 && (!encode_extra_map(&mek, ek, bf16, g.B, g.n_extra, g.Hkv, g.D, kChunk) ||
+                          !encode_extra_map(&mev, ev, bf16, g.B, g.n_extra, g.Hkv, g.Dv, kChunk)))
         return -2;
     plan.p.status = status_ptr();
     plan.p.trace = trace_ptr();
@@ -481,7 +500,7 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
             cudaFuncSetAttribute(tc_fwd_kernel<kDh, kBf, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
             once = true;
         }
-        tc_fwd_kernel<kDh, kBf, kInner><<<grid, kThreads, SM::kTotal, s>>>(mq, mk, mv, plan.p, (uint16_t*)out, (float*)lse);
+        tc_fwd_kernel<kDh, kBf, kInner><<<grid, kThreads, SM::kTotal, s>>>(mq, mk, mv, mek, mev, plan.p, (uint16_t*)out, (float*)lse);
     };
     auto by_inner = [&](auto dh, auto bf) {
         if (plan.p.cb[2] == 16) launch(dh, bf, std::integral_constant<int, 16>{});

@@ -24,6 +24,7 @@ struct TcParams {
     int tile1_log, tile2_log;            // tile extents are powers of two
     unsigned ntile_mul[3], dil_mul[3];   // ceil(2^32 / d) for d >= 2, 0 for d == 1 (see fast_div)
     int rank, B, Hq, Hkv, group, ntiles, nchunks;
+    int n_extra;           // additional key/value tokens every query attends to (0 = none)
     float scale_log2, scale;
     const int* extents;
     long long ltot;
@@ -237,6 +238,7 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk)
         if (blocks * dmax >= (1ll << 32) || (long long)(p.L[0] + p.L[1] + p.L[2] + dmax) * dmax >= (1ll << 32)) return false;
     }
     p.rank = g.rank; p.B = g.B; p.Hq = g.Hq; p.Hkv = g.Hkv; p.group = g.group;
+    p.n_extra = g.n_extra;
     p.scale_log2 = (float)(g.scale * 1.4426950408889634);
     p.scale = (float)g.scale;
     p.extents = g.extents;
@@ -263,11 +265,33 @@ inline bool encode_map(CUtensorMap* map, const void* base, bool bf16, const TcPa
     return r == CUDA_SUCCESS;
 }
 
+// Map over the additional tokens [B, Ne, heads, dh]: same 5-D form, one spatial axis of extent Ne.
+inline bool encode_extra_map(CUtensorMap* map, const void* base, bool bf16, int B, int n_extra, int heads,
+                             int dh, int box_cols)
+{
+    EncodeFn enc = get_encode();
+    if (!enc || n_extra <= 0) return false;
+    const cuuint64_t tok = (cuuint64_t)heads * dh * 2;
+    cuuint64_t dims[5] = {(cuuint64_t)heads * dh, (cuuint64_t)n_extra, 1, 1, (cuuint64_t)B};
+    cuuint64_t gstr[4] = {tok, tok * n_extra, tok * n_extra, tok * n_extra};
+    cuuint32_t bx[5] = {64, (cuuint32_t)box_cols, 1, 1, 1};
+    cuuint32_t es[5] = {1, 1, 1, 1, 1};
+    return enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
+               const_cast<void*>(base), dims, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Bits [0, n) of a 32-bit word (n may be <= 0 or >= 32).
+__device__ __forceinline__ uint32_t low_bits(int n)
+{
+    return n <= 0 ? 0u : (n >= 32 ? 0xffffffffu : ((1u << n) - 1u));
+}
+
 inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, const void* v)
 {
     if (dtype != 1 && dtype != 2) return false;                 // f16 / bf16
     if ((g.D != 64 && g.D != 128) || g.Dv != g.D) return false;
-    if (g.n_extra != 0) return false;
     if (!(g.scale > 0.0)) return false;
     for (int a = 0; a < g.rank; ++a) {
         if (g.st[a] != 1) return false;

@@ -97,3 +97,45 @@ def test_tc_backward_matches_simt(case, dtype):
         err = (a.float() - r.float()).abs().max().item()
         scale = max(1.0, r.float().abs().max().item())
         assert err <= 2e-2 * scale, f"{name} differs by {err} (scale {scale})"
+
+
+EXTRA_CASES = [
+    # spatial, B, Hq, Hkv, D, kernel, n_extra, extents
+    ((400,), 2, 4, 1, 128, (63,), 16, [[400], [170]]),
+    ((20, 24), 2, 2, 2, 64, (7, 7), 3, None),
+    ((300,), 1, 2, 2, 64, (31,), 130, None),          # more than one chunk of additional tokens
+    ((4, 10, 12), 1, 2, 1, 64, (3, 5, 5), 20, None),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", EXTRA_CASES, ids=lambda c: "x".join(map(str, c[0])) + f"_e{c[6]}_h{c[4]}")
+def test_tc_additional_tokens_match_simt(case, dtype):
+    spatial, B, Hq, Hkv, D, ks, n_extra, extents = case
+    rank = len(spatial)
+    g = torch.Generator(device="cpu").manual_seed(23)
+    mk = lambda *shape: torch.randn(shape, generator=g).to(dtype).cuda()
+    q, k, v = mk(B, *spatial, Hq, D), mk(B, *spatial, Hkv, D), mk(B, *spatial, Hkv, D)
+    ek, ev, go = mk(B, n_extra, Hkv, D), mk(B, n_extra, Hkv, D), mk(B, *spatial, Hq, D)
+    ext = None if extents is None else torch.tensor(extents, dtype=torch.int32).cuda()
+    geo = (ks, (1,) * rank, (1,) * rank, (False,) * rank, D ** -0.5)
+    kw = dict(extra_k=ek, extra_v=ev, extents=ext)
+    try:
+        _cabi.set_force("simt")
+        ref_out, ref_lse = _backend.fused_forward(q, k, v, *geo, **kw)
+        ref = _backend.fused_backward(q, k, v, ref_out, ref_lse, go, *geo, **kw)
+        _cabi.set_force("tc")
+        out, lse = _backend.fused_forward(q, k, v, *geo, **kw)
+        assert _cabi.last_path() == "tcgen05"
+        got = _backend.fused_backward(q, k, v, ref_out, ref_lse, go, *geo, **kw)
+        assert _cabi.last_path() == "tcgen05"
+    finally:
+        _cabi.set_force(None)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    assert (out.float() - ref_out.float()).abs().max().item() <= 1.6e-2
+    assert (lse - ref_lse).abs().max().item() <= 2e-3
+    for name, a, r in zip(("dq", "dk", "dv", "dek", "dev"), got, ref):
+        err = (a.float() - r.float()).abs().max().item()
+        scale = max(1.0, r.float().abs().max().item())
+        assert err <= 2e-2 * scale, f"{name} differs by {err} (scale {scale})"
