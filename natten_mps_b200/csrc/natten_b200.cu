@@ -109,9 +109,10 @@ size_t natten_workspace_bytes(const natten_params_t* p, int op)
     Geo g;
     if (make_geo(p, g)) return 0;
     if (op == NATTEN_OP_FUSED_BWD) {
-        // delta = rowsum(out * dout), one accumulator per (batch, query, head)
-        const size_t acc = p->dtype == NATTEN_F64 ? 8 : 4;
-        size_t bytes = (size_t)g.B * (size_t)g.otot * (size_t)g.Hq * acc;
+        // delta = rowsum(out * dout), one accumulator per (batch, query, head); then the
+        // partial sums of the additional tokens' gradients
+        size_t bytes = simt_delta_bytes(g, p->dtype == NATTEN_F64 ? 8 : 4);
+        bytes += simt_extra_partial_bytes(p->dtype, g);
         bytes += tc_bwd_workspace_bytes(p->dtype, g);
         return (bytes + 255) & ~(size_t)255;
     }

@@ -15,8 +15,11 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>
+#include <type_traits>
 
 namespace natten {
+
+size_t simt_delta_bytes(const Geo& g, size_t acc_size);
 
 namespace {
 
@@ -536,6 +539,121 @@ fused_bwd_extra_kernel(const __grid_constant__ Geo g, const T* __restrict__ q,
     }
 }
 
+// Gradients of the additional tokens, fast path (float accumulation, head dims <= 128).
+// A block owns a contiguous segment of (query, head-of-group) pairs of one (batch, kv head) and
+// up to kExtraGroup tokens; every query row is read once and kept in registers while the
+// tokens' rows sit in shared memory.  Blocks write partial sums that a second kernel adds in
+// a fixed order (deterministic, no atomics).
+constexpr int kExtraGroup = 16;
+constexpr int kExtraSegRows = 2048;
+
+template <typename T, int ND>
+__global__ void __launch_bounds__(kWarps * 32)
+extra_grad_partial_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T* __restrict__ ek,
+                          const T* __restrict__ ev, const float* __restrict__ lse,
+                          const float* __restrict__ delta, const T* __restrict__ dout,
+                          const float* __restrict__ dlse, float* __restrict__ partial, int e0, int ne)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* eks = reinterpret_cast<float*>(smem_raw);           // [ne][D]
+    float* evs = eks + kExtraGroup * g.D;                      // [ne][Dv]
+    float* red = evs + kExtraGroup * g.Dv;                     // [ne][D + Dv]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int W = g.D + g.Dv;
+    for (int i = threadIdx.x; i < ne * g.D; i += blockDim.x)
+        eks[i] = to_acc(ek[(((long long)b * g.n_extra + e0 + i / g.D) * g.Hkv + hk) * g.D + i % g.D]);
+    for (int i = threadIdx.x; i < ne * g.Dv; i += blockDim.x)
+        evs[i] = to_acc(ev[(((long long)b * g.n_extra + e0 + i / g.Dv) * g.Hkv + hk) * g.Dv + i % g.Dv]);
+    for (int i = threadIdx.x; i < kExtraGroup * W; i += blockDim.x) red[i] = 0.f;
+    __syncthreads();
+
+    float acck[kExtraGroup][ND], accv[kExtraGroup][ND];
+#pragma unroll
+    for (int e = 0; e < kExtraGroup; ++e)
+#pragma unroll
+        for (int i = 0; i < ND; ++i) { acck[e][i] = 0.f; accv[e][i] = 0.f; }
+    const float scale = (float)g.scale;
+    const long long total = g.otot * g.group;
+    long long end = (long long)(seg + 1) * kExtraSegRows;
+    if (end > total) end = total;
+    for (long long cnd = (long long)seg * kExtraSegRows + warp; cnd < end; cnd += kWarps) {
+        const int gi = (int)(cnd / g.otot);
+        const int h = hk * g.group + gi;
+        QueryCtx c;
+        decode_query(g, ((long long)b * g.otot + cnd % g.otot) * g.Hq + h, c);
+        if (!c.inside) continue;                               // warp-uniform
+        const T* qrow = q + c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
+        const T* dorow = dout + c.row * g.Dv;
+        float qr[ND], dor[ND];
+#pragma unroll
+        for (int i = 0; i < ND; ++i) {
+            const int d = lane + 32 * i;
+            qr[i] = d < g.D ? to_acc(qrow[d]) : 0.f;
+            dor[i] = d < g.Dv ? to_acc(dorow[d]) : 0.f;
+        }
+        const float lse_i = lse[c.row];
+        const float dl = delta[c.row] - (dlse ? dlse[c.row] : 0.f);
+#pragma unroll
+        for (int e = 0; e < kExtraGroup; ++e) {
+            if (e < ne) {
+                float sd = 0.f, dp = 0.f;
+#pragma unroll
+                for (int i = 0; i < ND; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < g.D) sd += qr[i] * eks[e * g.D + d];
+                    if (d < g.Dv) dp += dor[i] * evs[e * g.Dv + d];
+                }
+                sd = warp_sum(sd);
+                dp = warp_sum(dp);
+                const float p = expf(sd * scale - lse_i);
+                const float ds = p * (dp - dl) * scale;
+#pragma unroll
+                for (int i = 0; i < ND; ++i) { acck[e][i] += ds * qr[i]; accv[e][i] += p * dor[i]; }
+            }
+        }
+    }
+    // warps add into the shared buffer one after the other (fixed order)
+    for (int w = 0; w < kWarps; ++w) {
+        if (warp == w) {
+#pragma unroll
+            for (int e = 0; e < kExtraGroup; ++e) {
+                if (e < ne) {
+#pragma unroll
+                    for (int i = 0; i < ND; ++i) {
+                        const int d = lane + 32 * i;
+                        if (d < g.D) red[e * W + d] += acck[e][i];
+                        if (d < g.Dv) red[e * W + g.D + d] += accv[e][i];
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    float* dst = partial + ((((long long)b * g.Hkv + hk) * gridDim.x + seg) * kExtraGroup) * W;
+    for (int i = threadIdx.x; i < ne * W; i += blockDim.x) dst[i] = red[i];
+}
+
+template <typename T>
+__global__ void extra_grad_reduce_kernel(const __grid_constant__ Geo g, const float* __restrict__ partial,
+                                         int nseg, int e0, int ne, T* __restrict__ dek, T* __restrict__ dev)
+{
+    const int W = g.D + g.Dv;
+    const long long n = (long long)g.B * g.Hkv * ne * W;
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n) return;
+    const int d = (int)(t % W);
+    const int e = (int)((t / W) % ne);
+    const long long bh = t / ((long long)W * ne);              // b * Hkv + hk
+    float acc = 0.f;
+    for (int sgm = 0; sgm < nseg; ++sgm) acc += partial[((bh * nseg + sgm) * kExtraGroup + e) * W + d];
+    const int hk = (int)(bh % g.Hkv);
+    const long long b = bh / g.Hkv;
+    const long long tok = (b * g.n_extra + e0 + e) * g.Hkv + hk;
+    if (d < g.D) dek[tok * g.D + d] = from_acc<T, float>(acc);
+    else dev[tok * g.Dv + (d - g.D)] = from_acc<T, float>(acc);
+}
+
 // ---------------------------------------------------------------------------
 // Split QK
 // ---------------------------------------------------------------------------
@@ -730,6 +848,44 @@ inline unsigned grid_for(long long rows) { return (unsigned)((rows + kWarps - 1)
         else { constexpr int NAME = 8; __VA_ARGS__; }                       \
     } while (0)
 
+
+inline int extra_segments(const Geo& g) { return (int)((g.otot * g.group + kExtraSegRows - 1) / kExtraSegRows); }
+
+// Fast path for the additional tokens' gradients; returns false when it does not apply.
+template <typename T>
+bool launch_extra_fast(const Geo& g, const void* q, const void* ek, const void* ev, const void* lse,
+                       const void* delta, const void* dout, const void* dlse, void* dek, void* dev,
+                       void* partial, cudaStream_t s)
+{
+    if constexpr (!std::is_same<typename AccOf<T>::type, float>::value) {
+        return false;
+    } else {
+    if (g.D > 128 || g.Dv > 128 || !partial) return false;
+    const int nseg = extra_segments(g);
+    const int W = g.D + g.Dv;
+    const size_t smem = (size_t)kExtraGroup * 2 * W * sizeof(float);
+    for (int e0 = 0; e0 < g.n_extra; e0 += kExtraGroup) {
+        const int ne = g.n_extra - e0 < kExtraGroup ? g.n_extra - e0 : kExtraGroup;
+        const dim3 grid((unsigned)nseg, (unsigned)g.Hkv, (unsigned)g.B);
+        const int dmax = g.D > g.Dv ? g.D : g.Dv;
+        if (dmax <= 32)
+            extra_grad_partial_kernel<T, 1><<<grid, kWarps * 32, smem, s>>>(g, (const T*)q, (const T*)ek, (const T*)ev,
+                (const float*)lse, (const float*)delta, (const T*)dout, (const float*)dlse, (float*)partial, e0, ne);
+        else if (dmax <= 64)
+            extra_grad_partial_kernel<T, 2><<<grid, kWarps * 32, smem, s>>>(g, (const T*)q, (const T*)ek, (const T*)ev,
+                (const float*)lse, (const float*)delta, (const T*)dout, (const float*)dlse, (float*)partial, e0, ne);
+        else
+            extra_grad_partial_kernel<T, 4><<<grid, kWarps * 32, smem, s>>>(g, (const T*)q, (const T*)ek, (const T*)ev,
+                (const float*)lse, (const float*)delta, (const T*)dout, (const float*)dlse, (float*)partial, e0, ne);
+        const long long n = (long long)g.B * g.Hkv * ne * W;
+        extra_grad_reduce_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(g, (const float*)partial, nseg, e0, ne,
+                                                                            (T*)dek, (T*)dev);
+        g_launches += 2;
+    }
+    return true;
+    }
+}
+
 template <typename T>
 cudaError_t fused_fwd_t(const Geo& g, const void* q, const void* k, const void* v, const void* ek,
                         const void* ev, void* out, void* lse, cudaStream_t s)
@@ -782,14 +938,17 @@ cudaError_t fused_bwd_t(const Geo& g, const void* q, const void* k, const void* 
         ++g_launches;
     }
     if (g.n_extra > 0 && g.B > 0) {
-        const size_t smem = (size_t)(kWarps + 1) * (g.D + g.Dv) * sizeof(A);
-        const int dmax = g.D > g.Dv ? g.D : g.Dv;
-        const unsigned blocks = (unsigned)((long long)g.B * g.n_extra * g.Hkv);
-        NATTEN_DISPATCH_N(dmax, ND,
-            fused_bwd_extra_kernel<T, ND, ND><<<blocks, kWarps * 32, smem, s>>>(
-                g, (const T*)q, (const T*)ek, (const T*)ev, (const A*)lse, delta, (const T*)dout,
-                (const A*)dlse, (T*)dek, (T*)dev));
-        ++g_launches;
+        void* partial = static_cast<unsigned char*>(workspace) + simt_delta_bytes(g, sizeof(A));
+        if (!launch_extra_fast<T>(g, q, ek, ev, lse, delta, dout, dlse, dek, dev, partial, s)) {
+            const size_t smem = (size_t)(kWarps + 1) * (g.D + g.Dv) * sizeof(A);
+            const int dmax = g.D > g.Dv ? g.D : g.Dv;
+            const unsigned blocks = (unsigned)((long long)g.B * g.n_extra * g.Hkv);
+            NATTEN_DISPATCH_N(dmax, ND,
+                fused_bwd_extra_kernel<T, ND, ND><<<blocks, kWarps * 32, smem, s>>>(
+                    g, (const T*)q, (const T*)ek, (const T*)ev, (const A*)lse, delta, (const T*)dout,
+                    (const A*)dlse, (T*)dek, (T*)dev));
+            ++g_launches;
+        }
     }
     return cudaGetLastError();
 }
@@ -900,10 +1059,12 @@ cudaError_t simt_fused_bwd(int dtype, const Geo& g, const void* q, const void* k
 // covers dq/dk/dv).  `delta` must already hold rowsum(out*dout) - dlse.
 template <typename T>
 cudaError_t fused_bwd_extra_t(const Geo& g, const void* q, const void* ek, const void* ev, const void* lse,
-                              const void* delta, const void* dout, void* dek, void* dev, cudaStream_t s)
+                              const void* delta, const void* dout, void* dek, void* dev, void* partial,
+                              cudaStream_t s)
 {
     using A = typename AccOf<T>::type;
     if (g.n_extra <= 0 || g.B <= 0) return cudaSuccess;
+    if (launch_extra_fast<T>(g, q, ek, ev, lse, delta, dout, nullptr, dek, dev, partial, s)) return cudaGetLastError();
     const size_t smem = (size_t)(kWarps + 1) * (g.D + g.Dv) * sizeof(A);
     const int dmax = g.D > g.Dv ? g.D : g.Dv;
     const unsigned blocks = (unsigned)((long long)g.B * g.n_extra * g.Hkv);
@@ -917,9 +1078,22 @@ cudaError_t fused_bwd_extra_t(const Geo& g, const void* q, const void* ek, const
 
 cudaError_t simt_fused_bwd_extra(int dtype, const Geo& g, const void* q, const void* ek, const void* ev,
                                  const void* lse, const void* delta, const void* dout, void* dek, void* dev,
-                                 cudaStream_t s)
+                                 void* partial, cudaStream_t s)
 {
-    NATTEN_BY_DTYPE(dtype, fused_bwd_extra_t<T>(g, q, ek, ev, lse, delta, dout, dek, dev, s));
+    NATTEN_BY_DTYPE(dtype, fused_bwd_extra_t<T>(g, q, ek, ev, lse, delta, dout, dek, dev, partial, s));
+}
+
+size_t simt_delta_bytes(const Geo& g, size_t acc_size)
+{
+    const size_t bytes = (size_t)g.B * (size_t)g.otot * (size_t)g.Hq * acc_size;
+    return (bytes + 255) & ~(size_t)255;
+}
+
+size_t simt_extra_partial_bytes(int dtype, const Geo& g)
+{
+    if (g.n_extra <= 0 || dtype == 3 || g.D > 128 || g.Dv > 128) return 0;
+    const size_t bytes = (size_t)g.B * g.Hkv * (size_t)extra_segments(g) * kExtraGroup * (g.D + g.Dv) * sizeof(float);
+    return (bytes + 255) & ~(size_t)255;
 }
 
 cudaError_t simt_qk_fwd(int dtype, const Geo& g, const void* q, const void* k, void* logits, cudaStream_t s)

@@ -12,7 +12,11 @@ cudaError_t simt_fused_bwd(int dtype, const Geo& g, const void* q, const void* k
                            void* dek, void* dev, void* workspace, cudaStream_t s);
 cudaError_t simt_fused_bwd_extra(int dtype, const Geo& g, const void* q, const void* ek, const void* ev,
                                  const void* lse, const void* delta, const void* dout, void* dek, void* dev,
-                                 cudaStream_t s);
+                                 void* partial, cudaStream_t s);
+// Workspace layout of the fused backward: [delta, one accumulator per (batch, query, head)]
+// [partial sums of the additional tokens' gradients].
+size_t simt_delta_bytes(const Geo& g, size_t acc_size);
+size_t simt_extra_partial_bytes(int dtype, const Geo& g);
 cudaError_t simt_qk_fwd(int dtype, const Geo& g, const void* q, const void* k, void* logits, cudaStream_t s);
 cudaError_t simt_qk_bwd(int dtype, const Geo& g, const void* q, const void* k, const void* dlogits,
                         void* dq, void* dk, cudaStream_t s);

@@ -632,7 +632,8 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
     cudaError_t err = cudaGetLastError();
     // The additional tokens' own gradients sum over every query of the sample: SIMT kernel.
     if (err == cudaSuccess && g.n_extra > 0)
-        err = simt_fused_bwd_extra(dtype, g, q, ek, ev, lse, delta, dout, dek, dev, s);
+        err = simt_fused_bwd_extra(dtype, g, q, ek, ev, lse, delta, dout, dek, dev,
+                                   reinterpret_cast<unsigned char*>(delta) + simt_delta_bytes(g, 4), s);
     return err == cudaSuccess ? 0 : (int)err;
 }
 
