@@ -73,45 +73,57 @@ def algorithmic(w, batch):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons every 100 ms with one streaming nvidia-smi
+    process for as long as the timed sections run."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+        self.index, self.rows, self._proc, self._t = index, [], None, None
 
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                     "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                parts = [p.strip() for p in out.strip().split(",")]
-                if len(parts) >= 6:
-                    self.rows.append(parts)
-            except Exception:
-                pass
-            self._stop.wait(0.05)
+    def _pump(self):
+        for line in self._proc.stdout:
+            parts = [p.strip() for p in line.strip().split(",")]
+            if len(parts) >= 6:
+                self.rows.append(parts)
 
     def __enter__(self):
-        self._t = threading.Thread(target=self._run, daemon=True)
-        self._t.start()
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._t = threading.Thread(target=self._pump, daemon=True)
+            self._t.start()
+        except Exception:
+            self._proc = None
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        self._t.join(timeout=10)
+        if self._proc is not None:
+            self._proc.terminate()          # the exact process started above
+            try:
+                self._proc.wait(timeout=5)
+            except Exception:
+                self._proc.kill()
+            self._t.join(timeout=5)
 
     def summary(self):
         if not self.rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
-        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        num = lambda x: x.replace(".", "", 1).isdigit()
+        sm = [float(r[0]) for r in self.rows if num(r[0])]
+        mx = [float(r[1]) for r in self.rows if num(r[1])]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(self.rows)}
+
+
+# DRAM bytes (read + write) the backward / forward kernels move per launch set at config 2, batch 8,
+# from the committed ncu capture (profiles/c2_na2d_7x7_bf16_tc_kernels_ncu_full.md); scales with batch.
+NCU_TRAFFIC_C2 = {"backward": 394.8e6, "forward": 116.1e6}
 
 
 def measured_peaks():
@@ -255,18 +267,21 @@ def run_ours(args, w):
     # ---- device-resident timing: K steps between two events ------------------
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = _cabi.launch_count()
-    with ClockSampler(local) as clocks:
-        sync_all()
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        sync_all()
+    clocks = ClockSampler(local)
+    clocks.__enter__()
+    time.sleep(0.25)                                  # let the sampler take its first reading
+    sync_all()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync_all()
     launches = _cabi.launch_count() - launches0
     ms_total = e0.elapsed_time(e1)
     path = _cabi.last_path()
 
     if args.kernels_only:
+        clocks.__exit__(None, None, None)
         if rank == 0:
             print(json.dumps({"ms_per_step": ms_total / args.steps, "kernel_path": path,
                               "gpu_launches": launches}), flush=True)
@@ -310,6 +325,13 @@ def run_ours(args, w):
     e3.record()
     sync_all()
     e2e_ms = e2.elapsed_time(e3) / e2e_steps
+    # keep the GPU busy a little longer so that the clock record has samples under load
+    t_end = time.time() + 0.6
+    while time.time() < t_end:
+        for _ in range(20):
+            step()
+        torch.cuda.synchronize()
+    clocks.__exit__(None, None, None)
 
     # ---- reduce over ranks ---------------------------------------------------
     vals = torch.tensor([ms_total, e2e_ms, fwd_t, bwd_t], dtype=torch.float64, device=dev)
@@ -340,7 +362,8 @@ def run_ours(args, w):
                        "algorithmic_gb_per_step": (fwd_bytes + bwd_bytes) / 1e9},
             "fwd_ms": fwd_t, "bwd_ms": bwd_t,
             "roofline": {"bound": "hbm", "kernel": dominant[0], "achieved": achieved, "peak": hbm_peak,
-                         "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None,
+                         "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "traffic": (NCU_TRAFFIC_C2[dominant[0]] * B / 8 if args.workload == "c2" else None),
                          "peak_source": which,
                          "step_frac": ((fwd_bytes + bwd_bytes) / (ms_step * 1e-3) / 1e9) / hbm_peak,
                          "step_frac_nominal_8tbs": ((fwd_bytes + bwd_bytes) / (ms_step * 1e-3) / 1e9) / 8000.0},
@@ -360,7 +383,7 @@ def run_ours(args, w):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
