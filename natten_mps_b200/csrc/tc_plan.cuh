@@ -25,6 +25,9 @@ struct TcParams {
     unsigned ntile_mul[3], dil_mul[3];   // ceil(2^32 / d) for d >= 2, 0 for d == 1 (see fast_div)
     int rank, B, Hq, Hkv, group, ntiles, nchunks;
     int n_extra;           // additional key/value tokens every query attends to (0 = none)
+    int ngroups;           // dilation sub-grids = prod(dil)
+    unsigned per_head;     // tiles of one (batch, head) = ntiles * ngroups
+    unsigned work_q, work_kv;   // work items of a launch: per_head * B * Hq / Hkv
     float scale_log2, scale;
     const int* extents;
     long long ltot;
@@ -239,6 +242,12 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk)
     }
     p.rank = g.rank; p.B = g.B; p.Hq = g.Hq; p.Hkv = g.Hkv; p.group = g.group;
     p.n_extra = g.n_extra;
+    p.ngroups = 1;
+    for (int a = 0; a < 3; ++a) p.ngroups *= p.dil[a];
+    p.per_head = (unsigned)p.ntiles * (unsigned)p.ngroups;
+    if ((long long)p.per_head * g.B * g.Hq >= (1ll << 31)) return false;
+    p.work_q = p.per_head * (unsigned)g.B * (unsigned)g.Hq;
+    p.work_kv = p.per_head * (unsigned)g.B * (unsigned)g.Hkv;
     p.scale_log2 = (float)(g.scale * 1.4426950408889634);
     p.scale = (float)g.scale;
     p.extents = g.extents;
@@ -286,6 +295,19 @@ inline bool encode_extra_map(CUtensorMap* map, const void* base, bool bf16, int 
 __device__ __forceinline__ uint32_t low_bits(int n)
 {
     return n <= 0 ? 0u : (n >= 32 ? 0xffffffffu : ((1u << n) - 1u));
+}
+
+// CTAs of a persistent launch: `per_sm` per multiprocessor, never more than there is work.
+inline unsigned persistent_grid(unsigned work, int per_sm)
+{
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const unsigned cap = (unsigned)(sms * per_sm);
+    return work < cap ? work : cap;
 }
 
 inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, const void* v)
