@@ -58,9 +58,11 @@ struct SmemMap {
     static constexpr int kK = kQ + kQBufs * kTile;
     static constexpr int kV = kK + kKStages * kTile;
     static constexpr int kBar = kV + kVStages * kTile;
-    // barriers (q, k, v full/empty per buffer, s, sp, o), abort flag, TMEM slot: 192 bytes,
-    // then 512 bytes for the two column halves to exchange their row maxima
+    // barriers (q, k, v full/empty per buffer, s, sr, sp, o), abort flag, TMEM slot: 192 bytes,
+    // then 512 bytes for the two column halves to exchange their row maxima.
+    // Two CTAs share an SM only while kTotal + 1 KB (reserved per CTA) <= 114 KB.
     static constexpr int kTotal = kBar + 192 + 512;
+    static_assert(DH != 64 || 2 * (kTotal + 1024) <= 233472, "two CTAs per SM must fit");
     static constexpr uint32_t kTmemCols = DH == 64 ? 256 : 512;
     static constexpr uint32_t kColO = DH == 64 ? 192 : 256;
 };
@@ -121,7 +123,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const uint32_t sbase = smem_u32(smem);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::kBar + 176);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::kBar + 184);
-    uint16_t* xmax = reinterpret_cast<uint16_t*>(smem + SM::kBar + 192);      // [2][128] partial row maxima (bf16 bits)
+    uint16_t* xmax = reinterpret_cast<uint16_t*>(smem + SM::kBar + 192);      // [2 halves][128] row maxima (bf16 bits)
     const uint32_t bar_q_full = sbase + SM::kBar + 0;       // [2]
     const uint32_t bar_q_empty = sbase + SM::kBar + 16;     // [2]
     const uint32_t bar_k_full = sbase + SM::kBar + 32;      // [kKStages]
@@ -131,6 +133,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const uint32_t bar_s = sbase + SM::kBar + 112;
     const uint32_t bar_sp = sbase + SM::kBar + 120;
     const uint32_t bar_o = sbase + SM::kBar + 128;
+    const uint32_t bar_sr = sbase + SM::kBar + 136;         // every softmax thread holds S(c) in registers
 
     if (warp == 8) {
         if (lane == 0) {
@@ -142,6 +145,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             mbar_init(bar_s, 1);
             mbar_init(bar_sp, 256);
             mbar_init(bar_o, 1);
+            mbar_init(bar_sr, 256);
             mbar_init_fence();
             fence_async_smem();
         }
@@ -220,8 +224,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (lane == 0 && !*abort_flag) {
             constexpr uint32_t idesc_qk = instr_desc(BF16 ? 1 : 0, kChunk, 0, 0);
             constexpr uint32_t idesc_pv = instr_desc(BF16 ? 1 : 0, DH, 0, 1);
-            uint64_t dq0 = 0;                             // descriptor of the current tile's Q buffer
-            auto issue_qk = [&](unsigned g) {
+            auto issue_qk = [&](unsigned g, uint64_t dq0) {
                 const uint64_t dk0 = smem_desc(sbase + SM::kK + (g % kKStages) * SM::kTile, 16, 1024);
                 tc_fence_after();
 #pragma unroll
@@ -232,51 +235,71 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 mma_commit(bar_s);
                 mma_commit(bar_k_empty + 8 * (g % kKStages));        // the K stage can be reloaded
             };
-            auto issue_pv = [&](unsigned g) {
-                // V read MN-major: 16 key rows per k-step, the second 64-channel block sits kHalf bytes further
+            auto issue_pv = [&](unsigned g, bool accumulate) {
+                // V read MN-major: 16 key rows per k-step, the second 64-channel block sits kHalf bytes further.
+                // O stays in TMEM for the whole tile: every chunk after the first adds to it.
                 const uint64_t dv0 = smem_desc(sbase + SM::kV + (g % kVStages) * SM::kTile, SM::kHalf, 1024);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kChunk / 16; ++ks)
-                    mma_ts(tmem + kColO, tmem + kColP + 8 * ks, dv0 + 128 * ks, idesc_pv, ks > 0);
+                    mma_ts(tmem + kColO, tmem + kColP + 8 * ks, dv0 + 128 * ks, idesc_pv, accumulate || ks > 0);
                 mma_commit(bar_o);
                 mma_commit(bar_v_empty + 8 * (g % kVStages));        // the V stage can be reloaded
             };
+            // next work item of this CTA that has anything to attend
+            auto next_active = [&](unsigned w, FwdTile& X) {
+                for (; w < P.work_q; w += gridDim.x) {
+                    fwd_tile_setup(P, w, X);
+                    if (X.active) break;
+                }
+                return w;
+            };
             unsigned gc = 0, tq = 0;                      // chunks / tiles processed so far
             bool ok = true;
-            for (unsigned work = blockIdx.x; work < P.work_q && ok; work += gridDim.x) {
-                stamp(0);
-                FwdTile T;
-                fwd_tile_setup(P, work, T);
-                if (!T.active) continue;
+            // first scores of a tile: its queries and its first keys have landed
+            auto first_qk = [&](const FwdTile& X, unsigned t, unsigned g) {
+                const unsigned qb = t & 1;
+                ok = mbar_wait(bar_q_full + 8 * qb, (t >> 1) & 1, abort_flag) &&
+                     mbar_wait(bar_k_full + 8 * (g % kKStages), (g / kKStages) & 1, abort_flag);
+                if (!ok) return;
+                issue_qk(g, smem_desc(sbase + SM::kQ + qb * SM::kTile, 16, 1024));
+                if (X.nch == 1) mma_commit(bar_q_empty + 8 * qb);
+            };
+            FwdTile T, Tn;
+            unsigned work = next_active(blockIdx.x, T);
+            if (work < P.work_q) first_qk(T, 0, 0);
+            while (work < P.work_q && ok) {
                 stamp(0);
                 const unsigned qb = tq & 1;
-                ok = mbar_wait(bar_q_full + 8 * qb, (tq >> 1) & 1, abort_flag);
-                stamp(0);
-                dq0 = smem_desc(sbase + SM::kQ + qb * SM::kTile, 16, 1024);
-                ++tq;
+                const uint64_t dq0 = smem_desc(sbase + SM::kQ + qb * SM::kTile, 16, 1024);
+                unsigned wnext = P.work_q;
                 for (int c = 0; c < T.nch && ok; ++c, ++gc) {
-                    if (c == 0) {       // S is free: its previous contents were consumed before the last PV was issued
-                        ok = mbar_wait(bar_k_full + 8 * (gc % kKStages), (gc / kKStages) & 1, abort_flag);
-                        if (!ok) break;
-                        issue_qk(gc);
-                        if (T.nch == 1) mma_commit(bar_q_empty + 8 * qb);
-                        stamp(0);
-                    }
-                    ok = mbar_wait(bar_sp, gc & 1, abort_flag);          // S(c) consumed, P(c) stored
+                    const bool last = c + 1 == T.nch;
+                    if (last) wnext = next_active(work + gridDim.x, Tn);
+                    // S(c) sits in the threads' registers: the next scores may overwrite it while they work
+                    ok = mbar_wait(bar_sr, gc & 1, abort_flag);
                     if (!ok) break;
                     stamp(0);
-                    if (c + 1 < T.nch) {                                 // next scores first: the threads wait for them
+                    if (!last) {
                         ok = mbar_wait(bar_k_full + 8 * ((gc + 1) % kKStages), ((gc + 1) / kKStages) & 1, abort_flag);
                         if (!ok) break;
-                        issue_qk(gc + 1);
+                        issue_qk(gc + 1, dq0);
                         if (c + 2 == T.nch) mma_commit(bar_q_empty + 8 * qb);   // last QK of the tile: its Q buffer is free after it
+                    } else if (wnext < P.work_q) {
+                        first_qk(Tn, tq + 1, gc + 1);
+                        if (!ok) break;
                     }
+                    ok = mbar_wait(bar_sp, gc & 1, abort_flag);          // P(c) stored
+                    if (!ok) break;
+                    stamp(0);
                     ok = mbar_wait(bar_v_full + 8 * (gc % kVStages), (gc / kVStages) & 1, abort_flag);
                     if (!ok) break;
-                    issue_pv(gc);
+                    issue_pv(gc, c > 0);
                     stamp(0);
                 }
+                T = Tn;
+                work = wnext;
+                ++tq;
             }
         }
     } else {
@@ -323,10 +346,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 continue;
             }
 
+            // O accumulates in TMEM over the tile's chunks.  m is the stabiliser the stored
+            // probabilities use; it only moves (and O, l are rescaled) when a chunk's maximum
+            // exceeds it by more than 2^8, so probabilities stay below 256.
             float m = -INFINITY, l = 0.f;
-            float acc[CH];
-#pragma unroll
-            for (int i = 0; i < CH; ++i) acc[i] = 0.f;
             int ci[3] = {0, 0, 0};
             uint32_t colbits = 0u;               // separable geometry: valid columns of one inner row
             int cached_c2 = -1;
@@ -338,7 +361,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
                     for (int pc = 0; pc < 2; ++pc)
                         words[pc] = valid_q ? low_bits(P.n_extra - ((c - T.nnb) * kChunk + 64 * team + 32 * pc)) : 0u;
-                } else if (kInner > 0) {
+                } else if constexpr (kInner > 0) {
                     if (ci[2] != cached_c2) {
                         cached_c2 = ci[2];
                         int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
@@ -364,29 +387,35 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     for (int pc = 0; pc < 2; ++pc) words[pc] = piece_word(P, ci, 2 * team + pc, f, e);
                 }
 
-                if (warp == 0 && lane == 0) stamp(64);
+                // ---- scores of this half into registers; S is free for the next chunk after that ----
                 ok = ok && mbar_wait(bar_s, gc & 1, abort_flag);
                 tc_fence_after();
-                if (warp == 0 && lane == 0) stamp(64);
+                uint32_t s0[32], s1[32];
+                const bool any0 = __any_sync(0xffffffffu, words[0] != 0u);
+                const bool any1 = __any_sync(0xffffffffu, words[1] != 0u);
+                if (any0) tmem_ld32(trow + kColS + 64 * team, s0);
+                if (any1) tmem_ld32(trow + kColS + 64 * team + 32, s1);
+                tmem_ld_wait();
 
-                // ---- pass 1: maximum over the valid columns of this half, then agree with the other half ----
+                // ---- maximum over the valid columns of this half, then agree with the other half ----
+                // columns outside the row's neighbourhood become -inf once, here
                 float mc = -INFINITY;
-#pragma unroll
-                for (int pc = 0; pc < 2; ++pc) {
-                    if (!__any_sync(0xffffffffu, words[pc] != 0u)) continue;
-                    uint32_t s[32];
-                    tmem_ld32(trow + kColS + 64 * team + 32 * pc, s);
-                    tmem_ld_wait();
+                auto masked_max = [&](uint32_t (&s)[32], uint32_t w) {
                     float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
-                        m0 = fmaxf(m0, ((words[pc] >> i) & 1u) ? __uint_as_float(s[i]) : -INFINITY);
-                        m1 = fmaxf(m1, ((words[pc] >> (i + 1)) & 1u) ? __uint_as_float(s[i + 1]) : -INFINITY);
-                        m2 = fmaxf(m2, ((words[pc] >> (i + 2)) & 1u) ? __uint_as_float(s[i + 2]) : -INFINITY);
-                        m3 = fmaxf(m3, ((words[pc] >> (i + 3)) & 1u) ? __uint_as_float(s[i + 3]) : -INFINITY);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (!((w >> (i + j)) & 1u)) s[i + j] = 0xff800000u;
+                        m0 = fmaxf(m0, __uint_as_float(s[i]));
+                        m1 = fmaxf(m1, __uint_as_float(s[i + 1]));
+                        m2 = fmaxf(m2, __uint_as_float(s[i + 2]));
+                        m3 = fmaxf(m3, __uint_as_float(s[i + 3]));
                     }
                     mc = fmaxf(mc, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
-                }
+                };
+                if (any0) masked_max(s0, words[0]);
+                if (any1) masked_max(s1, words[1]);
                 if (!ok) mc = -INFINITY;
                 {
                     // Both halves must use one maximum.  Each publishes its own rounded up to bf16
@@ -398,40 +427,46 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     const uint32_t other = static_cast<uint32_t>(xmax[(1 - team) * 128 + row]) << 16;
                     mc = fmaxf(__uint_as_float(bits), __uint_as_float(other));
                 }
-                if (warp == 0 && lane == 0) stamp(64);
-                const float m_new = fmaxf(m, mc);
-                const float alpha = (m == -INFINITY) ? 0.f : fast_exp2((m - m_new) * P.scale_log2);
-                const float mb = (m_new == -INFINITY) ? 0.f : m_new * P.scale_log2;
+                // S(c) is in registers and the partner's maximum has been read: the next scores may
+                // land (they are what lets this thread overwrite its exchange slot again).
+                tc_fence_before();
+                mbar_arrive(bar_sr);
 
-                // ---- fold the previous chunk's P V (this team's channels) ----
+                // ---- P(c-1) V has finished: P may be rewritten, O may be rescaled ----
                 if (c > 0) {
                     ok = ok && mbar_wait(bar_o, (gc - 1) & 1, abort_flag);
                     tc_fence_after();
-#pragma unroll
-                    for (int part = 0; part < CH / 32; ++part) {
-                        uint32_t o[32];
-                        tmem_ld32(trow + kColO + CH * team + 32 * part, o);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) acc[32 * part + i] = (acc[32 * part + i] + __uint_as_float(o[i])) * alpha;
-                    }
                 }
-
-                if (warp == 0 && lane == 0) stamp(64);
-                // ---- pass 2: probabilities -> TMEM (16-bit pairs), row sum of this half ----
-                float r0 = 0.f, r1 = 0.f;
-#pragma unroll
-                for (int pc = 0; pc < 2; ++pc) {
-                    uint32_t packed[16];
-                    if (__any_sync(0xffffffffu, words[pc] != 0u)) {
-                        uint32_t s[32];
-                        tmem_ld32(trow + kColS + 64 * team + 32 * pc, s);
+                bool grow = false;
+                if (mc > -INFINITY) {
+                    if (m == -INFINITY) m = mc;
+                    else grow = (mc - m) * P.scale_log2 > 8.f;
+                }
+                if (__any_sync(0xffffffffu, grow)) {          // rare: both halves of a row decide alike
+                    const float fac = grow ? fast_exp2((m - mc) * P.scale_log2) : 1.f;
+#pragma unroll 1
+                    for (int part = 0; part < CH / 16; ++part) {
+                        uint32_t o[16];
+                        tmem_ld16(trow + kColO + CH * team + 16 * part, o);
                         tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * fac);
+                        tmem_st16(trow + kColO + CH * team + 16 * part, o);
+                    }
+                    l *= fac;
+                    if (grow) m = mc;
+                }
+                const float mb = (m == -INFINITY) ? 0.f : m * P.scale_log2;
+
+                // ---- probabilities -> TMEM (16-bit pairs), row sum of this half ----
+                float r0 = 0.f, r1 = 0.f;
+                auto probabilities = [&](const uint32_t (&s)[32], bool any, int pc) {
+                    uint32_t packed[16];
+                    if (any) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const float x0 = ((words[pc] >> (2 * i)) & 1u) ? fmaf(__uint_as_float(s[2 * i]), P.scale_log2, -mb) : -INFINITY;
-                            const float x1 = ((words[pc] >> (2 * i + 1)) & 1u) ? fmaf(__uint_as_float(s[2 * i + 1]), P.scale_log2, -mb) : -INFINITY;
-                            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                            const float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * i]), P.scale_log2, -mb));
+                            const float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), P.scale_log2, -mb));
                             r0 += p0;
                             r1 += p1;
                             packed[i] = cvt_pack<BF16>(p0, p1);
@@ -441,48 +476,49 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                         for (int i = 0; i < 16; ++i) packed[i] = 0u;
                     }
                     tmem_st16(trow + kColP + 32 * team + 16 * pc, packed);
-                }
-                l = l * alpha + (ok ? r0 + r1 : 0.f);
-                m = m_new;
+                };
+                probabilities(s0, any0, 0);
+                probabilities(s1, any1, 1);
+                l += ok ? r0 + r1 : 0.f;
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(bar_sp);
-                if (warp == 0 && lane == 0) stamp(64);
                 if (++ci[2] == T.nc[2]) { ci[2] = 0; if (++ci[1] == T.nc[1]) { ci[1] = 0; ++ci[0]; } }
             }
 
-            // ---- last chunk's P V, combine the two halves' sums, normalise, write out ----
+            // ---- all of P V is in O: combine the two halves' sums, normalise, write out ----
             ok = ok && mbar_wait(bar_o, (gc - 1) & 1, abort_flag);
             tc_fence_after();
-#pragma unroll
-            for (int part = 0; part < CH / 32; ++part) {
-                uint32_t o[32];
-                tmem_ld32(trow + kColO + CH * team + 32 * part, o);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[32 * part + i] += __uint_as_float(o[i]);
-            }
-            // The halves swap their row sums through two TMEM columns of the (now idle) P area.
+            // The halves swap their row sums through two TMEM columns of the (now idle) P area; the
+            // next tile's first chunk passes the pair's bar.sync again before it stores probabilities.
             tmem_st1(trow + kColP + team, __float_as_uint(l));
             tmem_st_wait();
             asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
-            l += __uint_as_float(tmem_ld1(trow + kColP + (1 - team)));
-            tmem_ld_wait();
-            asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");   // both read before P is written again
-            if (in_tensor) {
-                const bool live = valid_q && l > 0.f && ok;
-                const float inv = live ? 1.f / l : 0.f;
-                uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH + team * CH);
+            {
+                const bool live = valid_q && ok;
 #pragma unroll
-                for (int i = 0; i < CH / 8; ++i) {
-                    uint32_t w[4];
+                for (int part = 0; part < CH / 32; ++part) {
+                    uint32_t o[32], l_other = 0u;
+                    if (part == 0) l_other = tmem_ld1(trow + kColP + (1 - team));
+                    tmem_ld32(trow + kColO + CH * team + 32 * part, o);
+                    tmem_ld_wait();
+                    if (part == 0) l += __uint_as_float(l_other);
+                    const float inv = (live && l > 0.f) ? 1.f / l : 0.f;
+                    if (in_tensor) {
+                        uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH + team * CH + 32 * part);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        w[j] = live ? cvt_pack<BF16>(acc[8 * i + 2 * j] * inv, acc[8 * i + 2 * j + 1] * inv) : 0u;
-                    o4[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                w[j] = cvt_pack<BF16>(__uint_as_float(o[8 * i + 2 * j]) * inv, __uint_as_float(o[8 * i + 2 * j + 1]) * inv);
+                            o4[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
                 }
                 // natural-log lse of scale * logits
-                if (team == 0) lse[out_row] = live ? (m * P.scale_log2 + log2f(l)) * 0.6931471805599453f : 0.f;
+                if (in_tensor && team == 0)
+                    lse[out_row] = (live && l > 0.f) ? (m * P.scale_log2 + log2f(l)) * 0.6931471805599453f : 0.f;
             }
             if (tr && tid == 0) { tr[120] = t_begin; tr[121] = clock64(); tr = nullptr; }
         }
