@@ -14,6 +14,7 @@ _LAZY = {
     "merge_attentions": "merge",
     "NeighborhoodAttention1D": "nn", "NeighborhoodAttention2D": "nn", "NeighborhoodAttention3D": "nn",
     "get_support_matrix": "support_matrix",
+    "HostStep": "host_step",
 }
 
 __all__ = sorted(list(_LAZY) + ["has_cuda", "get_backend", "set_backend", "__version__"])

@@ -170,3 +170,15 @@ def test_module_parameter_names_match_the_reference_layout():
         nb.NeighborhoodAttention3D(30, 4, 3)
     x = torch.empty(2, 8, 8, 32, device="meta")
     assert m.to("meta")(x).shape == (2, 8, 8, 32)
+
+
+def test_host_step_needs_cuda_and_validates():
+    import torch
+    from natten_mps_b200.host_step import HostStep
+    with pytest.raises(ValueError):
+        HostStep(4, 3)
+    with pytest.raises(ValueError):
+        HostStep(2, 3, stride=5)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            HostStep(2, 3)
