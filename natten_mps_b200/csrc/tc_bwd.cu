@@ -71,6 +71,50 @@ __device__ __forceinline__ void inverse_range(int n, int L, int K, int causal, i
     }
 }
 
+// Geometry of one work item: a tile of 128 rows (queries | keys) of one (batch, head).
+struct BwdTile {
+    int b, hy;                 // batch; head of the row tensors (query head | kv head)
+    int rg[3], origin[3], Lp[3], boxlo[3], nc[3];
+    int nchunks;               // chunks of the column box
+    int nbox, total;           // column passes: box chunks x query heads of the group, then additional tokens
+    bool active;
+};
+
+template <bool kKeySide>
+__device__ __forceinline__ void bwd_tile_setup(const TcParams& P, unsigned work, BwdTile& T)
+{
+    const unsigned hb = work / P.per_head;
+    const unsigned bx = work - hb * P.per_head;
+    const unsigned H = (unsigned)(kKeySide ? P.Hkv : P.Hq);
+    T.b = (int)(hb / H);
+    T.hy = (int)(hb - (unsigned)T.b * H);
+    T.active = cta_geometry(P, bx, T.b, T.rg, T.origin, T.Lp);
+    T.nchunks = 1;
+    if (T.active) {
+#pragma unroll
+        for (int a = 0; a < 3; ++a) {
+            const int last = T.origin[a] + P.tile[a] - 1 < T.Lp[a] - 1 ? T.origin[a] + P.tile[a] - 1 : T.Lp[a] - 1;
+            int hi;
+            if (kKeySide) {
+                int t;
+                inverse_range(T.origin[a], T.Lp[a], P.K[a], P.causal[a], T.boxlo[a], t);
+                inverse_range(last, T.Lp[a], P.K[a], P.causal[a], t, hi);
+            } else {
+                T.boxlo[a] = P.causal[a] ? T.origin[a] - (P.K[a] - 1) : ws1(T.origin[a], T.Lp[a], P.K[a]);
+                hi = P.causal[a] ? last : ws1(last, T.Lp[a], P.K[a]) + P.K[a] - 1;
+            }
+            T.nc[a] = chunks_along(P, a, hi - T.boxlo[a] + 1);
+            T.nchunks *= T.nc[a];
+        }
+    }
+    T.nbox = T.nchunks * (kKeySide ? P.group : 1);
+    T.total = T.nbox + (kKeySide ? 0 : ((P.n_extra + kCols - 1) >> 6));
+}
+
+// Persistent kernel: every CTA walks the work items blockIdx.x, blockIdx.x + gridDim.x, ...;
+// barriers, TMEM and the column-stage ring live for the whole launch, so the next tile's
+// rows and first column chunks are already on their way while this tile's accumulators are
+// written out.  Barrier phases run on across tiles (g = chunks processed so far).
 // kInner: innermost chunk extent when it is 16 or 32 (separable row / column masks, packed
 // 16-bit arithmetic), 0 = any geometry (per-column validity words).
 template <int DH, bool BF16, bool kKeySide, int kInner>
@@ -86,185 +130,57 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     constexpr uint32_t kTmemCols = Smem::kTmemCols, kColA2 = Smem::kColA2;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // query side: blockIdx.y = query head.  key side: blockIdx.y = kv head.
-    const int hy = blockIdx.y, b = blockIdx.z;
-    const int n_heads_col = kKeySide ? P.group : 1;          // column passes (query heads of the group)
-    const int prior_abort = *reinterpret_cast<volatile int*>(P.status);   // loaded early, used at barrier set-up
-
-    // ---- CTA geometry -------------------------------------------------------
-    int rg[3], origin[3], Lp[3], boxlo[3], nc[3];
-    const bool cta_active = cta_geometry(P, blockIdx.x, b, rg, origin, Lp);
-    int nchunks = 1;
-    if (cta_active) {
-#pragma unroll
-        for (int a = 0; a < 3; ++a) {
-            const int last = origin[a] + P.tile[a] - 1 < Lp[a] - 1 ? origin[a] + P.tile[a] - 1 : Lp[a] - 1;
-            int hi;
-            if (kKeySide) {
-                int t;
-                inverse_range(origin[a], Lp[a], P.K[a], P.causal[a], boxlo[a], t);
-                inverse_range(last, Lp[a], P.K[a], P.causal[a], t, hi);
-            } else {
-                boxlo[a] = P.causal[a] ? origin[a] - (P.K[a] - 1) : ws1(origin[a], Lp[a], P.K[a]);
-                hi = P.causal[a] ? last : ws1(last, Lp[a], P.K[a]) + P.K[a] - 1;
-            }
-            nc[a] = chunks_along(P, a, hi - boxlo[a] + 1);
-            nchunks *= nc[a];
-        }
-    }
-
     const int quad = warp & 3, piece = (warp >> 2) & 1;      // compute warps: TMEM lane quadrant, 32-column piece
-    if (!cta_active) {                       // padding rows get zero gradients
-        if (warp < kComputeWarps) {
-            int ri[3];
-            row_offsets(P, quad * 32 + lane, ri);
-            bool inside = true;
-            long long pflat = 0;
-#pragma unroll
-            for (int a = 0; a < 3; ++a) {
-                const int pa = rg[a] + P.dil[a] * (origin[a] + ri[a]);
-                if (pa >= P.L[a]) inside = false;
-                pflat = pflat * P.L[a] + pa;
-            }
-            if (inside) {
-                const long long orow = ((long long)b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + hy;
-#pragma unroll
-                for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
-                    uint4* o = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + orow * DH + piece * CH);
-#pragma unroll
-                    for (int i = 0; i < CH / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
-                }
-            }
-        }
-        return;
-    }
+    const int prior_abort = *reinterpret_cast<volatile int*>(P.status);   // loaded early, used at barrier set-up
+    const unsigned nwork = kKeySide ? P.work_kv : P.work_q;
 
     // ---- shared memory, barriers, TMEM --------------------------------------
     const uint32_t sbase = smem_u32(smem);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kBar + 128);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Smem::kBar + 136);
-    const uint32_t bar_row = sbase + Smem::kBar + 0;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kBar + 160);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Smem::kBar + 168);
+    const uint32_t bar_row = sbase + Smem::kBar + 0;          // row tiles landed
     const uint32_t bar_col = sbase + Smem::kBar + 8;          // [kStages] C1, C2 landed
     const uint32_t bar_stats = sbase + Smem::kBar + 40;       // [kStages] column lse / delta staged
     const uint32_t bar_s = sbase + Smem::kBar + 72;           // S and dP of the chunk are in TMEM
     const uint32_t bar_sp = sbase + Smem::kBar + 80;          // threads consumed S/dP, wrote P/dS
     const uint32_t bar_acc = sbase + Smem::kBar + 88;         // accumulating MMAs of the chunk finished
+    const uint32_t bar_free = sbase + Smem::kBar + 96;        // [kStages] the same, per stage (for the statistics warp)
     float* stats = reinterpret_cast<float*>(smem + Smem::kStats);
 
-    // column passes of this CTA; on the query side the additional tokens follow, 64 per pass
-    const int nbox = nchunks * n_heads_col;
-    const int total = nbox + (kKeySide ? 0 : ((P.n_extra + kCols - 1) >> 6));
-    const int head_row = hy;                                  // head coordinate of the row tensors
-    const int head_kv = kKeySide ? hy : hy / P.group;
-    // Column loads are issued in order; counters avoid divisions.
-    int ld[3] = {0, 0, 0}, ld_head = 0, loaded = 0;
-    auto issue_cols = [&]() {
-        const int s = loaded % kStages;
-        const uint32_t bar = bar_col + 8 * s;
-        mbar_expect_tx(bar, 2 * kColTile);
-        if (loaded < nbox) {
-            int X[3];
-#pragma unroll
-            for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (boxlo[a] + ld[a] * P.cb[a]);
-            // query side: columns are keys (kv head); key side: columns are queries (query head)
-            const int hx = (kKeySide ? hy * P.group + ld_head : head_kv) * DH;
-#pragma unroll
-            for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                tma_load_5d(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmC1, bar, hx + 64 * hf, X[2], X[1], X[0], b);
-                tma_load_5d(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmC2, bar, hx + 64 * hf, X[2], X[1], X[0], b);
-            }
-            if (++ld[2] == nc[2]) { ld[2] = 0; if (++ld[1] == nc[1]) { ld[1] = 0; if (++ld[0] == nc[0]) { ld[0] = 0; ++ld_head; } } }
-        } else {                                 // additional tokens (rows past n_extra are zero-filled)
-            const int e0 = (loaded - nbox) * kCols;
-#pragma unroll
-            for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                tma_load_5d(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmE1, bar, head_kv * DH + 64 * hf, e0, 0, 0, b);
-                tma_load_5d(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmE2, bar, head_kv * DH + 64 * hf, e0, 0, 0, b);
-            }
-        }
-        ++loaded;
-    };
-    // The issuing warp sets up the barriers, allocates TMEM and starts the first loads right away,
-    // so they are in flight while the compute warps are still working out their row geometry.
     if (warp == kComputeWarps) {
         if (lane == 0) {
             *abort_flag = ((sbase & 1023u) || prior_abort) ? 1 : 0;
             mbar_init(bar_row, 1);
-            for (int s = 0; s < kStages; ++s) { mbar_init(bar_col + 8 * s, 1); mbar_init(bar_stats + 8 * s, 32); }
+            for (int s = 0; s < kStages; ++s) {
+                mbar_init(bar_col + 8 * s, 1);
+                mbar_init(bar_stats + 8 * s, 32);
+                mbar_init(bar_free + 8 * s, 1);
+            }
             mbar_init(bar_s, 1);
             mbar_init(bar_sp, kComputeWarps * 32);
             mbar_init(bar_acc, 1);
             mbar_init_fence();
             fence_async_smem();
-            if (!*abort_flag) {
-                const int hx = (kKeySide ? head_kv : head_row) * DH;
-                mbar_expect_tx(bar_row, 2 * kTile);
-#pragma unroll
-                for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                    tma_load_5d(sbase + Smem::kR1 + hf * kRowHalf, &tmR1, bar_row, hx + 64 * hf, rg[2] + P.dil[2] * origin[2],
-                                rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
-                    tma_load_5d(sbase + Smem::kR2 + hf * kRowHalf, &tmR2, bar_row, hx + 64 * hf, rg[2] + P.dil[2] * origin[2],
-                                rg[1] + P.dil[1] * origin[1], rg[0] + P.dil[0] * origin[0], b);
-                }
-                for (int cc = 0; cc < total && cc < kStages; ++cc) issue_cols();
-            }
         }
         __syncwarp();
         tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     }
-    // ---- per-thread row ------------------------------------------------------
-    int f[3] = {0, 0, 0}, e[3] = {0, 0, 0};
-    bool valid_row = false, in_tensor = false;
-    long long out_row = 0;
-    float row_lse2 = 0.f, row_delta = 0.f;
-    if (warp < kComputeWarps) {
-        int ri[3];
-        row_offsets(P, quad * 32 + lane, ri);
-        valid_row = true; in_tensor = true;
-        long long pflat = 0;
-#pragma unroll
-        for (int a = 0; a < 3; ++a) {
-            const int xa = origin[a] + ri[a];
-            const int pa = rg[a] + P.dil[a] * xa;
-            if (xa >= Lp[a]) valid_row = false;
-            if (pa >= P.L[a]) in_tensor = false;
-            pflat = pflat * P.L[a] + pa;
-            if (cta_active) {
-                if (kKeySide) {
-                    int qlo, qhi;
-                    inverse_range(xa, Lp[a], P.K[a], P.causal[a], qlo, qhi);
-                    f[a] = qlo - boxlo[a];
-                    e[a] = qhi + 1 - boxlo[a];
-                } else {
-                    const int first = P.causal[a] ? xa - (P.K[a] - 1) : ws1(xa, Lp[a], P.K[a]);
-                    f[a] = (first > 0 ? first : 0) - boxlo[a];
-                    e[a] = (first + P.K[a] < Lp[a] ? first + P.K[a] : Lp[a]) - boxlo[a];
-                }
-            }
-        }
-        if (!valid_row) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
-        out_row = ((long long)b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + hy;
-        if (!kKeySide && valid_row && cta_active) {          // negated, pre-scaled addends
-            row_lse2 = -lse[out_row] * 1.4426950408889634f;
-            row_delta = -delta[out_row] * P.scale;
-        }
-    }
-
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // debug clock stamps: CTA (5, 0, 0); key side uses the upper half of the buffer
-    long long* tr = (P.trace && blockIdx.x == 5 && blockIdx.y == 0 && blockIdx.z == 0) ? P.trace + (kKeySide ? 128 : 0) : nullptr;
+    // debug clock stamps of CTA 5; key side uses the upper half of the buffer
+    long long* tr = (P.trace && blockIdx.x == 5) ? P.trace + (kKeySide ? 128 : 0) : nullptr;
     int tn = 0;
-    auto stamp = [&](int base) { if (tr && tn < 60) tr[base + tn++] = clock64(); };
+    auto stamp = [&](int base) { if (tr && tn < 56) tr[base + tn++] = clock64(); };
 
-    auto chunk_index = [&](int cc, int (&ci)[3], int& head_col) {
-        head_col = kKeySide ? hy * P.group + cc / nchunks : hy;
-        int c = cc % nchunks;
-        ci[2] = c % nc[2]; c /= nc[2];
-        ci[1] = c % nc[1]; c /= nc[1];
-        ci[0] = c;
+    // next work item of this CTA with anything to do for the tensor cores
+    auto next_active = [&](unsigned w, BwdTile& X) {
+        for (; w < nwork; w += gridDim.x) {
+            bwd_tile_setup<kKeySide>(P, w, X);
+            if (X.active) break;
+        }
+        return w;
     };
 
     if (warp == kComputeWarps) {
@@ -275,8 +191,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             constexpr uint32_t idesc_kk = instr_desc(BF16 ? 1 : 0, kCols, 0, 0);    // both operands K-major
             constexpr uint32_t idesc_acc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A from TMEM, B MN-major
             const uint64_t dR1 = smem_desc(sbase + Smem::kR1, 16, 1024), dR2 = smem_desc(sbase + Smem::kR2, 16, 1024);
-            auto issue_s_dp = [&](int cc) {
-                const int s = cc % kStages;
+            auto issue_s_dp = [&](unsigned g) {
+                const int s = g % kStages;
                 const uint64_t dC1 = smem_desc(sbase + Smem::kC1 + s * kColTile, 16, 1024);
                 const uint64_t dC2 = smem_desc(sbase + Smem::kC2 + s * kColTile, 16, 1024);
                 tc_fence_after();
@@ -294,46 +210,110 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             // k-step ks covers columns 16*ks..16*ks+15 of the chunk; their 16-bit pairs sit in the
             // first 16 TMEM columns of the 32-column piece they came from.  The column tile is read
             // MN-major: 16 rows (2048 bytes) per k-step, the second 64-channel block kColHalf further.
-            auto issue_acc = [&](int cc) {
-                const int s = cc % kStages;
+            auto issue_acc = [&](unsigned g, bool accumulate) {
+                const int s = g % kStages;
                 const uint64_t dC1 = smem_desc(sbase + Smem::kC1 + s * kColTile, kColHalf, 1024);
                 const uint64_t dC2 = smem_desc(sbase + Smem::kC2 + s * kColTile, kColHalf, 1024);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kCols / 16; ++ks)
                     mma_ts(tmem + kColA1, tmem + kColDP + 32 * (ks / 2) + 8 * (ks % 2), dC1 + 128 * ks, idesc_acc,
-                           (cc > 0 || ks > 0) ? 1u : 0u);
+                           (accumulate || ks > 0) ? 1u : 0u);
                 if (kKeySide) {
 #pragma unroll
                     for (int ks = 0; ks < kCols / 16; ++ks)
                         mma_ts(tmem + kColA2, tmem + kColS + 32 * (ks / 2) + 8 * (ks % 2), dC2 + 128 * ks, idesc_acc,
-                               (cc > 0 || ks > 0) ? 1u : 0u);
+                               (accumulate || ks > 0) ? 1u : 0u);
                 }
                 mma_commit(bar_acc);
+                if (kKeySide) mma_commit(bar_free + 8 * s);
+            };
+            auto issue_rows = [&](const BwdTile& X) {
+                const int hx = X.hy * DH;
+                mbar_expect_tx(bar_row, 2 * kTile);
+#pragma unroll
+                for (int hf = 0; hf < Smem::kHalves; ++hf) {
+                    tma_load_5d(sbase + Smem::kR1 + hf * kRowHalf, &tmR1, bar_row, hx + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
+                                X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
+                    tma_load_5d(sbase + Smem::kR2 + hf * kRowHalf, &tmR2, bar_row, hx + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
+                                X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
+                }
+            };
+            // Column loads run ahead of the MMAs, across tiles: their own cursor.
+            BwdTile Tl;
+            unsigned wl = next_active(blockIdx.x, Tl), loaded = 0;
+            int ld[3] = {0, 0, 0}, ld_head = 0, ld_in_tile = 0;
+            auto issue_cols = [&]() {
+                if (wl >= nwork) return;
+                const int s = loaded % kStages;
+                const uint32_t bar = bar_col + 8 * s;
+                mbar_expect_tx(bar, 2 * kColTile);
+                const int head_kv = kKeySide ? Tl.hy : Tl.hy / P.group;
+                if (ld_in_tile < Tl.nbox) {
+                    int X[3];
+#pragma unroll
+                    for (int a = 0; a < 3; ++a) X[a] = Tl.rg[a] + P.dil[a] * (Tl.boxlo[a] + ld[a] * P.cb[a]);
+                    // query side: columns are keys (kv head); key side: columns are queries (query head)
+                    const int hx = (kKeySide ? Tl.hy * P.group + ld_head : head_kv) * DH;
+#pragma unroll
+                    for (int hf = 0; hf < Smem::kHalves; ++hf) {
+                        tma_load_5d(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmC1, bar, hx + 64 * hf, X[2], X[1], X[0], Tl.b);
+                        tma_load_5d(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmC2, bar, hx + 64 * hf, X[2], X[1], X[0], Tl.b);
+                    }
+                    if (++ld[2] == Tl.nc[2]) { ld[2] = 0; if (++ld[1] == Tl.nc[1]) { ld[1] = 0; if (++ld[0] == Tl.nc[0]) { ld[0] = 0; ++ld_head; } } }
+                } else {                                 // additional tokens (rows past n_extra are zero-filled)
+                    const int e0 = (ld_in_tile - Tl.nbox) * kCols;
+#pragma unroll
+                    for (int hf = 0; hf < Smem::kHalves; ++hf) {
+                        tma_load_5d(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmE1, bar, head_kv * DH + 64 * hf, e0, 0, 0, Tl.b);
+                        tma_load_5d(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmE2, bar, head_kv * DH + 64 * hf, e0, 0, 0, Tl.b);
+                    }
+                }
+                ++loaded;
+                if (++ld_in_tile == Tl.total) {
+                    wl = next_active(wl + gridDim.x, Tl);
+                    ld[0] = ld[1] = ld[2] = 0; ld_head = 0; ld_in_tile = 0;
+                }
             };
 
-            stamp(0);
-            bool ok = mbar_wait(bar_row, 0, abort_flag);
-            ok = ok && mbar_wait(bar_col, 0, abort_flag);
-            stamp(0);
-            if (ok) issue_s_dp(0);
-            stamp(0);
-            for (int cc = 0; cc < total && ok; ++cc) {
-                ok = mbar_wait(bar_sp, cc & 1, abort_flag);              // S/dP consumed, P/dS stored
+            BwdTile T, Tn;
+            unsigned work = next_active(blockIdx.x, T);
+            if (work < nwork) {
+                issue_rows(T);
+                for (int i = 0; i < kStages; ++i) issue_cols();
+            }
+            unsigned g = 0, tileno = 0;
+            bool ok = true;
+            while (work < nwork && ok) {
+                stamp(0);
+                ok = mbar_wait(bar_row, tileno & 1, abort_flag) &&
+                     mbar_wait(bar_col + 8 * (g % kStages), (g / kStages) & 1, abort_flag);
                 if (!ok) break;
                 stamp(0);
-                issue_acc(cc);                                           // reads P/dS ...
-                if (cc + 1 < total) {
-                    ok = mbar_wait(bar_col + 8 * ((cc + 1) % kStages), ((cc + 1) / kStages) & 1, abort_flag);
+                issue_s_dp(g);
+                unsigned wnext = nwork;
+                for (int cc = 0; cc < T.total && ok; ++cc, ++g) {
+                    const bool last = cc + 1 == T.total;
+                    if (last) wnext = next_active(work + gridDim.x, Tn);     // while the threads work on the chunk
+                    ok = mbar_wait(bar_sp, g & 1, abort_flag);               // S/dP consumed, P/dS stored
                     if (!ok) break;
-                    issue_s_dp(cc + 1);                                  // ... before the next S/dP overwrite them
-                }
-                stamp(0);
-                if (cc + kStages < total) {
-                    ok = mbar_wait(bar_acc, cc & 1, abort_flag);         // stage cc % kStages is free again
+                    stamp(0);
+                    issue_acc(g, cc > 0);                                    // reads P/dS ...
+                    if (!last) {
+                        ok = mbar_wait(bar_col + 8 * ((g + 1) % kStages), ((g + 1) / kStages) & 1, abort_flag);
+                        if (!ok) break;
+                        issue_s_dp(g + 1);                                   // ... before the next S/dP overwrite them
+                    } else if (wnext < nwork) {
+                        issue_rows(Tn);        // every S/dP product of this tile has finished: its rows are free
+                    }
+                    stamp(0);
+                    ok = mbar_wait(bar_acc, g & 1, abort_flag);              // stage g % kStages is free again
                     if (!ok) break;
                     issue_cols();
                 }
+                T = Tn;
+                work = wnext;
+                ++tileno;
             }
         }
     } else if (warp == kComputeWarps + 1) {
@@ -342,34 +322,38 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         // =====================================================================
         if (kKeySide) {
             bool ok = !*abort_flag;
-            for (int cc = 0; cc < total; ++cc) {
-                const int s = cc % kStages;
-                if (cc >= kStages) ok = ok && mbar_wait(bar_acc, (cc - kStages) & 1, abort_flag);
-                int ci[3], hc;
-                chunk_index(cc, ci, hc);
-                float* st = stats + s * 128;
+            unsigned g = 0;
+            BwdTile T;
+            for (unsigned work = next_active(blockIdx.x, T); work < nwork; work = next_active(work + gridDim.x, T)) {
+                int ci[3] = {0, 0, 0}, hc = T.hy * P.group;
+                for (int cc = 0; cc < T.total; ++cc, ++g) {
+                    const int s = g % kStages;
+                    if (g >= (unsigned)kStages) ok = ok && mbar_wait(bar_free + 8 * s, ((g / kStages) - 1) & 1, abort_flag);
+                    float* st = stats + s * 128;
 #pragma unroll
-                for (int k = 0; k < kCols / 32; ++k) {
-                    const int j = lane + 32 * k;
-                    const int j2 = j & (P.cb[2] - 1);
-                    const int j1 = (j >> P.cb2_log) & (P.cb[1] - 1);
-                    const int j0 = j >> (P.cb2_log + P.cb1_log);
-                    const int q0 = boxlo[0] + ci[0] * P.cb[0] + j0;
-                    const int q1 = boxlo[1] + ci[1] * P.cb[1] + j1;
-                    const int q2 = boxlo[2] + ci[2] * P.cb[2] + j2;
-                    const bool inside = ok && q0 >= 0 && q0 < Lp[0] && q1 >= 0 && q1 < Lp[1] && q2 >= 0 && q2 < Lp[2];
-                    float l2 = 0.f, dl = 0.f;
-                    if (inside) {
-                        const long long pflat = ((long long)(rg[0] + P.dil[0] * q0) * P.L[1] + (rg[1] + P.dil[1] * q1)) * P.L[2]
-                                                + (rg[2] + P.dil[2] * q2);
-                        const long long row = ((long long)b * P.ltot + pflat) * P.Hq + hc;
-                        l2 = -lse[row] * 1.4426950408889634f;        // negated, pre-scaled addends
-                        dl = -delta[row] * P.scale;
+                    for (int k = 0; k < kCols / 32; ++k) {
+                        const int j = lane + 32 * k;
+                        const int j2 = j & (P.cb[2] - 1);
+                        const int j1 = (j >> P.cb2_log) & (P.cb[1] - 1);
+                        const int j0 = j >> (P.cb2_log + P.cb1_log);
+                        const int q0 = T.boxlo[0] + ci[0] * P.cb[0] + j0;
+                        const int q1 = T.boxlo[1] + ci[1] * P.cb[1] + j1;
+                        const int q2 = T.boxlo[2] + ci[2] * P.cb[2] + j2;
+                        const bool inside = ok && q0 >= 0 && q0 < T.Lp[0] && q1 >= 0 && q1 < T.Lp[1] && q2 >= 0 && q2 < T.Lp[2];
+                        float l2 = 0.f, dl = 0.f;
+                        if (inside) {
+                            const long long pflat = ((long long)(T.rg[0] + P.dil[0] * q0) * P.L[1] + (T.rg[1] + P.dil[1] * q1)) * P.L[2]
+                                                    + (T.rg[2] + P.dil[2] * q2);
+                            const long long row = ((long long)T.b * P.ltot + pflat) * P.Hq + hc;
+                            l2 = -lse[row] * 1.4426950408889634f;        // negated, pre-scaled addends
+                            dl = -delta[row] * P.scale;
+                        }
+                        st[j] = l2;
+                        st[kCols + j] = dl;
                     }
-                    st[j] = l2;
-                    st[kCols + j] = dl;
+                    mbar_arrive(bar_stats + 8 * s);
+                    if (++ci[2] == T.nc[2]) { ci[2] = 0; if (++ci[1] == T.nc[1]) { ci[1] = 0; if (++ci[0] == T.nc[0]) { ci[0] = 0; ++hc; } } }
                 }
-                mbar_arrive(bar_stats + 8 * s);
             }
         }
     } else {
@@ -378,163 +362,219 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         // =====================================================================
         const uint32_t trow = tmem + (static_cast<uint32_t>(quad * 32) << 16);
         bool ok = true;
+        unsigned g = 0;                          // chunks processed so far (all tiles)
         constexpr int kPairs = kInner > 0 ? kInner / 2 : 1;
         constexpr int kRows = kInner > 0 ? 32 / kInner : 1;
-        int ci[3] = {0, 0, 0};                   // chunk index per axis, advanced without divisions
-        uint32_t colmask[kPairs];                // separable geometry: 16-bit lane masks per column pair
-        bool cols_any = false;
-        int cached_c2 = -1;
-        for (int cc = 0; cc < total; ++cc) {
-            // ---- validity of this warp's 32 columns for this thread's row ----
-            uint32_t word = 0u;                  // generic geometry: one bit per column
-            uint32_t rowmask[kRows];             // separable geometry: all-ones / zero per inner row
-            bool mine = false;
-            const bool extra = !kKeySide && cc >= nbox;      // additional tokens: first n_extra columns, every live row
-            if (extra) {
-                word = valid_row ? low_bits(P.n_extra - ((cc - nbox) * kCols + 32 * piece)) : 0u;
-                mine = word != 0u;
-            } else if (kInner > 0) {
-                if (ci[2] != cached_c2) {        // the column masks only change with the innermost chunk index
-                    cached_c2 = ci[2];
-                    const int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
+        for (unsigned work = blockIdx.x; work < nwork; work += gridDim.x) {
+            BwdTile T;
+            bwd_tile_setup<kKeySide>(P, work, T);
+            // ---- this thread's row ----
+            int f[3] = {0, 0, 0}, e[3] = {0, 0, 0};
+            bool valid_row = true, in_tensor = true;
+            long long out_row;
+            float row_lse2 = 0.f, row_delta = 0.f;
+            {
+                int ri[3];
+                row_offsets(P, quad * 32 + lane, ri);
+                long long pflat = 0;
 #pragma unroll
-                    for (int i = 0; i < kPairs; ++i)
-                        colmask[i] = ((2 * i >= lo2 && 2 * i < hi2) ? 0x0000FFFFu : 0u) |
-                                     ((2 * i + 1 >= lo2 && 2 * i + 1 < hi2) ? 0xFFFF0000u : 0u);
-                    cols_any = hi2 > 0 && lo2 < kInner && hi2 > lo2;
+                for (int a = 0; a < 3; ++a) {
+                    const int xa = T.origin[a] + ri[a];
+                    const int pa = T.rg[a] + P.dil[a] * xa;
+                    if (xa >= T.Lp[a]) valid_row = false;
+                    if (pa >= P.L[a]) in_tensor = false;
+                    pflat = pflat * P.L[a] + pa;
+                    if (T.active) {
+                        if (kKeySide) {
+                            int qlo, qhi;
+                            inverse_range(xa, T.Lp[a], P.K[a], P.causal[a], qlo, qhi);
+                            f[a] = qlo - T.boxlo[a];
+                            e[a] = qhi + 1 - T.boxlo[a];
+                        } else {
+                            const int first = P.causal[a] ? xa - (P.K[a] - 1) : ws1(xa, T.Lp[a], P.K[a]);
+                            f[a] = (first > 0 ? first : 0) - T.boxlo[a];
+                            e[a] = (first + P.K[a] < T.Lp[a] ? first + P.K[a] : T.Lp[a]) - T.boxlo[a];
+                        }
+                    }
                 }
-#pragma unroll
-                for (int t = 0; t < kRows; ++t) {
-                    const int jj = 32 * piece + t * kInner;
-                    const int j1 = (jj >> P.cb2_log) & (P.cb[1] - 1);
-                    const int j0 = jj >> (P.cb2_log + P.cb1_log);
-                    const int i0 = ci[0] * P.cb[0] + j0, i1 = ci[1] * P.cb[1] + j1;
-                    const bool rok = i0 >= f[0] && i0 < e[0] && i1 >= f[1] && i1 < e[1];
-                    rowmask[t] = rok ? 0xFFFFFFFFu : 0u;
-                    mine = mine || (rok && cols_any);
-                }
-            } else {
-                word = piece_word(P, ci, piece, f, e);
-                mine = word != 0u;
+                if (!valid_row) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
+                out_row = ((long long)T.b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + T.hy;
             }
-            const bool any = __any_sync(0xffffffffu, mine);
-            const bool separable = kInner > 0 && !extra;
-            const bool full = !separable && __all_sync(0xffffffffu, word == 0xffffffffu);
+            if (!T.active) {                     // padding rows get zero gradients
+                if (in_tensor) {
+#pragma unroll
+                    for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
+                        uint4* o = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * DH + piece * CH);
+#pragma unroll
+                        for (int i = 0; i < CH / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
+                    }
+                }
+                continue;
+            }
+            if (!kKeySide && valid_row) {        // negated, pre-scaled addends
+                row_lse2 = -lse[out_row] * 1.4426950408889634f;
+                row_delta = -delta[out_row] * P.scale;
+            }
+            const int nbox = T.nbox;
+            int ci[3] = {0, 0, 0};               // chunk index per axis, advanced without divisions
+            uint32_t colmask[kPairs];            // separable geometry: 16-bit lane masks per column pair
+            bool cols_any = false;
+            int cached_c2 = -1;
+            for (int cc = 0; cc < T.total; ++cc, ++g) {
+                // ---- validity of this warp's 32 columns for this thread's row ----
+                uint32_t word = 0u;                  // generic geometry: one bit per column
+                uint32_t rowmask[kRows];             // separable geometry: all-ones / zero per inner row
+                bool mine = false;
+                const bool extra = !kKeySide && cc >= nbox;      // additional tokens: first n_extra columns, every live row
+                if (extra) {
+                    word = valid_row ? low_bits(P.n_extra - ((cc - nbox) * kCols + 32 * piece)) : 0u;
+                    mine = word != 0u;
+                } else if (kInner > 0) {
+                    if (ci[2] != cached_c2) {        // the column masks only change with the innermost chunk index
+                        cached_c2 = ci[2];
+                        const int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
+#pragma unroll
+                        for (int i = 0; i < kPairs; ++i)
+                            colmask[i] = ((2 * i >= lo2 && 2 * i < hi2) ? 0x0000FFFFu : 0u) |
+                                         ((2 * i + 1 >= lo2 && 2 * i + 1 < hi2) ? 0xFFFF0000u : 0u);
+                        cols_any = hi2 > 0 && lo2 < kInner && hi2 > lo2;
+                    }
+#pragma unroll
+                    for (int t = 0; t < kRows; ++t) {
+                        const int jj = 32 * piece + t * kInner;
+                        const int j1 = (jj >> P.cb2_log) & (P.cb[1] - 1);
+                        const int j0 = jj >> (P.cb2_log + P.cb1_log);
+                        const int i0 = ci[0] * P.cb[0] + j0, i1 = ci[1] * P.cb[1] + j1;
+                        const bool rok = i0 >= f[0] && i0 < e[0] && i1 >= f[1] && i1 < e[1];
+                        rowmask[t] = rok ? 0xFFFFFFFFu : 0u;
+                        mine = mine || (rok && cols_any);
+                    }
+                } else {
+                    word = piece_word(P, ci, piece, f, e);
+                    mine = word != 0u;
+                }
+                const bool any = __any_sync(0xffffffffu, mine);
+                const bool separable = kInner > 0 && !extra;
+                const bool full = !separable && __all_sync(0xffffffffu, word == 0xffffffffu);
 
-            if (warp == 0 && lane == 0) stamp(64);
-            ok = ok && mbar_wait(bar_s, cc & 1, abort_flag);     // also: the previous chunk's P/dS were consumed
-            if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (cc % kStages), (cc / kStages) & 1, abort_flag);
-            tc_fence_after();
-            if (warp == 0 && lane == 0) stamp(64);
-            if (any) {
-                const float* stp = stats + (cc % kStages) * 128 + 32 * piece;
-                const float4* st4 = reinterpret_cast<const float4*>(stp);
+
+                if (warp == 0 && lane == 0) stamp(64);
+                ok = ok && mbar_wait(bar_s, g & 1, abort_flag);      // also: the previous chunk's P/dS were consumed
+                if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (g % kStages), (g / kStages) & 1, abort_flag);
+                tc_fence_after();
+                if (warp == 0 && lane == 0) stamp(64);
+                if (any) {
+                    const float* stp = stats + (g % kStages) * 128 + 32 * piece;
+                    const float4* st4 = reinterpret_cast<const float4*>(stp);
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {               // 16 columns at a time
-                    uint32_t s[16], dp[16], pk_p[8], pk_ds[8];
-                    tmem_ld16(trow + kColS + 32 * piece + 16 * half, s);
-                    tmem_ld16(trow + kColDP + 32 * piece + 16 * half, dp);
-                    tmem_ld_wait();
-                    if (separable || full) {
-                        // P = 2^(s*c - lse2), dS = P * (dP*scale - delta*scale); fp32, rounded once each
+                    for (int half = 0; half < 2; ++half) {               // 16 columns at a time
+                        uint32_t s[16], dp[16], pk_p[8], pk_ds[8];
+                        tmem_ld16(trow + kColS + 32 * piece + 16 * half, s);
+                        tmem_ld16(trow + kColDP + 32 * piece + 16 * half, dp);
+                        tmem_ld_wait();
+                        if (separable || full) {
+                            // P = 2^(s*c - lse2), dS = P * (dP*scale - delta*scale); fp32, rounded once each
 #pragma unroll
-                        for (int g4 = 0; g4 < 4; ++g4) {             // four columns at a time
-                            float nl[4], nd[4];
-                            if (kKeySide) {
-                                const float4 a = st4[4 * half + g4], d = st4[kCols / 4 + 4 * half + g4];
-                                nl[0] = a.x; nl[1] = a.y; nl[2] = a.z; nl[3] = a.w;
-                                nd[0] = d.x; nd[1] = d.y; nd[2] = d.z; nd[3] = d.w;
-                            } else {
-#pragma unroll
-                                for (int u = 0; u < 4; ++u) { nl[u] = row_lse2; nd[u] = row_delta; }
-                            }
-#pragma unroll
-                            for (int h2 = 0; h2 < 2; ++h2) {
-                                const int pl = 2 * g4 + h2, j = 2 * pl;      // pair / column inside the half
-                                const int pi = 8 * half + pl;                // pair inside the piece
-                                const float x0 = fmaf(__uint_as_float(s[j]), P.scale_log2, nl[2 * h2]);
-                                const float x1 = fmaf(__uint_as_float(s[j + 1]), P.scale_log2, nl[2 * h2 + 1]);
-                                const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-                                const float g0 = fmaf(__uint_as_float(dp[j]), P.scale, nd[2 * h2]);
-                                const float g1 = fmaf(__uint_as_float(dp[j + 1]), P.scale, nd[2 * h2 + 1]);
-                                uint32_t dd = cvt_pack<BF16>(p0 * g0, p1 * g1);
-                                if (separable) dd = dd & colmask[pi % kPairs] & rowmask[pi / kPairs];
-                                pk_ds[pl] = dd;
+                            for (int g4 = 0; g4 < 4; ++g4) {             // four columns at a time
+                                float nl[4], nd[4];
                                 if (kKeySide) {
-                                    uint32_t pp = cvt_pack<BF16>(p0, p1);
-                                    if (separable) pp = pp & colmask[pi % kPairs] & rowmask[pi / kPairs];
-                                    pk_p[pl] = pp;
+                                    const float4 a = st4[4 * half + g4], d = st4[kCols / 4 + 4 * half + g4];
+                                    nl[0] = a.x; nl[1] = a.y; nl[2] = a.z; nl[3] = a.w;
+                                    nd[0] = d.x; nd[1] = d.y; nd[2] = d.z; nd[3] = d.w;
+                                } else {
+#pragma unroll
+                                    for (int u = 0; u < 4; ++u) { nl[u] = row_lse2; nd[u] = row_delta; }
+                                }
+#pragma unroll
+                                for (int h2 = 0; h2 < 2; ++h2) {
+                                    const int pl = 2 * g4 + h2, j = 2 * pl;      // pair / column inside the half
+                                    const int pi = 8 * half + pl;                // pair inside the piece
+                                    const float x0 = fmaf(__uint_as_float(s[j]), P.scale_log2, nl[2 * h2]);
+                                    const float x1 = fmaf(__uint_as_float(s[j + 1]), P.scale_log2, nl[2 * h2 + 1]);
+                                    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                                    const float g0 = fmaf(__uint_as_float(dp[j]), P.scale, nd[2 * h2]);
+                                    const float g1 = fmaf(__uint_as_float(dp[j + 1]), P.scale, nd[2 * h2 + 1]);
+                                    uint32_t dd = cvt_pack<BF16>(p0 * g0, p1 * g1);
+                                    if (separable) dd = dd & colmask[pi % kPairs] & rowmask[pi / kPairs];
+                                    pk_ds[pl] = dd;
+                                    if (kKeySide) {
+                                        uint32_t pp = cvt_pack<BF16>(p0, p1);
+                                        if (separable) pp = pp & colmask[pi % kPairs] & rowmask[pi / kPairs];
+                                        pk_p[pl] = pp;
+                                    }
                                 }
                             }
-                        }
-                    } else {
-                        const float* st = stp + 16 * half;
+                        } else {
+                            const float* st = stp + 16 * half;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            float pv[2], dsv[2];
+                            for (int i = 0; i < 8; ++i) {
+                                float pv[2], dsv[2];
 #pragma unroll
-                            for (int u = 0; u < 2; ++u) {
-                                const int j = 2 * i + u;
-                                const float nl = kKeySide ? st[j] : row_lse2;
-                                const float nd = kKeySide ? st[kCols + j] : row_delta;
-                                const bool on = (word >> (16 * half + j)) & 1u;
-                                const float p = on ? fast_exp2(fmaf(__uint_as_float(s[j]), P.scale_log2, nl)) : 0.f;
-                                pv[u] = p;
-                                dsv[u] = p * fmaf(__uint_as_float(dp[j]), P.scale, nd);
+                                for (int u = 0; u < 2; ++u) {
+                                    const int j = 2 * i + u;
+                                    const float nl = kKeySide ? st[j] : row_lse2;
+                                    const float nd = kKeySide ? st[kCols + j] : row_delta;
+                                    const bool on = (word >> (16 * half + j)) & 1u;
+                                    const float p = on ? fast_exp2(fmaf(__uint_as_float(s[j]), P.scale_log2, nl)) : 0.f;
+                                    pv[u] = p;
+                                    dsv[u] = p * fmaf(__uint_as_float(dp[j]), P.scale, nd);
+                                }
+                                pk_p[i] = pack16(pv[0], pv[1], BF16);
+                                pk_ds[i] = pack16(dsv[0], dsv[1], BF16);
                             }
-                            pk_p[i] = pack16(pv[0], pv[1], BF16);
-                            pk_ds[i] = pack16(dsv[0], dsv[1], BF16);
+                        }
+                        // the pairs overwrite columns this warp has already read
+                        tmem_st8(trow + kColDP + 32 * piece + 8 * half, pk_ds);
+                        if (kKeySide) tmem_st8(trow + kColS + 32 * piece + 8 * half, pk_p);
+                    }
+                } else {                             // nothing valid here: the MMA must read zeros
+                    uint32_t z[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) z[i] = 0u;
+                    tmem_st16(trow + kColDP + 32 * piece, z);
+                    if (kKeySide) tmem_st16(trow + kColS + 32 * piece, z);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(bar_sp);
+                if (warp == 0 && lane == 0) stamp(64);
+                // next chunk (innermost axis fastest; wraps to the next query head on the key side)
+                if (++ci[2] == T.nc[2]) {
+                    ci[2] = 0;
+                    if (++ci[1] == T.nc[1]) {
+                        ci[1] = 0;
+                        if (++ci[0] == T.nc[0]) ci[0] = 0;
+                    }
+                }
+            }
+
+            // ---- accumulators -> global: this warp owns 32 of the 64 channels ----
+            ok = ok && mbar_wait(bar_acc, (g - 1) & 1, abort_flag);
+            tc_fence_after();
+            // The TMEM loads are warp-collective: every lane takes part, only the stores are per row.
+            const bool live = valid_row && ok;
+#pragma unroll
+            for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
+#pragma unroll
+                for (int part = 0; part < CH / 32; ++part) {
+                    uint32_t a[32];
+                    tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + CH * piece + 32 * part, a);
+                    tmem_ld_wait();
+                    if (in_tensor) {
+                        uint4* d4 = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * DH + piece * CH + 32 * part);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                w[j] = live ? pack16(__uint_as_float(a[8 * i + 2 * j]), __uint_as_float(a[8 * i + 2 * j + 1]), BF16) : 0u;
+                            d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     }
-                    // the pairs overwrite columns this warp has already read
-                    tmem_st8(trow + kColDP + 32 * piece + 8 * half, pk_ds);
-                    if (kKeySide) tmem_st8(trow + kColS + 32 * piece + 8 * half, pk_p);
                 }
-            } else {                             // nothing valid here: the MMA must read zeros
-                uint32_t z[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) z[i] = 0u;
-                tmem_st16(trow + kColDP + 32 * piece, z);
-                if (kKeySide) tmem_st16(trow + kColS + 32 * piece, z);
             }
-            tmem_st_wait();
+            // the next tile's first accumulating MMA is issued only after every thread has passed here
             tc_fence_before();
-            mbar_arrive(bar_sp);
-            if (warp == 0 && lane == 0) stamp(64);
-            // next chunk (innermost axis fastest; wraps to the next query head on the key side)
-            if (++ci[2] == nc[2]) {
-                ci[2] = 0;
-                if (++ci[1] == nc[1]) {
-                    ci[1] = 0;
-                    if (++ci[0] == nc[0]) ci[0] = 0;
-                }
-            }
-        }
-
-        // ---- accumulators -> global: this warp owns 32 of the 64 channels ----
-        ok = ok && mbar_wait(bar_acc, (total - 1) & 1, abort_flag);
-        tc_fence_after();
-        // The TMEM loads are warp-collective: every lane takes part, only the stores are per row.
-        const bool live = valid_row && ok;
-#pragma unroll
-        for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
-#pragma unroll
-            for (int part = 0; part < CH / 32; ++part) {
-                uint32_t a[32];
-                tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + CH * piece + 32 * part, a);
-                tmem_ld_wait();
-                if (in_tensor) {
-                    uint4* d4 = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * DH + piece * CH + 32 * part);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            w[j] = live ? pack16(__uint_as_float(a[8 * i + 2 * j]), __uint_as_float(a[8 * i + 2 * j + 1]), BF16) : 0u;
-                        d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
-                }
-            }
         }
     }
 
@@ -609,8 +649,8 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
         return -2;
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= p.dil[a];
-    const dim3 grid_q((unsigned)(p.ntiles * ngroups), (unsigned)g.Hq, (unsigned)g.B);
-    const dim3 grid_k((unsigned)(p.ntiles * ngroups), (unsigned)g.Hkv, (unsigned)g.B);
+    const dim3 grid_q(persistent_grid(p.work_q, DH == 64 ? 2 : 1));
+    const dim3 grid_k(persistent_grid(p.work_kv, DH == 64 ? 2 : 1));
     auto launch = [&](auto inner) {
         constexpr int kInner = decltype(inner)::value;
         static bool attr_done = false;
