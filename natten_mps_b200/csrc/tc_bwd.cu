@@ -51,7 +51,9 @@ struct SmemB {
     static constexpr int kC1 = kR2 + kTile;                     // [kStages]
     static constexpr int kC2 = kC1 + kStages * kColTile;        // [kStages]
     static constexpr int kStats = kC2 + kStages * kColTile;     // [kStages][2][64] float
-    static constexpr int kBar = kStats + kStages * 512;
+    static constexpr int kTab = kStats + kStages * 512;         // [2] row tables: 128 x RowEntry, then a TileHead
+    static constexpr int kTabBytes = 128 * 32 + 64;
+    static constexpr int kBar = kTab + 2 * kTabBytes;
     static constexpr int kTotal = kBar + 256;
     static constexpr uint32_t kTmemCols = DH == 64 ? 256 : 512;
     static constexpr uint32_t kColA2 = kColA1 + DH;
@@ -78,6 +80,19 @@ struct BwdTile {
     int nchunks;               // chunks of the column box
     int nbox, total;           // column passes: box chunks x query heads of the group, then additional tokens
     bool active;
+};
+
+// What a compute thread needs to know about its row of a tile; written one tile ahead by the
+// helper warp (32 bytes per row), so that the compute warps do no geometry of their own.
+struct __align__(16) RowEntry {
+    short f[3], e[3];          // valid column range per axis, relative to the column box
+    int flags;                 // bit 0: row inside the (sub-grid of the) sample, bit 1: row inside the tensor
+    long long out_row;         // row of the output tensors
+    float lse2, delta;         // query side: -lse*log2(e), -delta*scale
+};
+static_assert(sizeof(RowEntry) == 32, "row table entries are 32 bytes");
+struct TileHead {
+    int active, total, nbox, nc[3];
 };
 
 template <bool kKeySide>
@@ -145,6 +160,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     const uint32_t bar_sp = sbase + Smem::kBar + 80;          // threads consumed S/dP, wrote P/dS
     const uint32_t bar_acc = sbase + Smem::kBar + 88;         // accumulating MMAs of the chunk finished
     const uint32_t bar_free = sbase + Smem::kBar + 96;        // [kStages] the same, per stage (for the statistics warp)
+    const uint32_t bar_tab_full = sbase + Smem::kBar + 128;   // [2] row table written
+    const uint32_t bar_tab_empty = sbase + Smem::kBar + 144;  // [2] row table read by every compute thread
     float* stats = reinterpret_cast<float*>(smem + Smem::kStats);
 
     if (warp == kComputeWarps) {
@@ -159,6 +176,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             mbar_init(bar_s, 1);
             mbar_init(bar_sp, kComputeWarps * 32);
             mbar_init(bar_acc, 1);
+            for (int i = 0; i < 2; ++i) { mbar_init(bar_tab_full + 8 * i, 32); mbar_init(bar_tab_empty + 8 * i, kComputeWarps * 32); }
             mbar_init_fence();
             fence_async_smem();
         }
@@ -239,6 +257,15 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                                 X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
                 }
             };
+            auto prefetch_rows = [&](const BwdTile& X) {
+#pragma unroll
+                for (int hf = 0; hf < Smem::kHalves; ++hf) {
+                    tma_prefetch_l2_5d(&tmR1, X.hy * DH + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
+                                       X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
+                    tma_prefetch_l2_5d(&tmR2, X.hy * DH + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
+                                       X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
+                }
+            };
             // Column loads run ahead of the MMAs, across tiles: their own cursor.
             BwdTile Tl;
             unsigned wl = next_active(blockIdx.x, Tl), loaded = 0;
@@ -294,7 +321,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 unsigned wnext = nwork;
                 for (int cc = 0; cc < T.total && ok; ++cc, ++g) {
                     const bool last = cc + 1 == T.total;
-                    if (last) wnext = next_active(work + gridDim.x, Tn);     // while the threads work on the chunk
+                    if (cc == 0) {             // while the threads work on the chunk: find the next tile, warm L2 with its rows
+                        wnext = next_active(work + gridDim.x, Tn);
+                        if (wnext < nwork) prefetch_rows(Tn);
+                    }
                     ok = mbar_wait(bar_sp, g & 1, abort_flag);               // S/dP consumed, P/dS stored
                     if (!ok) break;
                     stamp(0);
@@ -318,13 +348,81 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         }
     } else if (warp == kComputeWarps + 1) {
         // =====================================================================
-        // column statistics (key side): lse*log2e and delta of the chunk's queries
+        // helper warp: row tables one tile ahead; on the key side also the column statistics
+        // (lse*log2e and delta of the chunk's queries)
         // =====================================================================
-        if (kKeySide) {
-            bool ok = !*abort_flag;
-            unsigned g = 0;
-            BwdTile T;
-            for (unsigned work = next_active(blockIdx.x, T); work < nwork; work = next_active(work + gridDim.x, T)) {
+        bool ok = !*abort_flag;
+        unsigned g = 0;
+        // table of work item `work` (the item-th of this CTA) into slot item & 1
+        auto write_table = [&](unsigned work, unsigned item, const BwdTile& X) {
+            const unsigned slot = item & 1;
+            if (item >= 2) ok = ok && mbar_wait(bar_tab_empty + 8 * slot, ((item >> 1) - 1) & 1, abort_flag);
+            uint8_t* tab = smem + Smem::kTab + slot * Smem::kTabBytes;
+            RowEntry* rows = reinterpret_cast<RowEntry*>(tab);
+#pragma unroll 1
+            for (int k = 0; k < 4; ++k) {
+                const int r = lane + 32 * k;
+                int ri[3];
+                row_offsets(P, r, ri);
+                RowEntry en;
+                bool valid_row = true, in_tensor = true;
+                long long pflat = 0;
+#pragma unroll
+                for (int a = 0; a < 3; ++a) {
+                    const int xa = X.origin[a] + ri[a];
+                    const int pa = X.rg[a] + P.dil[a] * xa;
+                    if (xa >= X.Lp[a]) valid_row = false;
+                    if (pa >= P.L[a]) in_tensor = false;
+                    pflat = pflat * P.L[a] + pa;
+                    int fa = 0, ea = 0;
+                    if (X.active) {
+                        if (kKeySide) {
+                            int qlo, qhi;
+                            inverse_range(xa, X.Lp[a], P.K[a], P.causal[a], qlo, qhi);
+                            fa = qlo - X.boxlo[a];
+                            ea = qhi + 1 - X.boxlo[a];
+                        } else {
+                            const int first = P.causal[a] ? xa - (P.K[a] - 1) : ws1(xa, X.Lp[a], P.K[a]);
+                            fa = (first > 0 ? first : 0) - X.boxlo[a];
+                            ea = (first + P.K[a] < X.Lp[a] ? first + P.K[a] : X.Lp[a]) - X.boxlo[a];
+                        }
+                    }
+                    en.f[a] = (short)fa;
+                    en.e[a] = (short)ea;
+                }
+                if (!valid_row) { en.e[0] = en.f[0]; en.e[1] = en.f[1]; en.e[2] = en.f[2]; }
+                en.flags = (valid_row ? 1 : 0) | (in_tensor ? 2 : 0);
+                en.out_row = ((long long)X.b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + X.hy;
+                en.lse2 = 0.f;
+                en.delta = 0.f;
+                if (!kKeySide && valid_row && in_tensor && X.active && ok) {      // negated, pre-scaled addends
+                    en.lse2 = -lse[en.out_row] * 1.4426950408889634f;
+                    en.delta = -delta[en.out_row] * P.scale;
+                }
+                rows[r] = en;
+            }
+            if (lane == 0) {
+                TileHead* hd = reinterpret_cast<TileHead*>(tab + 128 * 32);
+                hd->active = X.active ? 1 : 0;
+                hd->total = X.total;
+                hd->nbox = X.nbox;
+                hd->nc[0] = X.nc[0]; hd->nc[1] = X.nc[1]; hd->nc[2] = X.nc[2];
+            }
+            mbar_arrive(bar_tab_full + 8 * slot);
+        };
+        BwdTile T, Tn;
+        unsigned item = 0;
+        if (blockIdx.x < nwork) {
+            bwd_tile_setup<kKeySide>(P, blockIdx.x, T);
+            write_table(blockIdx.x, 0, T);
+        }
+        for (unsigned work = blockIdx.x; work < nwork; work += gridDim.x, ++item) {
+            const unsigned wn = work + gridDim.x;
+            if (wn < nwork) {                    // the next item's table first: it is needed before this tile ends
+                bwd_tile_setup<kKeySide>(P, wn, Tn);
+                write_table(wn, item + 1, Tn);
+            }
+            if (kKeySide && T.active) {
                 int ci[3] = {0, 0, 0}, hc = T.hy * P.group;
                 for (int cc = 0; cc < T.total; ++cc, ++g) {
                     const int s = g % kStages;
@@ -355,6 +453,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                     if (++ci[2] == T.nc[2]) { ci[2] = 0; if (++ci[1] == T.nc[1]) { ci[1] = 0; if (++ci[0] == T.nc[0]) { ci[0] = 0; ++hc; } } }
                 }
             }
+            T = Tn;
         }
     } else {
         // =====================================================================
@@ -365,41 +464,19 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         unsigned g = 0;                          // chunks processed so far (all tiles)
         constexpr int kPairs = kInner > 0 ? kInner / 2 : 1;
         constexpr int kRows = kInner > 0 ? 32 / kInner : 1;
-        for (unsigned work = blockIdx.x; work < nwork; work += gridDim.x) {
-            BwdTile T;
-            bwd_tile_setup<kKeySide>(P, work, T);
-            // ---- this thread's row ----
-            int f[3] = {0, 0, 0}, e[3] = {0, 0, 0};
-            bool valid_row = true, in_tensor = true;
-            long long out_row;
-            float row_lse2 = 0.f, row_delta = 0.f;
-            {
-                int ri[3];
-                row_offsets(P, quad * 32 + lane, ri);
-                long long pflat = 0;
-#pragma unroll
-                for (int a = 0; a < 3; ++a) {
-                    const int xa = T.origin[a] + ri[a];
-                    const int pa = T.rg[a] + P.dil[a] * xa;
-                    if (xa >= T.Lp[a]) valid_row = false;
-                    if (pa >= P.L[a]) in_tensor = false;
-                    pflat = pflat * P.L[a] + pa;
-                    if (T.active) {
-                        if (kKeySide) {
-                            int qlo, qhi;
-                            inverse_range(xa, T.Lp[a], P.K[a], P.causal[a], qlo, qhi);
-                            f[a] = qlo - T.boxlo[a];
-                            e[a] = qhi + 1 - T.boxlo[a];
-                        } else {
-                            const int first = P.causal[a] ? xa - (P.K[a] - 1) : ws1(xa, T.Lp[a], P.K[a]);
-                            f[a] = (first > 0 ? first : 0) - T.boxlo[a];
-                            e[a] = (first + P.K[a] < T.Lp[a] ? first + P.K[a] : T.Lp[a]) - T.boxlo[a];
-                        }
-                    }
-                }
-                if (!valid_row) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
-                out_row = ((long long)T.b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + T.hy;
-            }
+        unsigned item = 0;
+        for (unsigned work = blockIdx.x; work < nwork; work += gridDim.x, ++item) {
+            // ---- this thread's row, from the helper warp's table ----
+            const unsigned slot = item & 1;
+            ok = mbar_wait(bar_tab_full + 8 * slot, (item >> 1) & 1, abort_flag) && ok;
+            const uint8_t* tab = smem + Smem::kTab + slot * Smem::kTabBytes;
+            const RowEntry en = reinterpret_cast<const RowEntry*>(tab)[quad * 32 + lane];
+            const TileHead T = *reinterpret_cast<const TileHead*>(tab + 128 * 32);
+            mbar_arrive(bar_tab_empty + 8 * slot);
+            const int f[3] = {en.f[0], en.f[1], en.f[2]}, e[3] = {en.e[0], en.e[1], en.e[2]};
+            const bool valid_row = en.flags & 1, in_tensor = (en.flags & 2) != 0;
+            const long long out_row = en.out_row;
+            const float row_lse2 = en.lse2, row_delta = en.delta;
             if (!T.active) {                     // padding rows get zero gradients
                 if (in_tensor) {
 #pragma unroll
@@ -410,10 +487,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                     }
                 }
                 continue;
-            }
-            if (!kKeySide && valid_row) {        // negated, pre-scaled addends
-                row_lse2 = -lse[out_row] * 1.4426950408889634f;
-                row_delta = -delta[out_row] * P.scale;
             }
             const int nbox = T.nbox;
             int ci[3] = {0, 0, 0};               // chunk index per axis, advanced without divisions
