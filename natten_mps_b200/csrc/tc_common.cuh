@@ -41,6 +41,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint (nanoseconds): the thread may sleep in hardware until the
+// phase completes or the time is up, instead of taking issue slots from the working warps.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 
 // Wait with a cycle budget.  On expiry (or when another thread already gave up)
 // the shared abort flag is raised and the wait returns false; callers keep going
@@ -53,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_hint(bar, parity, 200000u)) return true;       // up to 0.2 ms asleep per try
         if (*abort_flag) return false;
         if (clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1; return false; }
     }
