@@ -77,6 +77,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     using SM = SmemMap<DH>;
     constexpr int kStages = SM::kStages;
     constexpr int CH = DH / 2;                 // output channels per softmax thread
+    // One CTA per SM (D = 128) has the registers to keep a chunk's scores: they are read from TMEM once
+    // and the next Q K^T is issued as soon as every thread holds them.  D = 64 reads them twice.
+    constexpr bool kKeepScores = DH == 128;
     constexpr uint32_t kColO = SM::kColO, kTmemCols = SM::kTmemCols;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -135,6 +138,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const uint32_t bar_s = sbase + SM::kBar + 32;
     const uint32_t bar_sp = sbase + SM::kBar + 40;
     const uint32_t bar_o = sbase + SM::kBar + 48;
+    const uint32_t bar_sr = sbase + SM::kBar + 56;      // (kKeepScores) every softmax thread holds S(c) in registers
 
     // The issuing warp sets up the barriers, allocates TMEM and starts the first loads right away,
     // so they are in flight while the softmax warps are still working out their row geometry.
@@ -175,6 +179,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             mbar_init(bar_s, 1);
             mbar_init(bar_sp, 256);
             mbar_init(bar_o, 1);
+            mbar_init(bar_sr, 256);
             mbar_init_fence();
             fence_async_smem();
             tw1 = clock64();
@@ -250,12 +255,13 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 mma_commit(bar_s);
             };
             auto issue_pv = [&](int c) {
-                // V read MN-major: 16 key rows per k-step, the second 64-channel block sits kHalf bytes further
+                // V read MN-major: 16 key rows per k-step, the second 64-channel block sits kHalf bytes further.
+                // O stays in TMEM for the whole tile: every chunk after the first adds to it.
                 const uint64_t dv0 = smem_desc(sbase + SM::kV + (c % kStages) * SM::kTile, SM::kHalf, 1024);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kChunk / 16; ++ks)
-                    mma_ts(tmem + kColO, tmem + kColP + 8 * ks, dv0 + 128 * ks, idesc_pv, ks > 0);
+                    mma_ts(tmem + kColO, tmem + kColP + 8 * ks, dv0 + 128 * ks, idesc_pv, c > 0 || ks > 0);
                 mma_commit(bar_o);
             };
 
@@ -266,10 +272,19 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             if (ok) issue_qk(0);
             stamp(0);
             for (int c = 0; c < nch && ok; ++c) {
+                if (kKeepScores) {       // S(c) sits in the threads' registers: the next scores may overwrite it
+                    ok = mbar_wait(bar_sr, c & 1, abort_flag);
+                    if (!ok) break;
+                    if (c + 1 < nch) {
+                        ok = mbar_wait(bar_kv + 8 * ((c + 1) % kStages), ((c + 1) / kStages) & 1, abort_flag);
+                        if (!ok) break;
+                        issue_qk(c + 1);
+                    }
+                }
                 ok = mbar_wait(bar_sp, c & 1, abort_flag);           // S(c) consumed, P(c) stored
                 if (!ok) break;
                 stamp(0);
-                if (c + 1 < nch) {                                   // next scores first: the threads wait for them
+                if (!kKeepScores && c + 1 < nch) {                   // next scores first: the threads wait for them
                     ok = mbar_wait(bar_kv + 8 * ((c + 1) % kStages), ((c + 1) / kStages) & 1, abort_flag);
                     if (!ok) break;
                     issue_qk(c + 1);
@@ -289,19 +304,19 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         // =====================================================================
         const uint32_t trow = tmem + (static_cast<uint32_t>(quad * 32) << 16);
         const int row = quad * 32 + lane;
-        float m = -INFINITY, l = 0.f;
-        float acc[CH];
-#pragma unroll
-        for (int i = 0; i < CH; ++i) acc[i] = 0.f;
         bool ok = true;
+        // O accumulates in TMEM over the tile's chunks.  m is the stabiliser the stored
+        // probabilities use; it only moves (and O, l are rescaled) when a chunk's maximum
+        // exceeds it by more than 2^8, so probabilities stay below 256.
+        float m = -INFINITY, l = 0.f;
         int ci[3] = {0, 0, 0};
-        uint32_t colbits = 0u;                   // separable geometry: valid columns of one inner row
+        uint32_t colbits = 0u;               // separable geometry: valid columns of one inner row
         int cached_c2 = -1;
 
         for (int c = 0; c < nch; ++c) {
             // ---- validity words of this thread's two 32-column pieces ----
             uint32_t words[2];
-            if (c >= nnb) {                       // additional tokens: every live row sees the first n_extra columns
+            if (c >= nnb) {                // additional tokens: every live row sees the first n_extra columns
 #pragma unroll
                 for (int pc = 0; pc < 2; ++pc)
                     words[pc] = valid_q ? low_bits(P.n_extra - ((c - nnb) * kChunk + 64 * team + 32 * pc)) : 0u;
@@ -311,7 +326,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
                     lo2 = lo2 > 0 ? lo2 : 0;
                     hi2 = hi2 < kInner ? hi2 : kInner;
-                    colbits = hi2 > lo2 ? (((hi2 - lo2 >= 32) ? 0xffffffffu : ((1u << (hi2 - lo2)) - 1u)) << lo2) : 0u;
+                    colbits = hi2 > lo2 ? (low_bits(hi2 - lo2) << lo2) : 0u;
                 }
 #pragma unroll
                 for (int pc = 0; pc < 2; ++pc) {
@@ -331,28 +346,50 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 for (int pc = 0; pc < 2; ++pc) words[pc] = piece_word(P, ci, 2 * team + pc, f, e);
             }
 
-            if (warp == 0 && lane == 0) stamp(64);
             ok = ok && mbar_wait(bar_s, c & 1, abort_flag);
             tc_fence_after();
-            if (warp == 0 && lane == 0) stamp(64);
-
-            // ---- pass 1: maximum over the valid columns of this half, then agree with the other half ----
+            const bool any[2] = {__any_sync(0xffffffffu, words[0] != 0u) != 0, __any_sync(0xffffffffu, words[1] != 0u) != 0};
+            uint32_t s0[kKeepScores ? 32 : 1], s1[kKeepScores ? 32 : 1];      // the chunk's scores (kKeepScores)
             float mc = -INFINITY;
-#pragma unroll
-            for (int pc = 0; pc < 2; ++pc) {
-                if (!__any_sync(0xffffffffu, words[pc] != 0u)) continue;
-                uint32_t s[32];
-                tmem_ld32(trow + kColS + 64 * team + 32 * pc, s);
+            if constexpr (kKeepScores) {
+                if (any[0]) tmem_ld32(trow + kColS + 64 * team, s0);
+                if (any[1]) tmem_ld32(trow + kColS + 64 * team + 32, s1);
                 tmem_ld_wait();
-                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+                // columns outside the row's neighbourhood become -inf once, here
+                auto masked_max = [&](uint32_t (&s)[kKeepScores ? 32 : 1], uint32_t w) {
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    m0 = fmaxf(m0, ((words[pc] >> i) & 1u) ? __uint_as_float(s[i]) : -INFINITY);
-                    m1 = fmaxf(m1, ((words[pc] >> (i + 1)) & 1u) ? __uint_as_float(s[i + 1]) : -INFINITY);
-                    m2 = fmaxf(m2, ((words[pc] >> (i + 2)) & 1u) ? __uint_as_float(s[i + 2]) : -INFINITY);
-                    m3 = fmaxf(m3, ((words[pc] >> (i + 3)) & 1u) ? __uint_as_float(s[i + 3]) : -INFINITY);
+                    for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (!((w >> (i + j)) & 1u)) s[i + j] = 0xff800000u;
+                        m0 = fmaxf(m0, __uint_as_float(s[i]));
+                        m1 = fmaxf(m1, __uint_as_float(s[i + 1]));
+                        m2 = fmaxf(m2, __uint_as_float(s[i + 2]));
+                        m3 = fmaxf(m3, __uint_as_float(s[i + 3]));
+                    }
+                    mc = fmaxf(mc, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+                };
+                if (any[0]) masked_max(s0, words[0]);
+                if (any[1]) masked_max(s1, words[1]);
+            } else {
+                // ---- pass 1: maximum over the valid columns of this half ----
+#pragma unroll
+                for (int pc = 0; pc < 2; ++pc) {
+                    if (!any[pc]) continue;
+                    uint32_t s[32];
+                    tmem_ld32(trow + kColS + 64 * team + 32 * pc, s);
+                    tmem_ld_wait();
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        m0 = fmaxf(m0, ((words[pc] >> i) & 1u) ? __uint_as_float(s[i]) : -INFINITY);
+                        m1 = fmaxf(m1, ((words[pc] >> (i + 1)) & 1u) ? __uint_as_float(s[i + 1]) : -INFINITY);
+                        m2 = fmaxf(m2, ((words[pc] >> (i + 2)) & 1u) ? __uint_as_float(s[i + 2]) : -INFINITY);
+                        m3 = fmaxf(m3, ((words[pc] >> (i + 3)) & 1u) ? __uint_as_float(s[i + 3]) : -INFINITY);
+                    }
+                    mc = fmaxf(mc, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
                 }
-                mc = fmaxf(mc, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
             }
             if (!ok) mc = -INFINITY;
             {
@@ -365,43 +402,68 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 const uint32_t other = static_cast<uint32_t>(xmax[(1 - team) * 128 + row]) << 16;
                 mc = fmaxf(__uint_as_float(bits), __uint_as_float(other));
             }
-            if (warp == 0 && lane == 0) stamp(64);
-            const float m_new = fmaxf(m, mc);
-            const float alpha = (m == -INFINITY) ? 0.f : fast_exp2((m - m_new) * P.scale_log2);
-            const float mb = (m_new == -INFINITY) ? 0.f : m_new * P.scale_log2;
+            if constexpr (kKeepScores) {
+                // S(c) is in registers and the partner's maximum has been read: the next scores may
+                // land (they are what lets this thread overwrite its exchange slot again).
+                tc_fence_before();
+                mbar_arrive(bar_sr);
+            }
 
-            // ---- fold the previous chunk's P V (this team's 32 channels) ----
+            // ---- P(c-1) V has finished: P may be rewritten, O may be rescaled ----
             if (c > 0) {
                 ok = ok && mbar_wait(bar_o, (c - 1) & 1, abort_flag);
                 tc_fence_after();
-#pragma unroll
-                for (int part = 0; part < CH / 32; ++part) {
-                    uint32_t o[32];
-                    tmem_ld32(trow + kColO + CH * team + 32 * part, o);
+            }
+            bool grow = false;
+            if (mc > -INFINITY) {
+                if (m == -INFINITY) m = mc;
+                else grow = (mc - m) * P.scale_log2 > 8.f;
+            }
+            if (__any_sync(0xffffffffu, grow)) {          // rare: both halves of a row decide alike
+                const float fac = grow ? fast_exp2((m - mc) * P.scale_log2) : 1.f;
+#pragma unroll 1
+                for (int part = 0; part < CH / 16; ++part) {
+                    uint32_t o[16];
+                    tmem_ld16(trow + kColO + CH * team + 16 * part, o);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[32 * part + i] = (acc[32 * part + i] + __uint_as_float(o[i])) * alpha;
+                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * fac);
+                    tmem_st16(trow + kColO + CH * team + 16 * part, o);
                 }
+                l *= fac;
+                if (grow) m = mc;
             }
+            const float mb = (m == -INFINITY) ? 0.f : m * P.scale_log2;
 
-            if (warp == 0 && lane == 0) stamp(64);
-            // ---- pass 2: probabilities -> TMEM (16-bit pairs), row sum of this half ----
+            // ---- probabilities -> TMEM (16-bit pairs), row sum of this half ----
             float r0 = 0.f, r1 = 0.f;
 #pragma unroll
             for (int pc = 0; pc < 2; ++pc) {
                 uint32_t packed[16];
-                if (__any_sync(0xffffffffu, words[pc] != 0u)) {
-                    uint32_t s[32];
-                    tmem_ld32(trow + kColS + 64 * team + 32 * pc, s);
-                    tmem_ld_wait();
+                if (any[pc]) {
+                    if constexpr (kKeepScores) {
+                        const uint32_t (&s)[kKeepScores ? 32 : 1] = pc == 0 ? s0 : s1;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float x0 = ((words[pc] >> (2 * i)) & 1u) ? fmaf(__uint_as_float(s[2 * i]), P.scale_log2, -mb) : -INFINITY;
-                        const float x1 = ((words[pc] >> (2 * i + 1)) & 1u) ? fmaf(__uint_as_float(s[2 * i + 1]), P.scale_log2, -mb) : -INFINITY;
-                        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-                        r0 += p0;
-                        r1 += p1;
-                        packed[i] = cvt_pack<BF16>(p0, p1);
+                        for (int i = 0; i < 16; ++i) {
+                            const float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * i]), P.scale_log2, -mb));
+                            const float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), P.scale_log2, -mb));
+                            r0 += p0;
+                            r1 += p1;
+                            packed[i] = cvt_pack<BF16>(p0, p1);
+                        }
+                    } else {                                         // pass 2 over TMEM
+                        uint32_t s[32];
+                        tmem_ld32(trow + kColS + 64 * team + 32 * pc, s);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float x0 = ((words[pc] >> (2 * i)) & 1u) ? fmaf(__uint_as_float(s[2 * i]), P.scale_log2, -mb) : -INFINITY;
+                            const float x1 = ((words[pc] >> (2 * i + 1)) & 1u) ? fmaf(__uint_as_float(s[2 * i + 1]), P.scale_log2, -mb) : -INFINITY;
+                            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                            r0 += p0;
+                            r1 += p1;
+                            packed[i] = cvt_pack<BF16>(p0, p1);
+                        }
                     }
                 } else {
 #pragma unroll
@@ -409,45 +471,46 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 }
                 tmem_st16(trow + kColP + 32 * team + 16 * pc, packed);
             }
-            l = l * alpha + (ok ? r0 + r1 : 0.f);
-            m = m_new;
+            l += ok ? r0 + r1 : 0.f;
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(bar_sp);
-            if (warp == 0 && lane == 0) stamp(64);
             if (++ci[2] == nc[2]) { ci[2] = 0; if (++ci[1] == nc[1]) { ci[1] = 0; ++ci[0]; } }
         }
 
-        // ---- last chunk's P V, combine the two halves' sums, normalise, write out ----
+        // ---- combine the two halves' sums while the last P V runs, then normalise and write out ----
+        // Every Q K^T has finished and no load is in flight, so the first K stage can carry the sums.
+        {
+            float* xsum = reinterpret_cast<float*>(smem + SM::kK);
+            xsum[team * 128 + row] = l;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+            l += xsum[(1 - team) * 128 + row];
+        }
         ok = ok && mbar_wait(bar_o, (nch - 1) & 1, abort_flag);
         tc_fence_after();
+        {
+            const bool live = valid_q && ok;
 #pragma unroll
-        for (int part = 0; part < CH / 32; ++part) {
-            uint32_t o[32];
-            tmem_ld32(trow + kColO + CH * team + 32 * part, o);
-            tmem_ld_wait();
+            for (int part = 0; part < CH / 32; ++part) {
+                uint32_t o[32];
+                tmem_ld32(trow + kColO + CH * team + 32 * part, o);
+                tmem_ld_wait();
+                const float inv = (live && l > 0.f) ? 1.f / l : 0.f;
+                if (in_tensor) {
+                    uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH + team * CH + 32 * part);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[32 * part + i] += __uint_as_float(o[i]);
-        }
-        // every MMA has finished, so the first K stage can carry the partial row sums
-        float* xsum = reinterpret_cast<float*>(smem + SM::kK);
-        xsum[team * 128 + row] = l;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
-        l += xsum[(1 - team) * 128 + row];
-        if (in_tensor) {
-            const bool live = valid_q && l > 0.f && ok;
-            const float inv = live ? 1.f / l : 0.f;
-            uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH + team * CH);
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t w[4];
 #pragma unroll
-            for (int i = 0; i < CH / 8; ++i) {
-                uint32_t w[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    w[j] = live ? cvt_pack<BF16>(acc[8 * i + 2 * j] * inv, acc[8 * i + 2 * j + 1] * inv) : 0u;
-                o4[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int j = 0; j < 4; ++j)
+                            w[j] = cvt_pack<BF16>(__uint_as_float(o[8 * i + 2 * j]) * inv, __uint_as_float(o[8 * i + 2 * j + 1]) * inv);
+                        o4[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
             }
             // natural-log lse of scale * logits
-            if (team == 0) lse[out_row] = live ? (m * P.scale_log2 + log2f(l)) * 0.6931471805599453f : 0.f;
+            if (in_tensor && team == 0)
+                lse[out_row] = (live && l > 0.f) ? (m * P.scale_log2 + log2f(l)) * 0.6931471805599453f : 0.f;
         }
     }
 
