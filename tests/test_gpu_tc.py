@@ -139,3 +139,38 @@ def test_tc_additional_tokens_match_simt(case, dtype):
         err = (a.float() - r.float()).abs().max().item()
         scale = max(1.0, r.float().abs().max().item())
         assert err <= 2e-2 * scale, f"{name} differs by {err} (scale {scale})"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("spatial,ks", [((700,), (255,)), ((40, 48), (13, 13))], ids=["1d", "2d"])
+def test_tc_forward_rescales_when_later_chunks_dominate(spatial, ks, D, dtype):
+    """Scores that grow steeply along the key axis: every later chunk of a tile raises the row
+    maximum by far more than the 2^8 the stored probabilities may exceed their stabiliser by,
+    so the output accumulated in TMEM has to be rescaled chunk after chunk."""
+    rank = len(spatial)
+    B, H = 2, 2
+    g = torch.Generator(device="cpu").manual_seed(23)
+    slope = 12.0 / 128.0 if rank == 1 else 1.0          # per key along the innermost axis: > 8 / log2(e) per chunk
+    ramp = (torch.arange(spatial[-1], dtype=torch.float32) * slope).reshape((1,) * (rank - 1) + (spatial[-1], 1, 1))
+    q = torch.randn((B, *spatial, H, D), generator=g) * 0.1 + 1.0
+    k = torch.randn((B, *spatial, H, D), generator=g) * 0.1 + ramp.unsqueeze(0) / (D ** 0.5)
+    v = torch.randn((B, *spatial, H, D), generator=g)
+    q, k, v = [t.to(dtype).cuda() for t in (q, k, v)]
+    args = (q, k, v, ks, (1,) * rank, (1,) * rank, (False,) * rank, D ** -0.5)
+    try:
+        _cabi.set_force("simt")
+        ref_out, ref_lse = _backend.fused_forward(*args)
+        _cabi.set_force("tc")
+        out, lse = _backend.fused_forward(*args)
+        assert _cabi.last_path() == "tcgen05"
+    finally:
+        _cabi.set_force(None)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    # the window's scores really span far more than 2^8
+    assert (ref_lse.max() - ref_lse.min()).item() > 20.0
+    err = (out.float() - ref_out.float()).abs().max().item()
+    lerr = ((lse - ref_lse).abs() / ref_lse.abs().clamp(min=1.0)).max().item()
+    assert err <= 2e-2, f"out differs by {err}"
+    assert lerr <= 2e-3, f"lse differs by {lerr} (relative)"
