@@ -123,7 +123,7 @@ class ClockSampler:
 
 # DRAM bytes (read + write) the backward / forward kernels move per launch set at config 2, batch 8,
 # from the committed ncu capture (profiles/c2_na2d_7x7_bf16_tc_kernels_ncu_full.md); scales with batch.
-NCU_TRAFFIC_C2 = {"backward": 394.8e6, "forward": 116.1e6}
+NCU_TRAFFIC_C2 = {"backward": 390.2e6, "forward": 114.2e6}
 
 
 def measured_peaks():
