@@ -634,6 +634,167 @@ extra_grad_partial_kernel(const __grid_constant__ Geo g, const T* __restrict__ q
     for (int i = threadIdx.x; i < ne * W; i += blockDim.x) dst[i] = red[i];
 }
 
+// The same partial sums for 16-bit inputs, organised as two small matrix products per tile of
+// 64 (query, head-of-group) rows staged in shared memory:
+//   phase 1  thread = (row, 4 tokens):   s = q . ek,  dp = dout . ev  ->  p, ds   (shared memory)
+//   phase 2  thread = (channel, dEK|dEV): acc[token] += ds[row][token] * q[row][channel]   (or p * dout)
+// 256 threads, about 50 registers, 61 KB of shared memory: several blocks per SM, where the
+// row-per-warp kernel above keeps 128 accumulators per thread and runs one.
+constexpr int kExtraTileRows = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+extra_grad_tile_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T* __restrict__ ek,
+                       const T* __restrict__ ev, const float* __restrict__ lse,
+                       const float* __restrict__ delta, const T* __restrict__ dout,
+                       const float* __restrict__ dlse, float* __restrict__ partial, int e0, int ne)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int D = g.D, Dv = g.Dv, W = D + Dv;
+    const int qstr = D + 8, vstr = Dv + 8;                     // padded row strides (elements): no bank conflicts
+    T* qt = reinterpret_cast<T*>(smem_raw);                     // [64][qstr]
+    T* gt = qt + kExtraTileRows * qstr;                         // [64][vstr]
+    float* eks = reinterpret_cast<float*>(gt + kExtraTileRows * vstr);   // [16][D]
+    float* evs = eks + kExtraGroup * D;                         // [16][Dv]
+    float* pp = evs + kExtraGroup * Dv;                         // [64][16]  p
+    float* dss = pp + kExtraTileRows * kExtraGroup;             // [64][16]  ds
+    float* rl = dss + kExtraTileRows * kExtraGroup;             // [64] lse
+    float* rd = rl + kExtraTileRows;                            // [64] delta
+    long long* qoff = reinterpret_cast<long long*>(rd + kExtraTileRows);   // [64] element offset of the q row, -1 = no row
+    long long* orow = qoff + kExtraTileRows;                    // [64] row of dout / lse / delta
+
+    const int tid = threadIdx.x;
+    const int seg = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    for (int i = tid; i < kExtraGroup * D; i += 256)
+        eks[i] = (i / D < ne) ? to_acc(ek[(((long long)b * g.n_extra + e0 + i / D) * g.Hkv + hk) * D + i % D]) : 0.f;
+    for (int i = tid; i < kExtraGroup * Dv; i += 256)
+        evs[i] = (i / Dv < ne) ? to_acc(ev[(((long long)b * g.n_extra + e0 + i / Dv) * g.Hkv + hk) * Dv + i % Dv]) : 0.f;
+
+    float acc[kExtraGroup];
+#pragma unroll
+    for (int e = 0; e < kExtraGroup; ++e) acc[e] = 0.f;
+    const float scale = (float)g.scale;
+    const long long total = g.otot * g.group;
+    long long end = (long long)(seg + 1) * kExtraSegRows;
+    if (end > total) end = total;
+
+    for (long long base = (long long)seg * kExtraSegRows; base < end; base += kExtraTileRows) {
+        __syncthreads();                                        // the previous tile has been consumed
+        // ---- which rows, where ----
+        bool mine_inside = false;
+        if (tid < kExtraTileRows) {
+            const long long cnd = base + tid;
+            long long qo = -1, ro = 0;
+            if (cnd < end) {
+                const int gi = (int)(cnd / g.otot);
+                QueryCtx c;
+                decode_query(g, ((long long)b * g.otot + cnd % g.otot) * g.Hq + hk * g.group + gi, c);
+                if (c.inside) {
+                    qo = c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
+                    ro = c.row;
+                    mine_inside = true;
+                }
+            }
+            qoff[tid] = qo;
+            orow[tid] = ro;
+            rl[tid] = mine_inside ? lse[ro] : 0.f;
+            rd[tid] = mine_inside ? delta[ro] - (dlse ? dlse[ro] : 0.f) : 0.f;
+        }
+        if (!__syncthreads_or(mine_inside ? 1 : 0)) continue;   // nothing of this tile is inside its sample
+        // ---- stage the rows (16 bytes at a time; rows outside are zero) ----
+        for (int i = tid; i < kExtraTileRows * (D / 8); i += 256) {
+            const int r = i / (D / 8), c8 = i % (D / 8);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (qoff[r] >= 0) v = *reinterpret_cast<const uint4*>(q + qoff[r] + 8 * c8);
+            *reinterpret_cast<uint4*>(qt + r * qstr + 8 * c8) = v;
+        }
+        for (int i = tid; i < kExtraTileRows * (Dv / 8); i += 256) {
+            const int r = i / (Dv / 8), c8 = i % (Dv / 8);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (qoff[r] >= 0) v = *reinterpret_cast<const uint4*>(dout + orow[r] * Dv + 8 * c8);
+            *reinterpret_cast<uint4*>(gt + r * vstr + 8 * c8) = v;
+        }
+        __syncthreads();
+        // ---- phase 1: probabilities and dS of 4 tokens for one row ----
+        {
+            const int r = tid & (kExtraTileRows - 1), eg = tid >> 6;
+            float sv[4] = {0.f, 0.f, 0.f, 0.f}, dp[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int c8 = 0; c8 < D / 8; ++c8) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(qt + r * qstr + 8 * c8);
+                const T* x = reinterpret_cast<const T*>(&raw);
+                float xf[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xf[i] = to_acc(x[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 a = *reinterpret_cast<const float4*>(eks + (4 * eg + j) * D + 8 * c8);
+                    const float4 c = *reinterpret_cast<const float4*>(eks + (4 * eg + j) * D + 8 * c8 + 4);
+                    sv[j] += xf[0] * a.x + xf[1] * a.y + xf[2] * a.z + xf[3] * a.w + xf[4] * c.x + xf[5] * c.y + xf[6] * c.z + xf[7] * c.w;
+                }
+            }
+            for (int c8 = 0; c8 < Dv / 8; ++c8) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(gt + r * vstr + 8 * c8);
+                const T* x = reinterpret_cast<const T*>(&raw);
+                float xf[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xf[i] = to_acc(x[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 a = *reinterpret_cast<const float4*>(evs + (4 * eg + j) * Dv + 8 * c8);
+                    const float4 c = *reinterpret_cast<const float4*>(evs + (4 * eg + j) * Dv + 8 * c8 + 4);
+                    dp[j] += xf[0] * a.x + xf[1] * a.y + xf[2] * a.z + xf[3] * a.w + xf[4] * c.x + xf[5] * c.y + xf[6] * c.z + xf[7] * c.w;
+                }
+            }
+            const bool live = qoff[r] >= 0;
+            float4 pv, dv;
+            float* pa = &pv.x;
+            float* da = &dv.x;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool on = live && 4 * eg + j < ne;
+                const float pj = on ? expf(sv[j] * scale - rl[r]) : 0.f;
+                pa[j] = pj;
+                da[j] = on ? pj * (dp[j] - rd[r]) * scale : 0.f;
+            }
+            *reinterpret_cast<float4*>(pp + r * kExtraGroup + 4 * eg) = pv;
+            *reinterpret_cast<float4*>(dss + r * kExtraGroup + 4 * eg) = dv;
+        }
+        __syncthreads();
+        // ---- phase 2: one channel of dEK (threads 0-127) or dEV (128-255), all 16 tokens ----
+        {
+            const int which = tid >> 7, d = tid & 127;
+            if (d < (which ? Dv : D)) {
+                const T* tile = which ? gt : qt;
+                const int str = which ? vstr : qstr;
+                const float* wsrc = which ? pp : dss;
+#pragma unroll 4
+                for (int r = 0; r < kExtraTileRows; ++r) {
+                    const float x = to_acc(tile[r * str + d]);
+                    const float4* w4 = reinterpret_cast<const float4*>(wsrc + r * kExtraGroup);
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const float4 w = w4[k4];
+                        acc[4 * k4] += w.x * x;
+                        acc[4 * k4 + 1] += w.y * x;
+                        acc[4 * k4 + 2] += w.z * x;
+                        acc[4 * k4 + 3] += w.w * x;
+                    }
+                }
+            }
+        }
+    }
+    // ---- this block's partial sums: [token][D | Dv] ----
+    {
+        const int which = tid >> 7, d = tid & 127;
+        float* dst = partial + ((((long long)b * g.Hkv + hk) * gridDim.x + seg) * kExtraGroup) * W;
+        if (d < (which ? Dv : D)) {
+#pragma unroll
+            for (int e = 0; e < kExtraGroup; ++e)
+                if (e < ne) dst[e * W + (which ? D + d : d)] = acc[e];
+        }
+    }
+}
+
 template <typename T>
 __global__ void extra_grad_reduce_kernel(const __grid_constant__ Geo g, const float* __restrict__ partial,
                                          int nseg, int e0, int ne, T* __restrict__ dek, T* __restrict__ dev)
@@ -868,7 +1029,26 @@ bool launch_extra_fast(const Geo& g, const void* q, const void* ek, const void* 
         const int ne = g.n_extra - e0 < kExtraGroup ? g.n_extra - e0 : kExtraGroup;
         const dim3 grid((unsigned)nseg, (unsigned)g.Hkv, (unsigned)g.B);
         const int dmax = g.D > g.Dv ? g.D : g.Dv;
-        if (dmax <= 32)
+        bool tiled = false;
+        if constexpr (sizeof(T) == 2) {
+            // rows must be readable 16 bytes at a time
+            const bool aligned = g.D % 8 == 0 && g.Dv % 8 == 0 && g.qs[0] % 8 == 0 && g.qs[1] % 8 == 0 && g.qs[2] % 8 == 0 &&
+                                 ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(dout)) & 15u) == 0;
+            if (aligned) {
+                const size_t tsmem = (size_t)kExtraTileRows * (g.D + 8 + g.Dv + 8) * sizeof(T) + (size_t)kExtraGroup * W * sizeof(float) +
+                                     (size_t)kExtraTileRows * (2 * kExtraGroup + 2) * sizeof(float) + (size_t)kExtraTileRows * 2 * sizeof(long long);
+                static bool attr_done = false;
+                if (!attr_done) {
+                    cudaFuncSetAttribute(extra_grad_tile_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+                    attr_done = true;
+                }
+                extra_grad_tile_kernel<T><<<grid, 256, tsmem, s>>>(g, (const T*)q, (const T*)ek, (const T*)ev, (const float*)lse,
+                    (const float*)delta, (const T*)dout, (const float*)dlse, (float*)partial, e0, ne);
+                tiled = true;
+            }
+        }
+        if (tiled) {
+        } else if (dmax <= 32)
             extra_grad_partial_kernel<T, 1><<<grid, kWarps * 32, smem, s>>>(g, (const T*)q, (const T*)ek, (const T*)ev,
                 (const float*)lse, (const float*)delta, (const T*)dout, (const float*)dlse, (float*)partial, e0, ne);
         else if (dmax <= 64)

@@ -382,11 +382,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     tmem_ld_wait();
                     float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        m0 = fmaxf(m0, ((words[pc] >> i) & 1u) ? __uint_as_float(s[i]) : -INFINITY);
-                        m1 = fmaxf(m1, ((words[pc] >> (i + 1)) & 1u) ? __uint_as_float(s[i + 1]) : -INFINITY);
-                        m2 = fmaxf(m2, ((words[pc] >> (i + 2)) & 1u) ? __uint_as_float(s[i + 2]) : -INFINITY);
-                        m3 = fmaxf(m3, ((words[pc] >> (i + 3)) & 1u) ? __uint_as_float(s[i + 3]) : -INFINITY);
+                    for (int i = 0; i < 32; i += 4) {        // guarded maxima: one predicate and one max per column
+                        if ((words[pc] >> i) & 1u) m0 = fmaxf(m0, __uint_as_float(s[i]));
+                        if ((words[pc] >> (i + 1)) & 1u) m1 = fmaxf(m1, __uint_as_float(s[i + 1]));
+                        if ((words[pc] >> (i + 2)) & 1u) m2 = fmaxf(m2, __uint_as_float(s[i + 2]));
+                        if ((words[pc] >> (i + 3)) & 1u) m3 = fmaxf(m3, __uint_as_float(s[i + 3]));
                     }
                     mc = fmaxf(mc, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
                 }
@@ -457,9 +457,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const float x0 = ((words[pc] >> (2 * i)) & 1u) ? fmaf(__uint_as_float(s[2 * i]), P.scale_log2, -mb) : -INFINITY;
-                            const float x1 = ((words[pc] >> (2 * i + 1)) & 1u) ? fmaf(__uint_as_float(s[2 * i + 1]), P.scale_log2, -mb) : -INFINITY;
-                            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                            float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * i]), P.scale_log2, -mb));
+                            float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), P.scale_log2, -mb));
+                            if (!((words[pc] >> (2 * i)) & 1u)) p0 = 0.f;
+                            if (!((words[pc] >> (2 * i + 1)) & 1u)) p1 = 0.f;
                             r0 += p0;
                             r1 += p1;
                             packed[i] = cvt_pack<BF16>(p0, p1);
