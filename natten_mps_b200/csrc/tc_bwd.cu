@@ -9,13 +9,15 @@
 //     kernels), for every query head of the GQA group.  S^T = K Q^T, dP^T = V dO^T;
 //     dV += P^T dO, dK += dS^T Q.  Per-column lse / delta are staged in shared memory
 //     by a helper warp.
-// The row accumulators live in TMEM for the whole CTA, so dK/dV are reduced in a
+// The row accumulators live in TMEM for the whole tile, so dK/dV are reduced in a
 // fixed order: results are bit-reproducible, no atomics.
 //
-// Chunks are 64 columns wide so that a CTA needs only 256 TMEM columns and 98 KB of
+// Chunks are 64 columns wide so that a CTA needs only 256 TMEM columns and 107 KB of
 // shared memory: two CTAs share an SM and one computes while the other waits for its
-// MMAs or loads.  Warps: 8 compute warps (two per TMEM lane quadrant, each owns one
-// 32-column piece of the chunk), one TMA + MMA issuing warp, one column-statistics warp.
+// MMAs or loads.  The grid is persistent (CTAs walk the tiles), so barriers, TMEM and the
+// column-stage ring are set up once and the next tile's loads run ahead.  Warps: 8 compute
+// warps (two per TMEM lane quadrant, each owns one 32-column piece of the chunk), one TMA + MMA
+// issuing warp, one helper warp (per-row tables one tile ahead; column statistics on the key side).
 // TMEM: S [0,64)  dP [64,128)  acc1 [128,192)  acc2 [192,256).  The 16-bit P and dS that
 // feed the accumulating MMAs overwrite the first half of the S / dP columns of the piece
 // they were computed from (same warp, after it has read them).
