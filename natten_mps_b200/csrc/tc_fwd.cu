@@ -90,35 +90,57 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int prior_abort = *reinterpret_cast<volatile int*>(P.status);   // loaded early, used at barrier set-up
 
     // ---- CTA geometry -------------------------------------------------------
-    int rg[3], origin[3], Lp[3], lo[3], nc[3];
-    const bool cta_active = cta_geometry(P, blockIdx.x, b, rg, origin, Lp);
+    // origin[] counts queries of the dilation group; query i of an axis sits at sub-grid index
+    // x0 + sx * i (every index when the output stride is 1).
+    int rg[3], origin[3], Lp[3], lo[3], nc[3], x0[3], sx[3], nq[3], nqf[3];
+    bool cta_active = cta_geometry(P, blockIdx.x, b, rg, origin, Lp);
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+        sx[a] = P.qstep[a];
+        x0[a] = P.qx0[a][rg[a]];
+        const int lpf = (P.L[a] - rg[a] + P.dil[a] - 1) / P.dil[a];          // sub-grid length of the whole tensor
+        if (x0[a] < 0) {                         // no output position falls into this dilation group
+            nq[a] = 0;
+            nqf[a] = 0;
+            x0[a] = 0;
+        } else if (sx[a] == 1) {
+            nq[a] = Lp[a];
+            nqf[a] = rg[a] < P.L[a] ? lpf : 0;
+        } else {
+            nq[a] = (x0[a] >= 0 && x0[a] < Lp[a]) ? (Lp[a] - x0[a] + sx[a] - 1) / sx[a] : 0;
+            nqf[a] = (x0[a] >= 0 && x0[a] < lpf) ? (lpf - x0[a] + sx[a] - 1) / sx[a] : 0;
+        }
+        if (origin[a] >= nq[a]) cta_active = false;
+    }
     int nnb = 1;                             // chunks of the neighbourhood box
     if (cta_active) {
 #pragma unroll
         for (int a = 0; a < 3; ++a) {
-            const int last = origin[a] + P.tile[a] - 1 < Lp[a] - 1 ? origin[a] + P.tile[a] - 1 : Lp[a] - 1;
-            lo[a] = P.causal[a] ? origin[a] - (P.K[a] - 1) : tc_window_start(origin[a], Lp[a], P.K[a]);
-            const int hi = P.causal[a] ? last : tc_window_start(last, Lp[a], P.K[a]) + P.K[a] - 1;
+            const int lastq = origin[a] + P.tile[a] - 1 < nq[a] - 1 ? origin[a] + P.tile[a] - 1 : nq[a] - 1;
+            const int xf = x0[a] + sx[a] * origin[a], xl = x0[a] + sx[a] * lastq;
+            lo[a] = P.causal[a] ? xf - (P.K[a] - 1) : tc_window_start(xf, Lp[a], P.K[a]);
+            const int hi = P.causal[a] ? xl : tc_window_start(xl, Lp[a], P.K[a]) + P.K[a] - 1;
             nc[a] = chunks_along(P, a, hi - lo[a] + 1);       // chunks this tile really needs
             nnb *= nc[a];
         }
     }
     const int nch = nnb + ((P.n_extra + kChunk - 1) >> 7);   // then the additional tokens, 128 per chunk
 
-    if (!cta_active) {                       // nothing to attend: padding rows are zero
+    if (!cta_active) {                       // nothing to attend: rows that exist in the output are zero
         if (warp < 8) {
             int qi[3];
             row_offsets(P, quad * 32 + lane, qi);
             bool inside = true;
-            long long pflat = 0;
+            long long oflat = 0;
 #pragma unroll
             for (int a = 0; a < 3; ++a) {
-                const int pa = rg[a] + P.dil[a] * (origin[a] + qi[a]);
-                if (pa >= P.L[a]) inside = false;
-                pflat = pflat * P.L[a] + pa;
+                const int qa = origin[a] + qi[a];
+                if (qa >= nqf[a]) inside = false;
+                const int pa = rg[a] + P.dil[a] * (x0[a] + sx[a] * qa);
+                oflat = oflat * P.O[a] + (P.st[a] == 1 ? pa : pa / P.st[a]);
             }
             if (inside) {
-                const long long orow = ((long long)b * P.ltot + pflat) * P.Hq + h;
+                const long long orow = ((long long)b * P.otot + oflat) * P.Hq + h;
                 uint4* o4 = reinterpret_cast<uint4*>(out + orow * DH + team * CH);
 #pragma unroll
                 for (int i = 0; i < CH / 8; ++i) o4[i] = make_uint4(0, 0, 0, 0);
@@ -185,8 +207,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
                 for (int hf = 0; hf < SM::kHalves; ++hf)
                     tma_load_5d(sbase + SM::kQ + hf * SM::kHalf, &tmQ, bar_q, h * DH + 64 * hf,
-                                rg[2] + P.dil[2] * origin[2], rg[1] + P.dil[1] * origin[1],
-                                rg[0] + P.dil[0] * origin[0], b);
+                                rg[2] + P.dil[2] * (x0[2] + sx[2] * origin[2]), rg[1] + P.dil[1] * (x0[1] + sx[1] * origin[1]),
+                                rg[0] + P.dil[0] * (x0[0] + sx[0] * origin[0]), b);
                 for (int c = 0; c < nch && c < kStages; ++c) issue_kv();
             }
         }
@@ -201,22 +223,23 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         int qi[3];
         row_offsets(P, quad * 32 + lane, qi);
         valid_q = true; in_tensor = true;
-        long long pflat = 0;
+        long long oflat = 0;
 #pragma unroll
         for (int a = 0; a < 3; ++a) {
-            const int qa = origin[a] + qi[a];
-            const int pa = rg[a] + P.dil[a] * qa;
-            if (qa >= Lp[a]) valid_q = false;
-            if (pa >= P.L[a]) in_tensor = false;
-            pflat = pflat * P.L[a] + pa;
+            const int qa = origin[a] + qi[a];                 // query count along the axis
+            const int xq = x0[a] + sx[a] * qa;                // its sub-grid index
+            const int pa = rg[a] + P.dil[a] * xq;             // its position in the tensor
+            if (qa >= nq[a]) valid_q = false;
+            if (qa >= nqf[a]) in_tensor = false;
+            oflat = oflat * P.O[a] + (P.st[a] == 1 ? pa : pa / P.st[a]);
             if (cta_active) {
-                const int first = P.causal[a] ? qa - (P.K[a] - 1) : tc_window_start(qa, Lp[a], P.K[a]);
+                const int first = P.causal[a] ? xq - (P.K[a] - 1) : tc_window_start(xq, Lp[a], P.K[a]);
                 f[a] = (first > 0 ? first : 0) - lo[a];
                 e[a] = (first + P.K[a] < Lp[a] ? first + P.K[a] : Lp[a]) - lo[a];
             }
         }
         if (!valid_q) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
-        out_row = (((long long)b * P.ltot + pflat) * P.Hq + h);
+        out_row = (((long long)b * P.otot + oflat) * P.Hq + h);
     }
 
     tc_fence_before();
@@ -522,13 +545,13 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const void* v, const void* ek,
                  const void* ev, void* out, void* lse, cudaStream_t s)
 {
-    if (!tc_eligible(dtype, g, q, k, v)) return -2;
+    if (!tc_eligible(dtype, g, q, k, v, /*allow_stride=*/true)) return -2;
     if (g.n_extra > 0 && ((reinterpret_cast<uintptr_t>(ek) | reinterpret_cast<uintptr_t>(ev)) & 15u)) return -2;
     Plan plan;
-    if (!make_plan(g, plan)) return -2;
+    if (!make_plan(g, plan, kChunk, /*with_stride=*/true)) return -2;
     const bool bf16 = dtype == 2;
     CUtensorMap mq, mk, mv, mek, mev;
-    if (!encode_map(&mq, q, bf16, plan.p, g.Hq, g.D, g.qs, plan.box_q) ||
+    if (!encode_map(&mq, q, bf16, plan.p, g.Hq, g.D, g.qs, plan.box_q, /*query_lattice=*/true) ||
         !encode_map(&mk, k, bf16, plan.p, g.Hkv, g.D, g.ks, plan.box_kv) ||
         !encode_map(&mv, v, bf16, plan.p, g.Hkv, g.Dv, g.vs, plan.box_kv))
         return -2;
@@ -540,7 +563,7 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     plan.p.trace = trace_ptr();
     if (!plan.p.status) return -2;
     int ngroups = 1;
-    for (int a = 0; a < 3; ++a) ngroups *= plan.p.dil[a];
+    for (int a = 0; a < 3; ++a) ngroups *= plan.p.grp_n[a];     // dilation groups that hold queries
     const dim3 grid((unsigned)(plan.p.ntiles * ngroups), (unsigned)g.Hq, (unsigned)g.B);
     if (grid.x == 0 || g.B == 0) return 0;
     if (g.Hq > 65535 || g.B > 65535) return -2;

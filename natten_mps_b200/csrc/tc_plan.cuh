@@ -33,6 +33,15 @@ struct TcParams {
     long long ltot;
     int* status;
     long long* trace;      // optional device buffer for clock stamps of one CTA (nullptr = off)
+    // Output stride (forward only).  Inside dilation group r of an axis the queries sit at the
+    // sub-grid indices x = qx0[axis][r] + qstep[axis] * i, i = 0, 1, ... (qx0 < 0: the group holds no
+    // query); with stride 1 that is every index.  Output position = input position / st.
+    int st[3], qstep[3], O[3];
+    int qx0[3][8];
+    // Dilation groups that hold queries: r = grp_step * j, j < grp_n (every group when the stride is 1).
+    int grp_n[3], grp_step[3];
+    unsigned grp_mul[3];
+    long long otot;
 };
 
 // n / d with a precomputed multiplier; exact while n * d < 2^32 (checked on the host).
@@ -53,8 +62,8 @@ __device__ __forceinline__ bool cta_geometry(const TcParams& P, unsigned bx, int
     bool active = true;
 #pragma unroll
     for (int a = 2; a >= 0; --a) {
-        const unsigned q = fast_div(x, P.dil_mul[a]);
-        rg[a] = static_cast<int>(x - q * P.dil[a]);
+        const unsigned q = fast_div(x, P.grp_mul[a]);
+        rg[a] = static_cast<int>(x - q * P.grp_n[a]) * P.grp_step[a];
         x = q;
         const int ea = a - (3 - P.rank);
         const int Ls = (P.extents && ea >= 0) ? P.extents[b * P.rank + ea] : P.L[a];
@@ -177,7 +186,7 @@ struct Plan {
 };
 
 // Pick the row-tile shape (128 rows) whose column box needs the fewest chunks of `chunk` columns.
-inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk)
+inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk, bool with_stride = false)
 {
     TcParams& p = plan.p;
     const int pad = 3 - g.rank;
@@ -187,7 +196,23 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk)
         p.K[a] = s >= 0 ? g.K[s] : 1;
         p.dil[a] = s >= 0 ? g.dil[s] : 1;
         p.causal[a] = s >= 0 ? g.causal[s] : 0;
+        p.st[a] = (with_stride && s >= 0) ? g.st[s] : 1;
+        p.O[a] = (p.L[a] + p.st[a] - 1) / p.st[a];
+        if (p.dil[a] > 8) return false;                          // tensor-map element strides, qx0 table
+        int gcd = p.dil[a], r = p.st[a];
+        while (r) { const int t = gcd % r; gcd = r; r = t; }
+        p.qstep[a] = p.st[a] / gcd;
+        p.grp_step[a] = gcd;
+        p.grp_n[a] = p.dil[a] / gcd;
+        p.grp_mul[a] = p.grp_n[a] >= 2 ? (unsigned)((0x100000000ull + p.grp_n[a] - 1) / p.grp_n[a]) : 0u;
+        for (int rgrp = 0; rgrp < 8; ++rgrp) {
+            p.qx0[a][rgrp] = -1;
+            if (rgrp >= p.dil[a]) continue;
+            for (int x = 0; x < p.qstep[a]; ++x)
+                if ((rgrp + p.dil[a] * x) % p.st[a] == 0) { p.qx0[a][rgrp] = x; break; }
+        }
     }
+    p.otot = (long long)p.O[0] * p.O[1] * p.O[2];
     long long best = -1;
     for (int t2 = 1; t2 <= 128; t2 *= 2)
         for (int t1 = 1; t1 * t2 <= 128; t1 *= 2) {
@@ -197,11 +222,11 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk)
             for (int a = 0; a < 3; ++a)
                 if (p.L[a] == 1 && t[a] != 1) fits = false;      // unused axis
             if (!fits) continue;
-            const int E2 = t2 + p.K[2] - 1;
+            const int E2 = (t2 - 1) * p.qstep[2] + p.K[2];
             int cb2 = pow2ceil(E2);
             if (cb2 > chunk) cb2 = chunk;
             if (cb2 * p.dil[2] > 256) continue;                  // TMA box limit
-            const int E1 = t1 + p.K[1] - 1;
+            const int E1 = (t1 - 1) * p.qstep[1] + p.K[1];
             int cb1 = chunk / cb2;
             if (p.L[1] == 1) cb1 = 1;
             if (cb1 > pow2ceil(E1)) cb1 = pow2ceil(E1);
@@ -209,7 +234,7 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk)
             int cb0 = chunk / (cb2 * cb1);
             if (p.L[0] == 1 && cb0 != 1) continue;               // would leave the chunk short of columns
             if (cb0 * p.dil[0] > 256) continue;
-            const int E0 = t0 + p.K[0] - 1;
+            const int E0 = (t0 - 1) * p.qstep[0] + p.K[0];
             const long long n = (long long)((E0 + cb0 - 1) / cb0) * ((E1 + cb1 - 1) / cb1) * ((E2 + cb2 - 1) / cb2);
             // prefer fewer chunks, then wider innermost tiles
             if (best < 0 || n < best) {
@@ -226,24 +251,25 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk)
     p.ntiles = 1;
     for (int a = 0; a < 3; ++a) {
         const int lp = (p.L[a] + p.dil[a] - 1) / p.dil[a];
-        p.ntile[a] = (lp + p.tile[a] - 1) / p.tile[a];
+        const int nq = (lp + p.qstep[a] - 1) / p.qstep[a];       // most queries a group can hold along this axis
+        p.ntile[a] = (nq + p.tile[a] - 1) / p.tile[a];
         p.ntiles *= p.ntile[a];
         p.ntile_mul[a] = p.ntile[a] >= 2 ? (unsigned)((0x100000000ull + p.ntile[a] - 1) / p.ntile[a]) : 0u;
         p.dil_mul[a] = p.dil[a] >= 2 ? (unsigned)((0x100000000ull + p.dil[a] - 1) / p.dil[a]) : 0u;
-        plan.box_q[a] = p.tile[a] * p.dil[a];
+        plan.box_q[a] = p.tile[a] * p.dil[a] * p.qstep[a];
         plan.box_kv[a] = p.cb[a] * p.dil[a];
         if (plan.box_q[a] > 256) return false;
     }
     {
         long long blocks = p.ntiles;
         int dmax = 1;
-        for (int a = 0; a < 3; ++a) { blocks *= p.dil[a]; dmax = p.dil[a] > dmax ? p.dil[a] : dmax; dmax = p.ntile[a] > dmax ? p.ntile[a] : dmax; }
+        for (int a = 0; a < 3; ++a) { blocks *= p.grp_n[a]; dmax = p.dil[a] > dmax ? p.dil[a] : dmax; dmax = p.ntile[a] > dmax ? p.ntile[a] : dmax; }
         if (blocks * dmax >= (1ll << 32) || (long long)(p.L[0] + p.L[1] + p.L[2] + dmax) * dmax >= (1ll << 32)) return false;
     }
     p.rank = g.rank; p.B = g.B; p.Hq = g.Hq; p.Hkv = g.Hkv; p.group = g.group;
     p.n_extra = g.n_extra;
     p.ngroups = 1;
-    for (int a = 0; a < 3; ++a) p.ngroups *= p.dil[a];
+    for (int a = 0; a < 3; ++a) p.ngroups *= p.grp_n[a];
     p.per_head = (unsigned)p.ntiles * (unsigned)p.ngroups;
     if ((long long)p.per_head * g.B * g.Hq >= (1ll << 31)) return false;
     p.work_q = p.per_head * (unsigned)g.B * (unsigned)g.Hq;
@@ -257,7 +283,7 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk)
 
 // 5-D map over [B, X0, X1, X2, heads*D] (innermost first in the arrays below).
 inline bool encode_map(CUtensorMap* map, const void* base, bool bf16, const TcParams& p, int heads, int dh,
-                const long long strides[3], const int box[3])
+                const long long strides[3], const int box[3], bool query_lattice = false)
 {
     EncodeFn enc = get_encode();
     if (!enc) return false;
@@ -266,6 +292,10 @@ inline bool encode_map(CUtensorMap* map, const void* base, bool bf16, const TcPa
     cuuint64_t gstr[4] = {tok, tok * p.L[2], tok * p.L[2] * p.L[1], (cuuint64_t)strides[0] * 2};
     cuuint32_t bx[5] = {64, (cuuint32_t)box[2], (cuuint32_t)box[1], (cuuint32_t)box[0], 1};
     cuuint32_t es[5] = {1, (cuuint32_t)p.dil[2], (cuuint32_t)p.dil[1], (cuuint32_t)p.dil[0], 1};
+    if (query_lattice)                                           // strided output: only every qstep-th sub-grid position is a query
+        for (int a = 0; a < 3; ++a) es[3 - a] *= (cuuint32_t)p.qstep[a];
+    for (int i = 1; i < 4; ++i)
+        if (es[i] > 8) return false;
     if (dims[4] == 0) return false;
     const CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
                            const_cast<void*>(base), dims, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -310,13 +340,13 @@ inline unsigned persistent_grid(unsigned work, int per_sm)
     return work < cap ? work : cap;
 }
 
-inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, const void* v)
+inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, const void* v, bool allow_stride = false)
 {
     if (dtype != 1 && dtype != 2) return false;                 // f16 / bf16
     if ((g.D != 64 && g.D != 128) || g.Dv != g.D) return false;
     if (!(g.scale > 0.0)) return false;
     for (int a = 0; a < g.rank; ++a) {
-        if (g.st[a] != 1) return false;
+        if (g.st[a] != 1 && !allow_stride) return false;
         if ((g.K[a] & 1) == 0) return false;                    // even kernels: SIMT path
         if (g.extents && g.dil[a] != 1) return false;
     }

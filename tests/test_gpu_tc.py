@@ -174,3 +174,42 @@ def test_tc_forward_rescales_when_later_chunks_dominate(spatial, ks, D, dtype):
     lerr = ((lse - ref_lse).abs() / ref_lse.abs().clamp(min=1.0)).max().item()
     assert err <= 2e-2, f"out differs by {err}"
     assert lerr <= 2e-3, f"lse differs by {lerr} (relative)"
+
+
+STRIDE_CASES = [
+    # spatial, B, Hq, Hkv, kernel, dilation, stride, causal, extents, D
+    ((64, 64), 1, 2, 2, (13, 13), (2, 2), (2, 2), (False, False), None, 64),     # config 3's strided variant, small
+    ((40, 36), 2, 2, 1, (7, 7), (1, 1), (2, 2), (False, False), None, 64),       # stride without dilation, GQA
+    ((37, 41), 1, 2, 2, (5, 7), (2, 3), (3, 2), (False, True), None, 64),        # coprime stride / dilation, ragged, causal
+    ((48, 40), 1, 1, 1, (5, 5), (2, 2), (4, 4), (False, False), None, 64),       # stride a multiple of the dilation
+    ((300,), 2, 4, 2, (31,), (1,), (2,), (False,), [[300], [170]], 64),          # 1-D, per-sample lengths
+    ((6, 20, 18), 1, 2, 2, (3, 7, 5), (1, 1, 2), (1, 2, 3), (True, False, False), None, 64),
+    ((33, 30), 1, 2, 1, (7, 7), (1, 1), (3, 2), (False, False), None, 128),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", STRIDE_CASES, ids=lambda c: "x".join(map(str, c[0])) + f"_s{c[6][-1]}_d{c[5][-1]}_h{c[9]}")
+def test_tc_forward_with_output_stride_matches_simt(case, dtype):
+    spatial, B, Hq, Hkv, ks, dil, st, causal, extents, D = case
+    g = torch.Generator(device="cpu").manual_seed(29)
+    q = torch.randn((B, *spatial, Hq, D), generator=g).to(dtype).cuda()
+    k = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    v = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    ext = None if extents is None else torch.tensor(extents, dtype=torch.int32).cuda()
+    args = (q, k, v, ks, st, dil, causal, D ** -0.5)
+    try:
+        _cabi.set_force("simt")
+        ref_out, ref_lse = _backend.fused_forward(*args, extents=ext)
+        _cabi.set_force("tc")
+        out, lse = _backend.fused_forward(*args, extents=ext)
+        assert _cabi.last_path() == "tcgen05"
+    finally:
+        _cabi.set_force(None)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    assert out.shape == ref_out.shape == (B, *[-(-n // s) for n, s in zip(spatial, st)], Hq, D)
+    err = (out.float() - ref_out.float()).abs().max().item()
+    lerr = (lse - ref_lse).abs().max().item()
+    assert err <= 1.6e-2, f"out differs by {err}"
+    assert lerr <= 2e-3, f"lse differs by {lerr}"
