@@ -15,6 +15,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>
+#include <initializer_list>
 #include <type_traits>
 
 namespace natten {
@@ -995,6 +996,216 @@ av_bwd_dattn_kernel(const __grid_constant__ Geo g, const T* __restrict__ v, cons
 }
 
 // ---------------------------------------------------------------------------
+// Split ops, vectorised variants for 16-bit tensors whose rows can be read 16 bytes at a time
+// (head dim 32 / 64 / 128 / 256, strides multiples of 8 elements).  A warp still owns one
+// (query, head) or (key, kv head) row, but LPR = D/8 lanes share one source row (16 bytes each),
+// so one load instruction covers 32/LPR whole rows instead of 32 scattered 2-byte pieces, and
+// the neighbour offsets are worked out once per row (lane per slot) instead of per channel.
+// ---------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8])
+{
+    const T* x = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = to_acc(x[i]);
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8])
+{
+    uint4 raw;
+    T* x = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = from_acc<T, float>(f[i]);
+    return raw;
+}
+
+// Element offsets (inside one batch) of a query's neighbours, one per slot; -1 = masked.
+__device__ __forceinline__ void neighbour_offsets(const Geo& g, const QueryCtx& c, long long token_stride,
+                                                  int lane, int* koff)
+{
+    for (int j = lane; j < g.ktot; j += 32) {
+        long long kf;
+        koff[j] = slot_key(g, c, j, kf) ? (int)(kf * token_stride) : -1;
+    }
+    __syncwarp();
+}
+
+// out[row, j] = scale * <x[row], y[neighbour j]>     (QK forward; AV backward w.r.t. attn)
+template <typename T, int LPR>
+__global__ void __launch_bounds__(kWarps * 32)
+dot_neighbours_vec_kernel(const __grid_constant__ Geo g, const T* __restrict__ x, long long xbs, long long xts,
+                          long long xhs, int x_by_position, int D, const T* __restrict__ y, long long ybs,
+                          long long yts, long long yhs, float scale, int masked_is_neg_inf,
+                          T* __restrict__ out, long long rows)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int* koff = reinterpret_cast<int*>(smem_raw) + (size_t)warp * g.ktot;
+    const long long row = (long long)blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    QueryCtx c;
+    decode_query(g, row, c);
+    neighbour_offsets(g, c, yts, lane, koff);
+    constexpr int G = 32 / LPR;
+    const int gl = lane % LPR, gi = lane / LPR;
+    const T* xrow = x_by_position ? x + c.b * xbs + c.pflat * xts + c.h * xhs : x + row * (long long)D;
+    float xf[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(xrow + 8 * gl), xf);
+    const T* ybase = y + c.b * ybs + c.hk * yhs + 8 * gl;
+    const float fill = masked_is_neg_inf ? -INFINITY : 0.f;
+    for (int j0 = 0; j0 < g.ktot; j0 += G) {
+        const int j = j0 + gi;
+        const int off = j < g.ktot ? koff[j] : -1;
+        float d = 0.f;
+        if (off >= 0) {
+            float yf[8];
+            unpack8<T>(*reinterpret_cast<const uint4*>(ybase + off), yf);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) d = fmaf(xf[i], yf[i], d);
+        }
+#pragma unroll
+        for (int m = LPR / 2; m > 0; m >>= 1) d += __shfl_xor_sync(kFull, d, m);
+        if (gl == 0 && j < g.ktot) out[row * g.ktot + j] = from_acc<T, float>(off >= 0 ? d * scale : fill);
+    }
+}
+
+// out[row] = scale * sum_j w[row, j] * y[neighbour j]   (AV forward; QK backward w.r.t. q)
+template <typename T, int LPR>
+__global__ void __launch_bounds__(kWarps * 32)
+sum_neighbours_vec_kernel(const __grid_constant__ Geo g, const T* __restrict__ w, const T* __restrict__ y,
+                          long long ybs, long long yts, long long yhs, int D, float scale,
+                          int out_by_position, T* __restrict__ out, long long rows)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int* koff = reinterpret_cast<int*>(smem_raw) + (size_t)warp * g.ktot;
+    const long long row = (long long)blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    QueryCtx c;
+    decode_query(g, row, c);
+    neighbour_offsets(g, c, yts, lane, koff);
+    constexpr int G = 32 / LPR;
+    const int gl = lane % LPR, gi = lane / LPR;
+    const T* ybase = y + c.b * ybs + c.hk * yhs + 8 * gl;
+    const T* wrow = w + row * g.ktot;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int j0 = 0; j0 < g.ktot; j0 += G) {
+        const int j = j0 + gi;
+        const int off = j < g.ktot ? koff[j] : -1;
+        if (off >= 0) {
+            const float wj = to_acc(wrow[j]);
+            float yf[8];
+            unpack8<T>(*reinterpret_cast<const uint4*>(ybase + off), yf);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(wj, yf[i], acc[i]);
+        }
+    }
+#pragma unroll
+    for (int m = LPR; m < 32; m <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(kFull, acc[i], m);
+    if (gi == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= scale;
+        T* orow = out_by_position ? out + (((long long)c.b * g.ltot + c.pflat) * g.Hq + c.h) * D : out + row * (long long)D;
+        *reinterpret_cast<uint4*>(orow + 8 * gl) = pack8<T>(acc);
+    }
+}
+
+// dst[key] = wscale * sum over the queries that attend to the key of weight[query, slot] * src[query]
+// (dK of the QK backward, dV of the AV backward).
+template <typename T, int LPR>
+__global__ void __launch_bounds__(kWarps * 32)
+inverse_gather_vec_kernel(const __grid_constant__ Geo g, const T* __restrict__ weights,
+                          const T* __restrict__ rows_src, long long src_bs, long long src_ts, long long src_hs,
+                          int src_is_query_input, int width, float wscale, T* __restrict__ dst, long long rows)
+{
+    __shared__ long long s_off[kWarps][32];
+    __shared__ float s_w[kWarps][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * kWarps + warp;   // (b*ltot + n)*Hkv + hk
+    if (row >= rows) return;
+    KeyCtx c;
+    decode_key(g, row, c);
+    constexpr int G = 32 / LPR;
+    const int gl = lane % LPR, gi = lane / LPR;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    const int total = c.inside ? c.ncand * g.group : 0;
+    for (int base = 0; base < total; base += 32) {
+        const int cnd = base + lane;
+        bool valid = false;
+        long long off = 0;
+        float wv = 0.f;
+        if (cnd < total) {
+            const int gidx = cnd / c.ncand, t = cnd % c.ncand;
+            long long oflat, pflat; int slot;
+            valid = candidate(g, c, t, oflat, pflat, slot);
+            if (valid) {
+                const int h = c.hk * g.group + gidx;
+                const long long r = ((long long)c.b * g.otot + oflat) * g.Hq + h;
+                wv = to_acc(weights[r * g.ktot + slot]);
+                off = src_is_query_input ? c.b * src_bs + pflat * src_ts + h * src_hs : r * (long long)width;
+            }
+        }
+        // compact the valid candidates of this batch of 32 into the warp's list (fixed order)
+        const unsigned mask = __ballot_sync(kFull, valid);
+        const int n = __popc(mask);
+        if (valid) {
+            const int pos = __popc(mask & ((1u << lane) - 1u));
+            s_off[warp][pos] = off;
+            s_w[warp][pos] = wv;
+        }
+        __syncwarp();
+        for (int i0 = 0; i0 < n; i0 += G) {
+            const int i = i0 + gi;
+            if (i < n) {
+                float yf[8];
+                unpack8<T>(*reinterpret_cast<const uint4*>(rows_src + s_off[warp][i] + 8 * gl), yf);
+                const float wj = s_w[warp][i];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc[u] = fmaf(wj, yf[u], acc[u]);
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int m = LPR; m < 32; m <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(kFull, acc[i], m);
+    if (gi == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= wscale;
+        *reinterpret_cast<uint4*>(dst + row * (long long)width + 8 * gl) = pack8<T>(acc);
+    }
+}
+
+// Can the vectorised split kernels serve this problem?  (16-bit T is checked by the callers.)
+inline bool split_vec_ok(const Geo& g, int D, std::initializer_list<const void*> ptrs,
+                         std::initializer_list<long long> strides, long long token_stride)
+{
+    if (D != 32 && D != 64 && D != 128 && D != 256) return false;
+    for (const void* p : ptrs)
+        if (reinterpret_cast<uintptr_t>(p) & 15u) return false;
+    for (long long st : strides)
+        if (st % 8 != 0) return false;
+    if ((long long)g.ktot * kWarps * (long long)sizeof(int) > 48 * 1024) return false;
+    return g.ltot * token_stride < (1ll << 31);                   // neighbour offsets inside a batch are 32-bit
+}
+
+#define NATTEN_DISPATCH_LPR(D, LPR, ...)                                  \
+    do {                                                                  \
+        if ((D) == 32) { constexpr int LPR = 4; __VA_ARGS__; }            \
+        else if ((D) == 64) { constexpr int LPR = 8; __VA_ARGS__; }       \
+        else if ((D) == 128) { constexpr int LPR = 16; __VA_ARGS__; }     \
+        else { constexpr int LPR = 32; __VA_ARGS__; }                     \
+    } while (0)
+
+// ---------------------------------------------------------------------------
 // Launch helpers
 // ---------------------------------------------------------------------------
 unsigned long long g_launches = 0;
@@ -1139,6 +1350,17 @@ cudaError_t qk_fwd_t(const Geo& g, const void* q, const void* k, void* logits, c
     using A = typename AccOf<T>::type;
     const long long rows = (long long)g.B * g.otot * g.Hq;
     if (rows == 0) return cudaSuccess;
+    if constexpr (sizeof(T) == 2) {
+        if (split_vec_ok(g, g.D, {q, k}, {g.qs[0], g.qs[1], g.qs[2], g.ks[0], g.ks[1], g.ks[2]}, g.ks[1])) {
+            const size_t smem = (size_t)kWarps * g.ktot * sizeof(int);
+            NATTEN_DISPATCH_LPR(g.D, LPR,
+                dot_neighbours_vec_kernel<T, LPR><<<grid_for(rows), kWarps * 32, smem, s>>>(
+                    g, (const T*)q, g.qs[0], g.qs[1], g.qs[2], 1, g.D, (const T*)k, g.ks[0], g.ks[1], g.ks[2],
+                    g.has_scale ? (float)g.scale : 1.f, 1, (T*)logits, rows));
+            ++g_launches;
+            return cudaGetLastError();
+        }
+    }
     qk_fwd_kernel<T><<<grid_for(rows), kWarps * 32, (size_t)kWarps * g.D * sizeof(A), s>>>(
         g, (const T*)q, (const T*)k, (T*)logits, rows);
     ++g_launches;
@@ -1157,17 +1379,39 @@ cudaError_t qk_bwd_t(const Geo& g, const void* q, const void* k, const void* dlo
         cudaError_t err = cudaMemsetAsync(dq, 0, sizeof(T) * (size_t)g.B * g.ltot * g.Hq * g.D, s);
         if (err != cudaSuccess) return err;
     }
+    bool vec = false;
+    if constexpr (sizeof(T) == 2)
+        vec = split_vec_ok(g, g.D, {q, k, dq, dk}, {g.qs[0], g.qs[1], g.qs[2], g.ks[0], g.ks[1], g.ks[2]}, g.ks[1]);
     if (qrows > 0) {
-        NATTEN_DISPATCH_N(g.D, ND,
-            qk_bwd_dq_kernel<T, ND><<<grid_for(qrows), kWarps * 32, 0, s>>>(
-                g, (const T*)k, (const T*)dlogits, (T*)dq, qrows));
+        if (vec) {
+            if constexpr (sizeof(T) == 2) {
+                const size_t smem = (size_t)kWarps * g.ktot * sizeof(int);
+                NATTEN_DISPATCH_LPR(g.D, LPR,
+                    sum_neighbours_vec_kernel<T, LPR><<<grid_for(qrows), kWarps * 32, smem, s>>>(
+                        g, (const T*)dlogits, (const T*)k, g.ks[0], g.ks[1], g.ks[2], g.D,
+                        g.has_scale ? (float)g.scale : 1.f, 1, (T*)dq, qrows));
+            }
+        } else {
+            NATTEN_DISPATCH_N(g.D, ND,
+                qk_bwd_dq_kernel<T, ND><<<grid_for(qrows), kWarps * 32, 0, s>>>(
+                    g, (const T*)k, (const T*)dlogits, (T*)dq, qrows));
+        }
         ++g_launches;
     }
     if (krows > 0) {
-        NATTEN_DISPATCH_N(g.D, ND,
-            inverse_gather_kernel<T, ND><<<grid_for(krows), kWarps * 32, 0, s>>>(
-                g, (const T*)dlogits, (const T*)q, g.qs[0], g.qs[1], g.qs[2], 1, g.D,
-                g.has_scale ? g.scale : 1.0, (T*)dk, krows));
+        if (vec) {
+            if constexpr (sizeof(T) == 2) {
+                NATTEN_DISPATCH_LPR(g.D, LPR,
+                    inverse_gather_vec_kernel<T, LPR><<<grid_for(krows), kWarps * 32, 0, s>>>(
+                        g, (const T*)dlogits, (const T*)q, g.qs[0], g.qs[1], g.qs[2], 1, g.D,
+                        g.has_scale ? (float)g.scale : 1.f, (T*)dk, krows));
+            }
+        } else {
+            NATTEN_DISPATCH_N(g.D, ND,
+                inverse_gather_kernel<T, ND><<<grid_for(krows), kWarps * 32, 0, s>>>(
+                    g, (const T*)dlogits, (const T*)q, g.qs[0], g.qs[1], g.qs[2], 1, g.D,
+                    g.has_scale ? g.scale : 1.0, (T*)dk, krows));
+        }
         ++g_launches;
     }
     return cudaGetLastError();
@@ -1178,6 +1422,16 @@ cudaError_t av_fwd_t(const Geo& g, const void* attn, const void* v, void* out, c
 {
     const long long rows = (long long)g.B * g.otot * g.Hq;
     if (rows == 0) return cudaSuccess;
+    if constexpr (sizeof(T) == 2) {
+        if (split_vec_ok(g, g.Dv, {v, out}, {g.vs[0], g.vs[1], g.vs[2]}, g.vs[1])) {
+            const size_t smem = (size_t)kWarps * g.ktot * sizeof(int);
+            NATTEN_DISPATCH_LPR(g.Dv, LPR,
+                sum_neighbours_vec_kernel<T, LPR><<<grid_for(rows), kWarps * 32, smem, s>>>(
+                    g, (const T*)attn, (const T*)v, g.vs[0], g.vs[1], g.vs[2], g.Dv, 1.f, 0, (T*)out, rows));
+            ++g_launches;
+            return cudaGetLastError();
+        }
+    }
     NATTEN_DISPATCH_N(g.Dv, NDV,
         av_fwd_kernel<T, NDV><<<grid_for(rows), kWarps * 32, 0, s>>>(
             g, (const T*)attn, (const T*)v, (T*)out, rows));
@@ -1192,15 +1446,35 @@ cudaError_t av_bwd_t(const Geo& g, const void* attn, const void* v, const void* 
     using A = typename AccOf<T>::type;
     const long long qrows = (long long)g.B * g.otot * g.Hq;
     const long long krows = (long long)g.B * g.ltot * g.Hkv;
+    bool vec = false;
+    if constexpr (sizeof(T) == 2) vec = split_vec_ok(g, g.Dv, {v, dout, dv}, {g.vs[0], g.vs[1], g.vs[2]}, g.vs[1]);
     if (qrows > 0) {
-        av_bwd_dattn_kernel<T><<<grid_for(qrows), kWarps * 32, (size_t)kWarps * g.Dv * sizeof(A), s>>>(
-            g, (const T*)v, (const T*)dout, (T*)dattn, qrows);
+        if (vec) {
+            if constexpr (sizeof(T) == 2) {
+                const size_t smem = (size_t)kWarps * g.ktot * sizeof(int);
+                NATTEN_DISPATCH_LPR(g.Dv, LPR,
+                    dot_neighbours_vec_kernel<T, LPR><<<grid_for(qrows), kWarps * 32, smem, s>>>(
+                        g, (const T*)dout, 0, 0, 0, 0, g.Dv, (const T*)v, g.vs[0], g.vs[1], g.vs[2], 1.f, 0,
+                        (T*)dattn, qrows));
+            }
+        } else {
+            av_bwd_dattn_kernel<T><<<grid_for(qrows), kWarps * 32, (size_t)kWarps * g.Dv * sizeof(A), s>>>(
+                g, (const T*)v, (const T*)dout, (T*)dattn, qrows);
+        }
         ++g_launches;
     }
     if (krows > 0) {
-        NATTEN_DISPATCH_N(g.Dv, ND,
-            inverse_gather_kernel<T, ND><<<grid_for(krows), kWarps * 32, 0, s>>>(
-                g, (const T*)attn, (const T*)dout, 0, 0, 0, 0, g.Dv, 1.0, (T*)dv, krows));
+        if (vec) {
+            if constexpr (sizeof(T) == 2) {
+                NATTEN_DISPATCH_LPR(g.Dv, LPR,
+                    inverse_gather_vec_kernel<T, LPR><<<grid_for(krows), kWarps * 32, 0, s>>>(
+                        g, (const T*)attn, (const T*)dout, 0, 0, 0, 0, g.Dv, 1.f, (T*)dv, krows));
+            }
+        } else {
+            NATTEN_DISPATCH_N(g.Dv, ND,
+                inverse_gather_kernel<T, ND><<<grid_for(krows), kWarps * 32, 0, s>>>(
+                    g, (const T*)attn, (const T*)dout, 0, 0, 0, 0, g.Dv, 1.0, (T*)dv, krows));
+        }
         ++g_launches;
     }
     return cudaGetLastError();
