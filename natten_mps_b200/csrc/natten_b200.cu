@@ -153,6 +153,13 @@ int natten_qk_fwd(const natten_params_t* p, const void* q, const void* k, void* 
     if (g.B == 0) return NATTEN_OK;
     if (!q || !k || !logits || g.extents || g.n_extra) return NATTEN_E_INVALID;
     set_vec_ok(g, p->dtype, true, true, false, {q, k});
+    if (!(p->flags & NATTEN_FLAG_FORCE_SIMT)) {
+        rc = tc_scores(p->dtype, g, q, g.qs, k, g.ks, g.has_scale ? (float)g.scale : 1.f, true, logits,
+                       (cudaStream_t)stream);
+        if (rc == 0) { t_last_path = NATTEN_PATH_TCGEN05; return NATTEN_OK; }
+        if (rc > 0) return rc;
+        if (p->flags & NATTEN_FLAG_FORCE_TC) return NATTEN_E_UNSUPPORTED;
+    }
     t_last_path = NATTEN_PATH_SIMT;
     return from_cuda(simt_qk_fwd(p->dtype, g, q, k, logits, (cudaStream_t)stream));
 }

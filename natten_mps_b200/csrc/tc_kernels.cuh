@@ -13,6 +13,10 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
                  const void* dlse, void* dq, void* dk, void* dv, void* dek, void* dev,
                  void* workspace, cudaStream_t s);
 size_t tc_bwd_workspace_bytes(int dtype, const Geo& g);
+// out[row, slot] = scale * <x[row], y[key of slot]> (QK forward; AV backward w.r.t. attn).  x is indexed by
+// input position with strides xs (batch, token, head); masked slots get -inf (neg_inf) or 0.
+int tc_scores(int dtype, const Geo& g, const void* x, const long long xs[3], const void* y, const long long ys[3],
+              float scale, bool neg_inf, void* out, cudaStream_t s);
 void tc_count_launch();
 unsigned long long tc_launch_count();
 // 0 = clean; 1 = some kernel gave up on a bounded wait (synchronises the device).

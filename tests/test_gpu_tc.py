@@ -213,3 +213,45 @@ def test_tc_forward_with_output_stride_matches_simt(case, dtype):
     lerr = (lse - ref_lse).abs().max().item()
     assert err <= 1.6e-2, f"out differs by {err}"
     assert lerr <= 2e-3, f"lse differs by {lerr}"
+
+
+SPLIT_CASES = [
+    # spatial, B, Hq, Hkv, kernel, dilation, stride, causal, D
+    ((64, 64), 2, 2, 2, (7, 7), (1, 1), (1, 1), (False, False), 64),
+    ((20, 19), 1, 2, 1, (7, 5), (1, 1), (1, 1), (False, False), 64),            # ragged tiles, GQA
+    ((33, 40), 1, 2, 2, (13, 13), (2, 2), (1, 1), (False, False), 64),          # 169 slots, dilation
+    ((27, 31), 1, 1, 1, (3, 7), (3, 2), (1, 1), (True, False), 64),             # causal axis: masked slots
+    ((40, 36), 1, 2, 2, (5, 5), (1, 1), (2, 2), (False, True), 64),             # output stride
+    ((300,), 2, 4, 2, (31,), (1,), (1,), (False,), 64),
+    ((260,), 1, 2, 2, (63,), (1,), (1,), (True,), 128),
+    ((6, 20, 18), 1, 2, 2, (3, 7, 7), (1, 1, 1), (1, 1, 1), (True, False, False), 64),     # 147 slots
+    ((5, 9, 11), 1, 2, 1, (3, 3, 5), (1, 2, 1), (1, 1, 1), (False, False, False), 128),
+]
+
+
+def _split_id(c):
+    return "x".join(map(str, c[0])) + f"_k{c[4][-1]}_d{c[5][-1]}_s{c[6][-1]}_h{c[8]}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", SPLIT_CASES, ids=_split_id)
+def test_tc_qk_forward_matches_simt(case, dtype):
+    spatial, B, Hq, Hkv, ks, dil, st, causal, D = case
+    g = torch.Generator(device="cpu").manual_seed(31)
+    q = torch.randn((B, *spatial, Hq, D), generator=g).to(dtype).cuda()
+    k = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    try:
+        _cabi.set_force("simt")
+        ref = _backend.qk_forward(q, k, ks, dil, st, causal, D ** -0.5)
+        _cabi.set_force("tc")
+        got = _backend.qk_forward(q, k, ks, dil, st, causal, D ** -0.5)
+        assert _cabi.last_path() == "tcgen05"
+    finally:
+        _cabi.set_force(None)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    assert got.shape == ref.shape
+    masked = torch.isinf(ref)
+    assert torch.equal(torch.isinf(got), masked)                 # the same slots are masked (-inf)
+    err = (got.float() - ref.float())[~masked].abs().max().item()
+    assert err <= 2e-2 * max(1.0, ref.float()[~masked].abs().max().item()), f"logits differ by {err}"
