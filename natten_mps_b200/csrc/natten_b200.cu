@@ -197,6 +197,22 @@ int natten_av_bwd(const natten_params_t* p, const void* attn, const void* v, con
     if (!attn || !v || !dout || !dattn || !dv || g.extents || g.n_extra) return NATTEN_E_INVALID;
     set_vec_ok(g, p->dtype, false, false, true, {v, dout});
     t_last_path = NATTEN_PATH_SIMT;
+    // d attn[row, slot] = <dout[row], v[key of slot]> is the scores product with x = dout (contiguous rows,
+    // indexed by position when the stride is 1); dV stays a gather over the inverse neighbourhood.
+    bool unit_stride = true;
+    for (int a = 0; a < g.rank; ++a) unit_stride = unit_stride && g.st[a] == 1;
+    if (!(p->flags & NATTEN_FLAG_FORCE_SIMT) && unit_stride) {
+        Geo gv = g;
+        gv.D = g.Dv;
+        const long long dos[3] = {g.otot * (long long)g.Hq * g.Dv, (long long)g.Hq * g.Dv, g.Dv};
+        rc = tc_scores(p->dtype, gv, dout, dos, v, g.vs, 1.f, false, dattn, (cudaStream_t)stream);
+        if (rc > 0) return rc;
+        if (rc == 0) {
+            t_last_path = NATTEN_PATH_TCGEN05;
+            return from_cuda(simt_av_bwd(p->dtype, g, attn, v, dout, nullptr, dv, (cudaStream_t)stream));
+        }
+    }
+    if (p->flags & NATTEN_FLAG_FORCE_TC) return NATTEN_E_UNSUPPORTED;
     return from_cuda(simt_av_bwd(p->dtype, g, attn, v, dout, dattn, dv, (cudaStream_t)stream));
 }
 

@@ -1448,7 +1448,7 @@ cudaError_t av_bwd_t(const Geo& g, const void* attn, const void* v, const void* 
     const long long krows = (long long)g.B * g.ltot * g.Hkv;
     bool vec = false;
     if constexpr (sizeof(T) == 2) vec = split_vec_ok(g, g.Dv, {v, dout, dv}, {g.vs[0], g.vs[1], g.vs[2]}, g.vs[1]);
-    if (qrows > 0) {
+    if (qrows > 0 && dattn) {                     // dattn == nullptr: another kernel has produced it
         if (vec) {
             if constexpr (sizeof(T) == 2) {
                 const size_t smem = (size_t)kWarps * g.ktot * sizeof(int);

@@ -255,3 +255,29 @@ def test_tc_qk_forward_matches_simt(case, dtype):
     assert torch.equal(torch.isinf(got), masked)                 # the same slots are masked (-inf)
     err = (got.float() - ref.float())[~masked].abs().max().item()
     assert err <= 2e-2 * max(1.0, ref.float()[~masked].abs().max().item()), f"logits differ by {err}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", [c for c in SPLIT_CASES if all(s == 1 for s in c[6])], ids=_split_id)
+def test_tc_av_backward_matches_simt(case, dtype):
+    spatial, B, Hq, Hkv, ks, dil, st, causal, D = case
+    g = torch.Generator(device="cpu").manual_seed(37)
+    ktot = 1
+    for kk in ks:
+        ktot *= kk
+    attn = torch.softmax(torch.randn((B, *spatial, Hq, ktot), generator=g), dim=-1).to(dtype).cuda()
+    v = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    go = torch.randn((B, *spatial, Hq, D), generator=g).to(dtype).cuda()
+    try:
+        _cabi.set_force("simt")
+        ref_da, ref_dv = _backend.av_backward(go, attn, v, ks, dil, st, causal)
+        _cabi.set_force("tc")
+        da, dv = _backend.av_backward(go, attn, v, ks, dil, st, causal)
+        assert _cabi.last_path() == "tcgen05"
+    finally:
+        _cabi.set_force(None)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    for name, a, r in (("dattn", da, ref_da), ("dv", dv, ref_dv)):
+        err = (a.float() - r.float()).abs().max().item()
+        assert err <= 2e-2 * max(1.0, r.float().abs().max().item()), f"{name} differs by {err}"
