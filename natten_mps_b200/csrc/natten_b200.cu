@@ -173,7 +173,23 @@ int natten_qk_bwd(const natten_params_t* p, const void* q, const void* k, const 
     if (g.B == 0) return NATTEN_OK;
     if (!q || !k || !dlogits || !dq || !dk || g.extents || g.n_extra) return NATTEN_E_INVALID;
     t_last_path = NATTEN_PATH_SIMT;
-    return from_cuda(simt_qk_bwd(p->dtype, g, q, k, dlogits, dq, dk, (cudaStream_t)stream));
+    // dq[row] = scale * sum_slot dlogits[row, slot] * k[key of slot] is the apply product; dK gathers
+    // dlogits * q over the inverse neighbourhood.  Whatever the tensor-core kernels do not cover goes to SIMT.
+    bool dq_done = false, dk_done = false;
+    if (!(p->flags & NATTEN_FLAG_FORCE_SIMT)) {
+        const float sc = g.has_scale ? (float)g.scale : 1.f;
+        rc = tc_apply(p->dtype, g, dlogits, k, g.ks, sc, true, dq, (cudaStream_t)stream);
+        if (rc > 0) return rc;
+        dq_done = rc == 0;
+        rc = tc_gather(p->dtype, g, dlogits, q, g.qs, sc, dk, (cudaStream_t)stream);
+        if (rc > 0) return rc;
+        dk_done = rc == 0;
+        if (dq_done || dk_done) t_last_path = NATTEN_PATH_TCGEN05;
+        if ((p->flags & NATTEN_FLAG_FORCE_TC) && !(dq_done && dk_done)) return NATTEN_E_UNSUPPORTED;
+        if (dq_done && dk_done) return NATTEN_OK;
+    }
+    return from_cuda(simt_qk_bwd(p->dtype, g, q, k, dlogits, dq_done ? nullptr : dq, dk_done ? nullptr : dk,
+                                 (cudaStream_t)stream));
 }
 
 int natten_av_fwd(const natten_params_t* p, const void* attn, const void* v, void* out, void* stream)
@@ -183,6 +199,14 @@ int natten_av_fwd(const natten_params_t* p, const void* attn, const void* v, voi
     if (rc) return rc;
     if (g.B == 0) return NATTEN_OK;
     if (!attn || !v || !out || g.extents || g.n_extra) return NATTEN_E_INVALID;
+    if (!(p->flags & NATTEN_FLAG_FORCE_SIMT)) {
+        Geo gv = g;
+        gv.D = g.Dv;
+        rc = tc_apply(p->dtype, gv, attn, v, g.vs, 1.f, false, out, (cudaStream_t)stream);
+        if (rc == 0) { t_last_path = NATTEN_PATH_TCGEN05; return NATTEN_OK; }
+        if (rc > 0) return rc;
+        if (p->flags & NATTEN_FLAG_FORCE_TC) return NATTEN_E_UNSUPPORTED;
+    }
     t_last_path = NATTEN_PATH_SIMT;
     return from_cuda(simt_av_fwd(p->dtype, g, attn, v, out, (cudaStream_t)stream));
 }
@@ -198,7 +222,8 @@ int natten_av_bwd(const natten_params_t* p, const void* attn, const void* v, con
     set_vec_ok(g, p->dtype, false, false, true, {v, dout});
     t_last_path = NATTEN_PATH_SIMT;
     // d attn[row, slot] = <dout[row], v[key of slot]> is the scores product with x = dout (contiguous rows,
-    // indexed by position when the stride is 1); dV stays a gather over the inverse neighbourhood.
+    // indexed by position when the stride is 1); dV gathers attn * dout over the inverse neighbourhood.
+    bool da_done = false, dv_done = false;
     bool unit_stride = true;
     for (int a = 0; a < g.rank; ++a) unit_stride = unit_stride && g.st[a] == 1;
     if (!(p->flags & NATTEN_FLAG_FORCE_SIMT) && unit_stride) {
@@ -207,13 +232,16 @@ int natten_av_bwd(const natten_params_t* p, const void* attn, const void* v, con
         const long long dos[3] = {g.otot * (long long)g.Hq * g.Dv, (long long)g.Hq * g.Dv, g.Dv};
         rc = tc_scores(p->dtype, gv, dout, dos, v, g.vs, 1.f, false, dattn, (cudaStream_t)stream);
         if (rc > 0) return rc;
-        if (rc == 0) {
-            t_last_path = NATTEN_PATH_TCGEN05;
-            return from_cuda(simt_av_bwd(p->dtype, g, attn, v, dout, nullptr, dv, (cudaStream_t)stream));
-        }
+        da_done = rc == 0;
+        rc = tc_gather(p->dtype, gv, attn, dout, dos, 1.f, dv, (cudaStream_t)stream);
+        if (rc > 0) return rc;
+        dv_done = rc == 0;
+        if (da_done || dv_done) t_last_path = NATTEN_PATH_TCGEN05;
+        if (da_done && dv_done) return NATTEN_OK;
     }
-    if (p->flags & NATTEN_FLAG_FORCE_TC) return NATTEN_E_UNSUPPORTED;
-    return from_cuda(simt_av_bwd(p->dtype, g, attn, v, dout, dattn, dv, (cudaStream_t)stream));
+    if ((p->flags & NATTEN_FLAG_FORCE_TC) && !(da_done && dv_done)) return NATTEN_E_UNSUPPORTED;
+    return from_cuda(simt_av_bwd(p->dtype, g, attn, v, dout, da_done ? nullptr : dattn, dv_done ? nullptr : dv,
+                                 (cudaStream_t)stream));
 }
 
 const char* natten_strerror(int code)

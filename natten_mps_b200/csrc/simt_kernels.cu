@@ -1375,14 +1375,14 @@ cudaError_t qk_bwd_t(const Geo& g, const void* q, const void* k, const void* dlo
     const long long krows = (long long)g.B * g.ltot * g.Hkv;
     bool partial = false;
     for (int a = 0; a < g.rank; ++a) partial = partial || g.st[a] != 1;
-    if (partial) {
+    if (partial && dq) {
         cudaError_t err = cudaMemsetAsync(dq, 0, sizeof(T) * (size_t)g.B * g.ltot * g.Hq * g.D, s);
         if (err != cudaSuccess) return err;
     }
     bool vec = false;
     if constexpr (sizeof(T) == 2)
         vec = split_vec_ok(g, g.D, {q, k, dq, dk}, {g.qs[0], g.qs[1], g.qs[2], g.ks[0], g.ks[1], g.ks[2]}, g.ks[1]);
-    if (qrows > 0) {
+    if (qrows > 0 && dq) {                        // dq == nullptr: another kernel has produced it
         if (vec) {
             if constexpr (sizeof(T) == 2) {
                 const size_t smem = (size_t)kWarps * g.ktot * sizeof(int);
@@ -1398,7 +1398,7 @@ cudaError_t qk_bwd_t(const Geo& g, const void* q, const void* k, const void* dlo
         }
         ++g_launches;
     }
-    if (krows > 0) {
+    if (krows > 0 && dk) {
         if (vec) {
             if constexpr (sizeof(T) == 2) {
                 NATTEN_DISPATCH_LPR(g.D, LPR,
@@ -1463,7 +1463,7 @@ cudaError_t av_bwd_t(const Geo& g, const void* attn, const void* v, const void* 
         }
         ++g_launches;
     }
-    if (krows > 0) {
+    if (krows > 0 && dv) {
         if (vec) {
             if constexpr (sizeof(T) == 2) {
                 NATTEN_DISPATCH_LPR(g.Dv, LPR,

@@ -17,6 +17,13 @@ size_t tc_bwd_workspace_bytes(int dtype, const Geo& g);
 // input position with strides xs (batch, token, head); masked slots get -inf (neg_inf) or 0.
 int tc_scores(int dtype, const Geo& g, const void* x, const long long xs[3], const void* y, const long long ys[3],
               float scale, bool neg_inf, void* out, cudaStream_t s);
+// out[row] = scale * sum_slot w[row, slot] * y[key of slot] (AV forward; QK backward w.r.t. q).
+int tc_apply(int dtype, const Geo& g, const void* w, const void* y, const long long ys[3], float scale,
+             bool out_by_position, void* out, cudaStream_t s);
+// dst[key] = scale * sum over attending (query, head) pairs of w[query, slot] * x[query]  (dK of the QK backward,
+// dV of the AV backward); unit stride.
+int tc_gather(int dtype, const Geo& g, const void* w, const void* x, const long long xs[3], float scale,
+              void* dst, cudaStream_t s);
 void tc_count_launch();
 unsigned long long tc_launch_count();
 // 0 = clean; 1 = some kernel gave up on a bounded wait (synchronises the device).

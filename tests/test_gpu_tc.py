@@ -281,3 +281,54 @@ def test_tc_av_backward_matches_simt(case, dtype):
     for name, a, r in (("dattn", da, ref_da), ("dv", dv, ref_dv)):
         err = (a.float() - r.float()).abs().max().item()
         assert err <= 2e-2 * max(1.0, r.float().abs().max().item()), f"{name} differs by {err}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", SPLIT_CASES, ids=_split_id)
+def test_tc_av_forward_matches_simt(case, dtype):
+    spatial, B, Hq, Hkv, ks, dil, st, causal, D = case
+    g = torch.Generator(device="cpu").manual_seed(41)
+    ktot = 1
+    for kk in ks:
+        ktot *= kk
+    osp = [-(-n // s) for n, s in zip(spatial, st)]
+    attn = torch.softmax(torch.randn((B, *osp, Hq, ktot), generator=g), dim=-1).to(dtype).cuda()
+    v = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    try:
+        _cabi.set_force("simt")
+        ref = _backend.av_forward(attn, v, ks, dil, st, causal)
+        _cabi.set_force("tc")
+        got = _backend.av_forward(attn, v, ks, dil, st, causal)
+        assert _cabi.last_path() == "tcgen05"
+    finally:
+        _cabi.set_force(None)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    err = (got.float() - ref.float()).abs().max().item()
+    assert err <= 2e-2 * max(1.0, ref.float().abs().max().item()), f"out differs by {err}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", [c for c in SPLIT_CASES if all(s == 1 for s in c[6])], ids=_split_id)
+def test_tc_qk_backward_matches_simt(case, dtype):
+    spatial, B, Hq, Hkv, ks, dil, st, causal, D = case
+    g = torch.Generator(device="cpu").manual_seed(43)
+    ktot = 1
+    for kk in ks:
+        ktot *= kk
+    q = torch.randn((B, *spatial, Hq, D), generator=g).to(dtype).cuda()
+    k = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    dl = torch.randn((B, *spatial, Hq, ktot), generator=g).to(dtype).cuda()
+    try:
+        _cabi.set_force("simt")
+        ref_dq, ref_dk = _backend.qk_backward(dl, q, k, ks, dil, st, causal, D ** -0.5)
+        _cabi.set_force("tc")
+        dq, dk = _backend.qk_backward(dl, q, k, ks, dil, st, causal, D ** -0.5)
+        assert _cabi.last_path() == "tcgen05"
+    finally:
+        _cabi.set_force(None)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    for name, a, r in (("dq", dq, ref_dq), ("dk", dk, ref_dk)):
+        err = (a.float() - r.float()).abs().max().item()
+        assert err <= 2e-2 * max(1.0, r.float().abs().max().item()), f"{name} differs by {err}"
