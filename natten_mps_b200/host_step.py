@@ -21,7 +21,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from . import _backend
+from . import _cabi
 from .utils.params import (check_dilation_kernel_vs_input, check_kernel_size_vs_input,
                            check_stride_vs_kernel, normalize_kernel_size, normalize_tuple_param)
 
@@ -55,6 +55,7 @@ class HostStep:
         self._host = None            # pinned result buffers, kept between calls
         self._key = None
         self._free = []              # per slice: event after which its staging buffers may be overwritten
+        self._copied = []            # per slice: event after which its device results may be overwritten
 
     # -- buffers ------------------------------------------------------------------------
     def _bounds(self, batch: int):
@@ -70,12 +71,33 @@ class HostStep:
         if key == self._key:
             return
         dev = self.device
-        self._stage = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in (q, k, v, q)]
-        osp = tuple(-(-n // s) for n, s in zip(q.shape[1:1 + self.rank], self.st))
+        rank = self.rank
+        osp = tuple(-(-n // s) for n, s in zip(q.shape[1:1 + rank], self.st))
         out_shape = (q.shape[0], *osp, q.shape[-2], v.shape[-1])
-        self._stage[3] = torch.empty(out_shape, dtype=q.dtype, device=dev)       # dout
+        with torch.cuda.device(dev):
+            # inputs (q, k, v, dout) and every result live in buffers that are allocated once:
+            # the step itself never touches the allocator
+            self._stage = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in (q, k, v)]
+            self._stage.append(torch.empty(out_shape, dtype=q.dtype, device=dev))          # dout
+            acc = torch.float64 if q.dtype == torch.float64 else torch.float32
+            self._dev_out = torch.empty(out_shape, dtype=q.dtype, device=dev)
+            self._dev_lse = torch.empty(out_shape[:-1], dtype=acc, device=dev)
+            self._dev_grads = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in (q, k, v)]
         shapes = [out_shape, q.shape, k.shape, v.shape]
         self._host = [torch.empty(s, dtype=q.dtype).pin_memory() for s in shapes]
+        # one parameter block per slice (slices differ in batch size only), one workspace for all
+        lib = _cabi.lib()
+        scale = q.shape[-1] ** -0.5 if self.scale is None else float(self.scale)
+        self._params = []
+        ws_bytes = 256
+        for lo, hi in self._bounds(q.shape[0]):
+            qs, ks_, vs = (_cabi.token_strides(t[lo:hi], rank) for t in self._stage[:3])
+            prm = _cabi.make_params(rank, q.dtype, hi - lo, q.shape[-2], k.shape[-2], q.shape[-1], v.shape[-1],
+                                    q.shape[1:1 + rank], self.ks, self.st, self.dil, self.causal, scale, 0,
+                                    qs, ks_, vs)
+            self._params.append(prm)
+            ws_bytes = max(ws_bytes, int(lib.natten_workspace_bytes(prm, _cabi.OP_FUSED_BWD)))
+        self._ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         self._key = key
 
     # -- the step -----------------------------------------------------------------------
@@ -94,7 +116,6 @@ class HostStep:
         spatial = tuple(q.shape[1:1 + self.rank])
         check_kernel_size_vs_input(self.ks, spatial)
         check_dilation_kernel_vs_input(self.dil, self.ks, spatial)
-        scale = q.shape[-1] ** -0.5 if self.scale is None else float(self.scale)
         self._prepare(q, k, v)
         if tuple(dout.shape) != tuple(self._stage[3].shape):
             raise ValueError(f"dout must have shape {tuple(self._stage[3].shape)}.")
@@ -104,6 +125,7 @@ class HostStep:
         bounds = self._bounds(q.shape[0])
         if len(self._free) != len(bounds):
             self._free = [None] * len(bounds)
+            self._copied = [None] * len(bounds)
         srcs = (q, k, v, dout)
         for i, (lo, hi) in enumerate(bounds):
             with torch.cuda.stream(self._s_in):
@@ -115,21 +137,39 @@ class HostStep:
                 ready.record(self._s_in)
             with torch.cuda.stream(self._s_cmp):
                 self._s_cmp.wait_event(ready)
-                qd, kd, vd, gd = (t[lo:hi] for t in self._stage)
-                out, lse = _backend.fused_forward(qd, kd, vd, self.ks, self.st, self.dil, self.causal, scale)
-                dq, dk, dv, _, _ = _backend.fused_backward(qd, kd, vd, out, lse, gd, self.ks, self.st,
-                                                           self.dil, self.causal, scale)
+                if self._copied[i] is not None:   # the previous call's results of this slice are on the host
+                    self._s_cmp.wait_event(self._copied[i])
+                self._launch(i, lo, hi)
                 done = torch.cuda.Event()
                 done.record(self._s_cmp)
                 self._free[i] = done
             with torch.cuda.stream(self._s_out):
                 self._s_out.wait_event(done)
-                results = (out, dq, dk, dv) if self.want_out else (None, dq, dk, dv)
+                results = (self._dev_out if self.want_out else None, *self._dev_grads)
                 for dst, src in zip(self._host, results):
                     if src is not None:
-                        dst[lo:hi].copy_(src, non_blocking=True)
-                        src.record_stream(self._s_out)
+                        dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
+                copied = torch.cuda.Event()
+                copied.record(self._s_out)
+                self._copied[i] = copied
         return (self._host[0] if self.want_out else None, self._host[1], self._host[2], self._host[3])
+
+    def _launch(self, i: int, lo: int, hi: int) -> None:
+        """Forward + backward of batch slice [lo, hi) on the current (compute) stream, through the C ABI."""
+        lib = _cabi.lib()
+        prm = self._params[i]
+        q, k, v, go = (t[lo:hi] for t in self._stage)
+        out, lse = self._dev_out[lo:hi], self._dev_lse[lo:hi]
+        dq, dk, dv = (t[lo:hi] for t in self._dev_grads)
+        stream = _cabi.stream_of(q)
+        with torch.cuda.device(self.device):
+            rc = lib.natten_fused_fwd(prm, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), None, None, _cabi.ptr(out),
+                                      _cabi.ptr(lse), stream)
+            _cabi.check(rc, "natten_fused_fwd")
+            rc = lib.natten_fused_bwd(prm, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), None, None, _cabi.ptr(out),
+                                      _cabi.ptr(lse), _cabi.ptr(go), None, _cabi.ptr(dq), _cabi.ptr(dk), _cabi.ptr(dv),
+                                      None, None, _cabi.ptr(self._ws), self._ws.numel(), stream)
+            _cabi.check(rc, "natten_fused_bwd")
 
     def wait(self):
         """Make the caller's current stream wait for everything queued so far (the copies out included)."""
