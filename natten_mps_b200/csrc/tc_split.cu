@@ -209,7 +209,7 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             e[a] = (first + P.K[a] < Lp[a] ? first + P.K[a] : Lp[a]) - lo[a];
         }
         if (!valid_q) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
-        if (team == 0) rowout[row] = valid_q ? ((long long)b * P.otot + oflat) * P.Hq + h : -1;
+        if (team == 0) rowout[row] = valid_q ? (((long long)b * P.otot + oflat) * P.Hq + h) * ktot : -1;   // element offset
         // column jj of a chunk sits at box offset (j0, j1, j2): its slot relative to the chunk's first column
         if (tid < 128) {
             const int j2 = tid & (P.cb[2] - 1);
@@ -266,6 +266,7 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             const int base = ((ci[0] * P.cb[0] - fs[0]) * P.K[1] + (ci[1] * P.cb[1] - fs[1])) * P.K[2] + (ci[2] * P.cb[2] - fs[2]);
             ok = ok && mbar_wait(bar_s, c & 1, abort_flag);
             tc_fence_after();
+            uint16_t* dstp = myrow + base;        // slot 0 of this chunk's first column, for this row
 #pragma unroll
             for (int pc = 0; pc < 2; ++pc) {
                 if (!__any_sync(0xffffffffu, words[pc] != 0u)) continue;
@@ -273,15 +274,12 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 tmem_ld32(trow + 64 * team + 32 * pc, s);
                 tmem_ld_wait();
                 if (ok) {
+                    const int* cs = colslot + 64 * team + 32 * pc;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if ((words[pc] >> i) & 1u) {
-                            const float v = __uint_as_float(s[i]) * scale;
-                            uint16_t bits;
-                            if (BF16) { const __nv_bfloat16 t = __float2bfloat16_rn(v); bits = *reinterpret_cast<const uint16_t*>(&t); }
-                            else { const __half t = __float2half_rn(v); bits = *reinterpret_cast<const uint16_t*>(&t); }
-                            myrow[base + colslot[64 * team + 32 * pc + i]] = bits;
-                        }
+                    for (int i = 0; i < 32; i += 2) {     // pairs: one conversion for two columns
+                        const uint32_t both = cvt_pack<BF16>(__uint_as_float(s[i]) * scale, __uint_as_float(s[i + 1]) * scale);
+                        if ((words[pc] >> i) & 1u) dstp[cs[i]] = static_cast<uint16_t>(both & 0xFFFFu);
+                        if ((words[pc] >> (i + 1)) & 1u) dstp[cs[i + 1]] = static_cast<uint16_t>(both >> 16);
                     }
                 }
             }
@@ -292,13 +290,16 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         // ---- the tile is complete: coalesced copy to the output ----
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (ok) {
+            // consecutive threads copy consecutive elements of a row: 256 elements ahead = dr rows and dj slots
             int r = tid / ktot, j = tid - r * ktot;
+            const int dr = 256 / ktot, dj = 256 - dr * ktot;
             const int total = kTileRows * ktot;
             for (int idx = tid; idx < total; idx += 256) {
-                const long long orow = rowout[r];
-                if (orow >= 0) out[orow * ktot + j] = tile[idx];
-                j += 256;
-                while (j >= ktot) { j -= ktot; ++r; }
+                const long long off = rowout[r];
+                if (off >= 0) out[off + j] = tile[idx];
+                r += dr;
+                j += dj;
+                if (j >= ktot) { j -= ktot; ++r; }
             }
         }
     }
@@ -424,7 +425,7 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
         const long long wrow = ((long long)b * P.otot + oflat) * P.Hq + h;          // row of w (by output position)
         orow = out_by_position ? ((long long)b * P.ltot + pflat) * P.Hq + h : wrow;
         if (!valid) orow = -1;
-        if (team == 0) rowout[row] = valid ? wrow : -1;
+        if (team == 0) rowout[row] = valid ? wrow * ktot : -1;                      // element offset of the row of w
         if (tid < 128) {
             const int j2 = tid & (P.cb[2] - 1);
             const int j1 = (tid >> P.cb2_log) & (P.cb[1] - 1);
@@ -463,12 +464,14 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
         // ---- stage this tile's weights: rows are contiguous runs of `ktot` values ----
         {
             int r = tid / ktot, j = tid - r * ktot;
+            const int dr = 256 / ktot, dj = 256 - dr * ktot;
             const int total = kTileRows * ktot;
             for (int idx = tid; idx < total; idx += 256) {
-                const long long wr = rowout[r];
-                wt[idx] = wr >= 0 ? w[wr * ktot + j] : static_cast<uint16_t>(0);
-                j += 256;
-                while (j >= ktot) { j -= ktot; ++r; }
+                const long long off = rowout[r];
+                wt[idx] = off >= 0 ? w[off + j] : static_cast<uint16_t>(0);
+                r += dr;
+                j += dj;
+                if (j >= ktot) { j -= ktot; ++r; }
             }
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -480,6 +483,7 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
 #pragma unroll
             for (int pc = 0; pc < 2; ++pc) words[pc] = piece_word(P, ci, 2 * team + pc, f, e);
             const int base = ((ci[0] * P.cb[0] - fs[0]) * P.K[1] + (ci[1] * P.cb[1] - fs[1])) * P.K[2] + (ci[2] * P.cb[2] - fs[2]);
+            const uint16_t* srcp = myrow + base;  // slot 0 of this chunk's first column, for this row
             // P buffer c & 1 was last read by the product of chunk c - 2
             if (c >= 2) {
                 ok = ok && mbar_wait(bar_o + 8 * (c & 1), ((c - 2) >> 1) & 1, abort_flag);
@@ -493,8 +497,8 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
                     for (int i = 0; i < 16; ++i) {
                         const int c0 = 64 * team + 32 * pc + 2 * i;
                         uint32_t lo16 = 0u, hi16 = 0u;
-                        if ((words[pc] >> (2 * i)) & 1u) lo16 = myrow[base + colslot[c0]];
-                        if ((words[pc] >> (2 * i + 1)) & 1u) hi16 = myrow[base + colslot[c0 + 1]];
+                        if ((words[pc] >> (2 * i)) & 1u) lo16 = srcp[colslot[c0]];
+                        if ((words[pc] >> (2 * i + 1)) & 1u) hi16 = srcp[colslot[c0 + 1]];
                         packed[i] = lo16 | (hi16 << 16);
                     }
                 } else {
