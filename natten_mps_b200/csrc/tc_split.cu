@@ -632,7 +632,6 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::kBar + 64);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::kBar + 72);
     long long* colrow = reinterpret_cast<long long*>(smem + SM::kColRow);
-    int* colfirst = reinterpret_cast<int*>(smem + SM::kColFirst);
     const uint32_t bar_x = sbase + SM::kBar + 0;         // [3] X chunk landed
     const uint32_t bar_p = sbase + SM::kBar + 48;        // [2] P^T buffer b stored by every thread
     const uint32_t bar_o = sbase + SM::kBar + 32;        // [2] the MMAs that read P buffer b have finished
@@ -672,6 +671,7 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     int f[3] = {0, 0, 0}, e[3] = {0, 0, 0}, kx[3] = {0, 0, 0};
     const int row = quad * 32 + lane;
     long long drow = -1;
+    int keyslot = 0;
     if (warp < 8) {
         int ri[3];
         row_offsets(P, row, ri);
@@ -689,6 +689,7 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
         if (!valid) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
         else drow = ((long long)b * P.ltot + pflat) * P.Hkv + hk;
+        keyslot = (kx[0] * P.K[1] + kx[1]) * P.K[2] + kx[2];
     }
     tc_fence_before();
     __syncthreads();
@@ -718,24 +719,29 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
     } else {
         const uint32_t trow = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+        const uint16_t* wkey = w + keyslot;
         bool ok = true;
         int ci[3] = {0, 0, 0}, hc = hk * P.group;
         for (int c = 0; c < total; ++c) {
             // ---- per-column tables of this chunk (one thread per column) ----
+            // The slot of key kx in the window of query xq is linear in both: (kx - first(xq)) folded over the
+            // axes = keyslot(kx) - firstslot(xq).  The table holds, per column, the element offset of the
+            // query's row of w minus firstslot; a thread adds its own keyslot.
             long long* crow = colrow + (c & 1) * 128;
-            int* cfirst = colfirst + (c & 1) * 384;
             if (tid < 128) {
                 const int j[3] = {tid >> (P.cb2_log + P.cb1_log), (tid >> P.cb2_log) & (P.cb[1] - 1), tid & (P.cb[2] - 1)};
                 bool inside = true;
                 long long pflat = 0;
+                int firstslot = 0;
 #pragma unroll
                 for (int a = 0; a < 3; ++a) {
                     const int xq = boxlo[a] + ci[a] * P.cb[a] + j[a];
                     if (xq < 0 || xq >= Lp[a]) inside = false;
                     pflat = pflat * P.L[a] + (rg[a] + P.dil[a] * xq);
-                    cfirst[a * 128 + tid] = P.causal[a] ? xq - (P.K[a] - 1) : tc_window_start(xq, Lp[a], P.K[a]);
+                    const int first = P.causal[a] ? xq - (P.K[a] - 1) : tc_window_start(xq, Lp[a], P.K[a]);
+                    firstslot = firstslot * P.K[a] + first;
                 }
-                crow[tid] = inside ? (((long long)b * P.ltot + pflat) * P.Hq + hc) * ktot : -1;
+                crow[tid] = inside ? (((long long)b * P.ltot + pflat) * P.Hq + hc) * ktot - firstslot : 0;
             }
             asm volatile("bar.sync 1, 256;" ::: "memory");
             uint32_t words[2];
@@ -755,10 +761,7 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 #pragma unroll
                         for (int u = 0; u < 2; ++u) {
                             const int col = 64 * team + 32 * pc + 2 * i + u;
-                            if ((words[pc] >> (2 * i + u)) & 1u) {
-                                const int s0 = kx[0] - cfirst[col], s1 = kx[1] - cfirst[128 + col], s2 = kx[2] - cfirst[256 + col];
-                                v16[u] = w[crow[col] + (s0 * P.K[1] + s1) * P.K[2] + s2];
-                            }
+                            if ((words[pc] >> (2 * i + u)) & 1u) v16[u] = wkey[crow[col]];
                         }
                         packed[i] = v16[0] | (v16[1] << 16);
                     }
