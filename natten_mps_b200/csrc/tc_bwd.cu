@@ -662,20 +662,34 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     }
 }
 
-// delta[row] = sum_d out[row,d]*dout[row,d] - dlse[row]      (DH/8 threads per row, 16 bytes each)
+// delta[row] = sum_d out[row,d]*dout[row,d] - dlse[row]      (DH/8 threads per row, 16 bytes each;
+// every thread takes kDeltaRows rows a grid-width apart, so that eight 16-byte loads are in flight)
+constexpr int kDeltaRows = 4;
 template <int DH, bool BF16>
-__global__ void tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ dout,
-                                const float* __restrict__ dlse, float* __restrict__ delta, long long rows)
+__global__ void __launch_bounds__(256)
+tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ dout,
+                const float* __restrict__ dlse, float* __restrict__ delta, long long rows, long long row_step)
 {
     constexpr int kPer = DH / 8;
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long row = t / kPer;
+    const long long row0 = t / kPer;
     const int part = (int)(t % kPer);
-    float acc = 0.f;
-    if (row < rows) {
-        const uint4 a = reinterpret_cast<const uint4*>(out + row * DH)[part];
-        const uint4 g = reinterpret_cast<const uint4*>(dout + row * DH)[part];
-        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+    uint4 a[kDeltaRows], g[kDeltaRows];
+#pragma unroll
+    for (int r = 0; r < kDeltaRows; ++r) {
+        const long long row = row0 + r * row_step;
+        a[r] = make_uint4(0, 0, 0, 0);
+        g[r] = make_uint4(0, 0, 0, 0);
+        if (row < rows) {
+            a[r] = reinterpret_cast<const uint4*>(out + row * DH)[part];
+            g[r] = reinterpret_cast<const uint4*>(dout + row * DH)[part];
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kDeltaRows; ++r) {
+        const long long row = row0 + r * row_step;
+        const uint32_t aw[4] = {a[r].x, a[r].y, a[r].z, a[r].w}, gw[4] = {g[r].x, g[r].y, g[r].z, g[r].w};
+        float acc = 0.f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             float2 x, y;
@@ -688,10 +702,10 @@ __global__ void tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t
             }
             acc += x.x * y.x + x.y * y.y;
         }
-    }
 #pragma unroll
-    for (int o = 1; o < kPer; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (row < rows && part == 0) delta[row] = acc - (dlse ? dlse[row] : 0.f);
+        for (int o = 1; o < kPer; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (row < rows && part == 0) delta[row] = acc - (dlse ? dlse[row] : 0.f);
+    }
 }
 
 template <int DH, bool BF16>
@@ -701,8 +715,13 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
 {
     const TcParams& p = plan.p;
     const long long qrows = (long long)g.B * g.ltot * g.Hq;
-    tc_delta_kernel<DH, BF16><<<(unsigned)((qrows * (DH / 8) + 255) / 256), 256, 0, s>>>(
-        (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, qrows);
+    {
+        // rows handled per pass of the grid: a whole number of blocks, a quarter of the rows each
+        const long long rows_per_block = 256 / (DH / 8);
+        const long long blocks = ((qrows + kDeltaRows - 1) / kDeltaRows + rows_per_block - 1) / rows_per_block;
+        tc_delta_kernel<DH, BF16><<<(unsigned)blocks, 256, 0, s>>>(
+            (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, qrows, blocks * rows_per_block);
+    }
     tc_count_launch();
 
     const long long dos[3] = {g.ltot * g.Hq * g.Dv, (long long)g.Hq * g.Dv, g.Dv};   // dout is contiguous
