@@ -131,12 +131,23 @@ const char* natten_strerror(int code);
 int natten_abi_version(void);
 int natten_last_path(void);              /* NATTEN_PATH_* of the last call, this thread */
 unsigned long long natten_launch_count(void); /* kernels launched by this library so far */
-/* Synchronises the device and reports whether any kernel of this library gave up
- * on a bounded wait since the library was loaded (NATTEN_OK or NATTEN_E_DEVICE). */
+/* Bounded waits.  Every barrier wait inside the tensor-core kernels has a cycle budget; a
+ * kernel whose wait runs out raises a status word on its device, stops touching data, frees
+ * what it holds and returns, and kernels launched afterwards on that device return at once
+ * without computing until the word is cleared.  The three calls below act on the current device.
+ *   natten_device_status  synchronises the device; NATTEN_OK or NATTEN_E_DEVICE.
+ *   natten_clear_status   synchronises, resets the word; 0 or a cudaError_t value.
+ *   natten_status_async   enqueues a 4-byte copy of the word into caller-owned pinned host
+ *                         memory on `stream` (no synchronisation, no allocation): non-zero there
+ *                         after the stream has passed that point means a kernel gave up.       */
 int natten_device_status(void);
-/* Debug aid: a device buffer of >= 256 int64 that one CTA of each tensor-core kernel
- * fills with clock64() stamps of its pipeline events (NULL switches it off).           */
-void natten_debug_trace(void* device_buffer);
+int natten_clear_status(void);
+int natten_status_async(int32_t* pinned_host_word, void* stream);
+/* Test hook: cycle budget of those waits (<= 0 restores the default of about two seconds) and a
+ * host-side fault to inject into the following launches (0 = none; 1 = the fused forward's first
+ * barrier expects more bytes than its loads deliver, so its wait runs out and the kernel
+ * returns with the status word set).  Process-wide.                                            */
+void natten_debug_wait(long long budget_cycles, int inject);
 
 #ifdef __cplusplus
 }

@@ -58,11 +58,13 @@ def fused_forward(q, k, v, kernel_size, stride, dilation, is_causal, scale: floa
     lse = torch.empty((B, *osp, Hq), dtype=_acc_dtype(q.dtype), device=q.device)
     p = _cabi.make_params(rank, q.dtype, B, Hq, Hkv, D, Dv, spatial, kernel_size, stride, dilation,
                           is_causal, scale, n_extra, qs, ks_, vs, ext)
+    _cabi.poll_status(q.device)
     with torch.cuda.device(q.device):
         rc = _cabi.lib().natten_fused_fwd(p, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v),
                                           _cabi.ptr(extra_k), _cabi.ptr(extra_v), _cabi.ptr(out),
                                           _cabi.ptr(lse), _cabi.stream_of(q))
     _cabi.check(rc, "natten_fused_fwd")
+    _cabi.track_status(q)
     return out, lse
 
 
@@ -97,6 +99,7 @@ def fused_backward(q, k, v, out, lse, dout, kernel_size, stride, dilation, is_ca
     L = _cabi.lib()
     ws_bytes = int(L.natten_workspace_bytes(p, _cabi.OP_FUSED_BWD))
     ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=q.device)
+    _cabi.poll_status(q.device)
     with torch.cuda.device(q.device):
         rc = L.natten_fused_bwd(p, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(extra_k),
                                 _cabi.ptr(extra_v), _cabi.ptr(out), _cabi.ptr(lse), _cabi.ptr(dout),
@@ -104,6 +107,7 @@ def fused_backward(q, k, v, out, lse, dout, kernel_size, stride, dilation, is_ca
                                 _cabi.ptr(dek), _cabi.ptr(dev), _cabi.ptr(ws), ws.numel(),
                                 _cabi.stream_of(q))
     _cabi.check(rc, "natten_fused_bwd")
+    _cabi.track_status(q)
     return dq, dk, dv, dek, dev
 
 
@@ -120,10 +124,12 @@ def qk_forward(q, k, kernel_size, dilation, stride, is_causal, scale: Optional[f
     logits = torch.empty((B, *_out_spatial(spatial, stride), Hq, ktot), dtype=q.dtype, device=q.device)
     p = _cabi.make_params(rank, q.dtype, B, Hq, k.shape[-2], D, D, spatial, kernel_size, stride,
                           dilation, is_causal, scale, 0, qs, ks_, ks_)
+    _cabi.poll_status(q.device)
     with torch.cuda.device(q.device):
         rc = _cabi.lib().natten_qk_fwd(p, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(logits),
                                        _cabi.stream_of(q))
     _cabi.check(rc, "natten_qk_fwd")
+    _cabi.track_status(q)
     return logits
 
 
@@ -139,10 +145,12 @@ def qk_backward(dlogits, q, k, kernel_size, dilation, stride, is_causal, scale: 
     dk = torch.empty(k.shape, dtype=k.dtype, device=q.device)
     p = _cabi.make_params(rank, q.dtype, B, Hq, k.shape[-2], D, D, spatial, kernel_size, stride,
                           dilation, is_causal, scale, 0, qs, ks_, ks_)
+    _cabi.poll_status(q.device)
     with torch.cuda.device(q.device):
         rc = _cabi.lib().natten_qk_bwd(p, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(dlogits),
                                        _cabi.ptr(dq), _cabi.ptr(dk), _cabi.stream_of(q))
     _cabi.check(rc, "natten_qk_bwd")
+    _cabi.track_status(q)
     return dq, dk
 
 
@@ -161,10 +169,12 @@ def av_forward(attn, v, kernel_size, dilation, stride, is_causal):
     attn = attn.to(v.dtype).contiguous()
     out = torch.empty((*attn.shape[:-1], v.shape[-1]), dtype=v.dtype, device=v.device)
     p = _av_params(attn, v, kernel_size, dilation, stride, is_causal, vs)
+    _cabi.poll_status(v.device)
     with torch.cuda.device(v.device):
         rc = _cabi.lib().natten_av_fwd(p, _cabi.ptr(attn), _cabi.ptr(v), _cabi.ptr(out),
                                        _cabi.stream_of(v))
     _cabi.check(rc, "natten_av_fwd")
+    _cabi.track_status(v)
     return out
 
 
@@ -177,8 +187,10 @@ def av_backward(dout, attn, v, kernel_size, dilation, stride, is_causal):
     dattn = torch.empty_like(attn)
     dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
     p = _av_params(attn, v, kernel_size, dilation, stride, is_causal, vs)
+    _cabi.poll_status(v.device)
     with torch.cuda.device(v.device):
         rc = _cabi.lib().natten_av_bwd(p, _cabi.ptr(attn), _cabi.ptr(v), _cabi.ptr(dout),
                                        _cabi.ptr(dattn), _cabi.ptr(dv), _cabi.stream_of(v))
     _cabi.check(rc, "natten_av_bwd")
+    _cabi.track_status(v)
     return dattn, dv

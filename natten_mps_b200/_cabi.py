@@ -23,7 +23,8 @@ EXPORTS = (
     "natten_fused_fwd", "natten_fused_bwd", "natten_workspace_bytes", "natten_qk_fwd",
     "natten_qk_bwd", "natten_av_fwd", "natten_av_bwd", "natten_strerror",
     "natten_abi_version", "natten_last_path", "natten_launch_count", "natten_device_status",
-    "natten_debug_trace", "natten_fused_bwd_static", "natten_static_scratch_bytes",
+    "natten_clear_status", "natten_status_async", "natten_debug_wait",
+    "natten_fused_bwd_static", "natten_static_scratch_bytes",
 )
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.float64: F64}
@@ -74,6 +75,9 @@ def lib():
         L.natten_strerror.argtypes = [ctypes.c_int]
         L.natten_strerror.restype = ctypes.c_char_p
         L.natten_launch_count.restype = ctypes.c_ulonglong
+        L.natten_status_async.argtypes = [vp, vp]
+        L.natten_debug_wait.argtypes = [ctypes.c_longlong, ctypes.c_int]
+        L.natten_debug_wait.restype = None
         for name in EXPORTS:
             getattr(L, name)
         _lib = L
@@ -93,6 +97,47 @@ def last_path() -> str:
 def device_status() -> int:
     """0 when no kernel ever gave up on a bounded wait (synchronises the device)."""
     return int(lib().natten_device_status())
+
+
+def clear_status() -> None:
+    """Reset the current device's status word after a kernel gave up on a wait (synchronises)."""
+    rc = int(lib().natten_clear_status())
+    for w in _status_words.values():
+        w.zero_()
+    if rc:
+        raise RuntimeError(f"natten_clear_status: CUDA error {rc}")
+
+
+# One pinned host word per device.  After every launch the library copies the device's status
+# word into it on the launching stream; the word is looked at (a plain host read) at the next
+# call and by ``poll_status``, so a kernel that gave up surfaces as a RuntimeError instead of
+# silently empty results.
+_status_words = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _status_words[idx] = w
+    return w
+
+
+def poll_status(device: torch.device) -> None:
+    """Raise if a kernel on ``device`` reported a timed-out wait (no synchronisation: sees what
+    the stream has copied back so far)."""
+    if int(_status_word(device)[0]) != 0:
+        raise RuntimeError(
+            "natten_b200: a tensor-core kernel gave up on a bounded wait (results since then are "
+            "invalid); call natten_mps_b200._cabi.clear_status() to re-arm the device")
+
+
+def track_status(t: torch.Tensor) -> None:
+    """Enqueue the status copy behind the kernels just launched on ``t``'s current stream."""
+    w = _status_word(t.device)
+    with torch.cuda.device(t.device):
+        lib().natten_status_async(ctypes.c_void_p(w.data_ptr()), stream_of(t))
 
 
 def launch_count() -> int:

@@ -261,7 +261,12 @@ const char* natten_strerror(int code)
 int natten_abi_version(void) { return 1; }
 int natten_last_path(void) { return t_last_path; }
 unsigned long long natten_launch_count(void) { return simt_launch_count() + tc_launch_count(); }
-void natten_debug_trace(void* device_buffer) { tc_set_trace(device_buffer); }
 int natten_device_status(void) { return tc_device_status() == 0 ? NATTEN_OK : NATTEN_E_DEVICE; }
+int natten_clear_status(void) { return tc_clear_status(); }
+int natten_status_async(int32_t* pinned_host_word, void* stream)
+{
+    return tc_status_async(reinterpret_cast<int*>(pinned_host_word), (cudaStream_t)stream);
+}
+void natten_debug_wait(long long budget_cycles, int inject) { tc_debug_wait(budget_cycles, inject); }
 
 } // extern "C"

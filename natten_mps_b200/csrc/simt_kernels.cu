@@ -12,6 +12,8 @@
 // results are bit-reproducible.
 #include "simt_kernels.cuh"
 
+#include "device_cache.cuh"
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>
@@ -1248,11 +1250,7 @@ bool launch_extra_fast(const Geo& g, const void* q, const void* ek, const void* 
             if (aligned) {
                 const size_t tsmem = (size_t)kExtraTileRows * (g.D + 8 + g.Dv + 8) * sizeof(T) + (size_t)kExtraGroup * W * sizeof(float) +
                                      (size_t)kExtraTileRows * (2 * kExtraGroup + 2) * sizeof(float) + (size_t)kExtraTileRows * 2 * sizeof(long long);
-                static bool attr_done = false;
-                if (!attr_done) {
-                    cudaFuncSetAttribute(extra_grad_tile_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-                    attr_done = true;
-                }
+                ensure_dynamic_smem((const void*)extra_grad_tile_kernel<T>, 96 * 1024);
                 extra_grad_tile_kernel<T><<<grid, 256, tsmem, s>>>(g, (const T*)q, (const T*)ek, (const T*)ev, (const float*)lse,
                     (const float*)delta, (const T*)dout, (const float*)dlse, (float*)partial, e0, ne);
                 tiled = true;

@@ -189,10 +189,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // debug clock stamps of CTA 5; key side uses the upper half of the buffer
-    long long* tr = (P.trace && blockIdx.x == 5) ? P.trace + (kKeySide ? 128 : 0) : nullptr;
-    int tn = 0;
-    auto stamp = [&](int base) { if (tr && tn < 56) tr[base + tn++] = clock64(); };
 
     // next work item of this CTA with anything to do for the tensor cores
     auto next_active = [&](unsigned w, BwdTile& X) {
@@ -211,8 +207,16 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             constexpr uint32_t idesc_kk = instr_desc(BF16 ? 1 : 0, kCols, 0, 0);    // both operands K-major
             constexpr uint32_t idesc_acc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A from TMEM, B MN-major
             const uint64_t dR1 = smem_desc(sbase + Smem::kR1, 16, 1024), dR2 = smem_desc(sbase + Smem::kR2, 16, 1024);
-            auto issue_s_dp = [&](unsigned g) {
+            auto issue_s_dp = [&](unsigned g, int cc, const BwdTile& X) {
                 const int s = g % kStages;
+                if (P.extents && cc < X.nbox) {      // rows of the column tiles past the sample's extent -> zeros
+                    int r = cc % X.nchunks;
+                    const int c2 = r % X.nc[2]; r /= X.nc[2];
+                    const int c1 = r % X.nc[1], c0 = r / X.nc[1];
+                    const int box0[3] = {X.boxlo[0] + c0 * P.cb[0], X.boxlo[1] + c1 * P.cb[1], X.boxlo[2] + c2 * P.cb[2]};
+                    zero_rows_past_extent(P, box0, X.Lp, kCols, Smem::kHalves, kColHalf,
+                                          smem + Smem::kC1 + s * kColTile, smem + Smem::kC2 + s * kColTile);
+                }
                 const uint64_t dC1 = smem_desc(sbase + Smem::kC1 + s * kColTile, 16, 1024);
                 const uint64_t dC2 = smem_desc(sbase + Smem::kC2 + s * kColTile, 16, 1024);
                 tc_fence_after();
@@ -314,12 +318,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             unsigned g = 0, tileno = 0;
             bool ok = true;
             while (work < nwork && ok) {
-                stamp(0);
-                ok = mbar_wait(bar_row, tileno & 1, abort_flag) &&
-                     mbar_wait(bar_col + 8 * (g % kStages), (g / kStages) & 1, abort_flag);
+                ok = mbar_wait(bar_row, tileno & 1, abort_flag, P.wait_budget) &&
+                     mbar_wait(bar_col + 8 * (g % kStages), (g / kStages) & 1, abort_flag, P.wait_budget);
                 if (!ok) break;
-                stamp(0);
-                issue_s_dp(g);
+                issue_s_dp(g, 0, T);
                 unsigned wnext = nwork;
                 for (int cc = 0; cc < T.total && ok; ++cc, ++g) {
                     const bool last = cc + 1 == T.total;
@@ -327,19 +329,17 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                         wnext = next_active(work + gridDim.x, Tn);
                         if (wnext < nwork) prefetch_rows(Tn);
                     }
-                    ok = mbar_wait(bar_sp, g & 1, abort_flag);               // S/dP consumed, P/dS stored
+                    ok = mbar_wait(bar_sp, g & 1, abort_flag, P.wait_budget);               // S/dP consumed, P/dS stored
                     if (!ok) break;
-                    stamp(0);
                     issue_acc(g, cc > 0);                                    // reads P/dS ...
                     if (!last) {
-                        ok = mbar_wait(bar_col + 8 * ((g + 1) % kStages), ((g + 1) / kStages) & 1, abort_flag);
+                        ok = mbar_wait(bar_col + 8 * ((g + 1) % kStages), ((g + 1) / kStages) & 1, abort_flag, P.wait_budget);
                         if (!ok) break;
-                        issue_s_dp(g + 1);                                   // ... before the next S/dP overwrite them
+                        issue_s_dp(g + 1, cc + 1, T);                                // ... before the next S/dP overwrite them
                     } else if (wnext < nwork) {
                         issue_rows(Tn);        // every S/dP product of this tile has finished: its rows are free
                     }
-                    stamp(0);
-                    ok = mbar_wait(bar_acc, g & 1, abort_flag);              // stage g % kStages is free again
+                    ok = mbar_wait(bar_acc, g & 1, abort_flag, P.wait_budget);              // stage g % kStages is free again
                     if (!ok) break;
                     issue_cols();
                 }
@@ -358,7 +358,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         // table of work item `work` (the item-th of this CTA) into slot item & 1
         auto write_table = [&](unsigned work, unsigned item, const BwdTile& X) {
             const unsigned slot = item & 1;
-            if (item >= 2) ok = ok && mbar_wait(bar_tab_empty + 8 * slot, ((item >> 1) - 1) & 1, abort_flag);
+            if (item >= 2) ok = ok && mbar_wait(bar_tab_empty + 8 * slot, ((item >> 1) - 1) & 1, abort_flag, P.wait_budget);
             uint8_t* tab = smem + Smem::kTab + slot * Smem::kTabBytes;
             RowEntry* rows = reinterpret_cast<RowEntry*>(tab);
 #pragma unroll 1
@@ -428,7 +428,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 int ci[3] = {0, 0, 0}, hc = T.hy * P.group;
                 for (int cc = 0; cc < T.total; ++cc, ++g) {
                     const int s = g % kStages;
-                    if (g >= (unsigned)kStages) ok = ok && mbar_wait(bar_free + 8 * s, ((g / kStages) - 1) & 1, abort_flag);
+                    if (g >= (unsigned)kStages) ok = ok && mbar_wait(bar_free + 8 * s, ((g / kStages) - 1) & 1, abort_flag, P.wait_budget);
                     float* st = stats + s * 128;
 #pragma unroll
                     for (int k = 0; k < kCols / 32; ++k) {
@@ -470,7 +470,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         for (unsigned work = blockIdx.x; work < nwork; work += gridDim.x, ++item) {
             // ---- this thread's row, from the helper warp's table ----
             const unsigned slot = item & 1;
-            ok = mbar_wait(bar_tab_full + 8 * slot, (item >> 1) & 1, abort_flag) && ok;
+            ok = mbar_wait(bar_tab_full + 8 * slot, (item >> 1) & 1, abort_flag, P.wait_budget) && ok;
             const uint8_t* tab = smem + Smem::kTab + slot * Smem::kTabBytes;
             const RowEntry en = reinterpret_cast<const RowEntry*>(tab)[quad * 32 + lane];
             const TileHead T = *reinterpret_cast<const TileHead*>(tab + 128 * 32);
@@ -531,13 +531,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 const bool any = __any_sync(0xffffffffu, mine);
                 const bool separable = kInner > 0 && !extra;
                 const bool full = !separable && __all_sync(0xffffffffu, word == 0xffffffffu);
-
-
-                if (warp == 0 && lane == 0) stamp(64);
-                ok = ok && mbar_wait(bar_s, g & 1, abort_flag);      // also: the previous chunk's P/dS were consumed
-                if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (g % kStages), (g / kStages) & 1, abort_flag);
+                ok = ok && mbar_wait(bar_s, g & 1, abort_flag, P.wait_budget);      // also: the previous chunk's P/dS were consumed
+                if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (g % kStages), (g / kStages) & 1, abort_flag, P.wait_budget);
                 tc_fence_after();
-                if (warp == 0 && lane == 0) stamp(64);
                 if (any) {
                     const float* stp = stats + (g % kStages) * 128 + 32 * piece;
                     const float4* st4 = reinterpret_cast<const float4*>(stp);
@@ -612,7 +608,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(bar_sp);
-                if (warp == 0 && lane == 0) stamp(64);
                 // next chunk (innermost axis fastest; wraps to the next query head on the key side)
                 if (++ci[2] == T.nc[2]) {
                     ci[2] = 0;
@@ -624,7 +619,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             }
 
             // ---- accumulators -> global: this warp owns 32 of the 64 channels ----
-            ok = ok && mbar_wait(bar_acc, (g - 1) & 1, abort_flag);
+            ok = ok && mbar_wait(bar_acc, (g - 1) & 1, abort_flag, P.wait_budget);
             tc_fence_after();
             // The TMEM loads are warp-collective: every lane takes part, only the stores are per row.
             const bool live = valid_row && ok;
@@ -653,6 +648,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         }
     }
 
+    if (*abort_flag) abort_grace_sleep();       // loads of a wait that gave up may still be landing
     tc_fence_before();
     __syncthreads();
     if (warp == kComputeWarps) {
@@ -747,12 +743,8 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
     const dim3 grid_k(persistent_grid(p.work_kv, DH == 64 ? 2 : 1));
     auto launch = [&](auto inner) {
         constexpr int kInner = decltype(inner)::value;
-        static bool attr_done = false;
-        if (!attr_done) {
-            cudaFuncSetAttribute(tc_bwd_kernel<DH, BF16, false, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
-            cudaFuncSetAttribute(tc_bwd_kernel<DH, BF16, true, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
-            attr_done = true;
-        }
+        ensure_dynamic_smem((const void*)tc_bwd_kernel<DH, BF16, false, kInner>, Smem::kTotal);
+        ensure_dynamic_smem((const void*)tc_bwd_kernel<DH, BF16, true, kInner>, Smem::kTotal);
         tc_bwd_kernel<DH, BF16, false, kInner><<<grid_q, kThreads, Smem::kTotal, s>>>(
             q_tile, do_tile, k_chunk, v_chunk, ek_chunk, ev_chunk, p, (const float*)lse, delta, (uint16_t*)dq, nullptr);
         tc_count_launch();
@@ -783,7 +775,6 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     Plan plan;
     if (!make_plan(g, plan, kCols)) return -2;
     plan.p.status = status_ptr();
-    plan.p.trace = trace_ptr();
     if (!plan.p.status) return -2;
     if (g.B == 0) return 0;
     if (g.Hq > 65535 || g.B > 65535) return -2;

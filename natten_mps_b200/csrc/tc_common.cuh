@@ -58,17 +58,28 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 // the shared abort flag is raised and the wait returns false; callers keep going
 // without touching the data so that the CTA always reaches its final barrier,
 // frees its TMEM and exits.
-constexpr long long kWaitBudgetCycles = 4000000000ll;   // about two seconds
+constexpr long long kWaitBudgetCycles = 4000000000ll;   // default budget: about two seconds
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long budget = kWaitBudgetCycles)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    // sleep at most 0.2 ms per try, and never longer than about a quarter of a short budget
+    const uint32_t nap = budget < 1600000ll ? static_cast<uint32_t>(budget >> 3) + 1000u : 200000u;
     while (true) {
-        if (mbar_try_wait_hint(bar, parity, 200000u)) return true;       // up to 0.2 ms asleep per try
+        if (mbar_try_wait_hint(bar, parity, nap)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1; return false; }
+        if (clock64() - t0 > budget) { *abort_flag = 1; return false; }
     }
+}
+
+// After a CTA has given up on a wait, bulk copies it issued may still be on their way into its
+// shared memory.  Before the CTA exits (and the memory goes to another CTA) it sleeps for a
+// bounded time that covers any load latency.
+__device__ __forceinline__ void abort_grace_sleep()
+{
+    for (int i = 0; i < 64; ++i) __nanosleep(1000u);       // about 64 microseconds
 }
 
 // ----------------------------------------------------------------------------- fences

@@ -26,21 +26,6 @@ namespace natten {
 using namespace tc;
 using namespace tcplan;
 
-__device__ int g_tc_status = 0;
-
-static long long* g_trace = nullptr;
-void tc_set_trace(void* p) { g_trace = reinterpret_cast<long long*>(p); }
-
-namespace tcplan {
-long long* trace_ptr() { return g_trace; }
-int* status_ptr()
-{
-    int* p = nullptr;
-    cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_tc_status);
-    return p;
-}
-} // namespace tcplan
-
 namespace {
 
 constexpr int kThreads = 288;            // 8 softmax warps + 1 TMA/MMA warp
@@ -86,7 +71,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y, b = blockIdx.z, hk = h / P.group;
     const int quad = warp & 3, team = (warp >> 2) & 1;        // softmax warps: TMEM lane quadrant, column half
-    const long long t_begin = clock64();
     const int prior_abort = *reinterpret_cast<volatile int*>(P.status);   // loaded early, used at barrier set-up
 
     // ---- CTA geometry -------------------------------------------------------
@@ -203,7 +187,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             mbar_init_fence();
             fence_async_smem();
             if (!*abort_flag) {
-                mbar_expect_tx(bar_q, SM::kTile);
+                mbar_expect_tx(bar_q, SM::kTile + (P.inject == 1 ? 16u : 0u));
 #pragma unroll
                 for (int hf = 0; hf < SM::kHalves; ++hf)
                     tma_load_5d(sbase + SM::kQ + hf * SM::kHalf, &tmQ, bar_q, h * DH + 64 * hf,
@@ -246,10 +230,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // debug clock stamps of CTA (5, 0, 0): forward uses entries [256, 384)
-    long long* tr = (P.trace && blockIdx.x == 5 && blockIdx.y == 0 && blockIdx.z == 0) ? P.trace + 256 : nullptr;
-    int tn = 0;
-    auto stamp = [&](int base) { if (tr && tn < 60) tr[base + tn++] = clock64(); };
 
     if (warp == 8) {
         // =====================================================================
@@ -259,7 +239,14 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             constexpr uint32_t idesc_qk = instr_desc(BF16 ? 1 : 0, kChunk, 0, 0);
             constexpr uint32_t idesc_pv = instr_desc(BF16 ? 1 : 0, DH, 0, 1);
             const uint64_t dq0 = smem_desc(sbase + SM::kQ, 16, 1024);
+            int qc[3] = {0, 0, 0};                   // chunk index per axis of the next Q K^T (per-sample extents only)
             auto issue_qk = [&](int c) {
+                if (P.extents && c < nnb) {
+                    const int box0[3] = {lo[0] + qc[0] * P.cb[0], lo[1] + qc[1] * P.cb[1], lo[2] + qc[2] * P.cb[2]};
+                    zero_rows_past_extent(P, box0, Lp, kChunk, SM::kHalves, SM::kHalf,
+                                          smem + SM::kK + (c % kStages) * SM::kTile, smem + SM::kV + (c % kStages) * SM::kTile);
+                    if (++qc[2] == nc[2]) { qc[2] = 0; if (++qc[1] == nc[1]) { qc[1] = 0; ++qc[0]; } }
+                }
                 const uint64_t dk0 = smem_desc(sbase + SM::kK + (c % kStages) * SM::kTile, 16, 1024);
                 tc_fence_after();
 #pragma unroll
@@ -279,35 +266,29 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     mma_ts(tmem + kColO, tmem + kColP + 8 * ks, dv0 + 128 * ks, idesc_pv, c > 0 || ks > 0);
                 mma_commit(bar_o);
             };
-
-            stamp(0);
-            bool ok = mbar_wait(bar_q, 0, abort_flag);
-            ok = ok && mbar_wait(bar_kv, 0, abort_flag);
-            stamp(0);
+            bool ok = mbar_wait(bar_q, 0, abort_flag, P.wait_budget);
+            ok = ok && mbar_wait(bar_kv, 0, abort_flag, P.wait_budget);
             if (ok) issue_qk(0);
-            stamp(0);
             for (int c = 0; c < nch && ok; ++c) {
                 if (kKeepScores) {       // S(c) sits in the threads' registers: the next scores may overwrite it
-                    ok = mbar_wait(bar_sr, c & 1, abort_flag);
+                    ok = mbar_wait(bar_sr, c & 1, abort_flag, P.wait_budget);
                     if (!ok) break;
                     if (c + 1 < nch) {
-                        ok = mbar_wait(bar_kv + 8 * ((c + 1) % kStages), ((c + 1) / kStages) & 1, abort_flag);
+                        ok = mbar_wait(bar_kv + 8 * ((c + 1) % kStages), ((c + 1) / kStages) & 1, abort_flag, P.wait_budget);
                         if (!ok) break;
                         issue_qk(c + 1);
                     }
                 }
-                ok = mbar_wait(bar_sp, c & 1, abort_flag);           // S(c) consumed, P(c) stored
+                ok = mbar_wait(bar_sp, c & 1, abort_flag, P.wait_budget);           // S(c) consumed, P(c) stored
                 if (!ok) break;
-                stamp(0);
                 if (!kKeepScores && c + 1 < nch) {                   // next scores first: the threads wait for them
-                    ok = mbar_wait(bar_kv + 8 * ((c + 1) % kStages), ((c + 1) / kStages) & 1, abort_flag);
+                    ok = mbar_wait(bar_kv + 8 * ((c + 1) % kStages), ((c + 1) / kStages) & 1, abort_flag, P.wait_budget);
                     if (!ok) break;
                     issue_qk(c + 1);
                 }
                 issue_pv(c);
-                stamp(0);
                 if (c + kStages < nch) {
-                    ok = mbar_wait(bar_o, c & 1, abort_flag);        // stage c % kStages is free again
+                    ok = mbar_wait(bar_o, c & 1, abort_flag, P.wait_budget);        // stage c % kStages is free again
                     if (!ok) break;
                     issue_kv();
                 }
@@ -361,7 +342,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 for (int pc = 0; pc < 2; ++pc) words[pc] = piece_word(P, ci, 2 * team + pc, f, e);
             }
 
-            ok = ok && mbar_wait(bar_s, c & 1, abort_flag);
+            ok = ok && mbar_wait(bar_s, c & 1, abort_flag, P.wait_budget);
             tc_fence_after();
             const bool any[2] = {__any_sync(0xffffffffu, words[0] != 0u) != 0, __any_sync(0xffffffffu, words[1] != 0u) != 0};
             uint32_t s0[kKeepScores ? 32 : 1], s1[kKeepScores ? 32 : 1];      // the chunk's scores (kKeepScores)
@@ -426,7 +407,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
             // ---- P(c-1) V has finished: P may be rewritten, O may be rescaled ----
             if (c > 0) {
-                ok = ok && mbar_wait(bar_o, (c - 1) & 1, abort_flag);
+                ok = ok && mbar_wait(bar_o, (c - 1) & 1, abort_flag, P.wait_budget);
                 tc_fence_after();
             }
             bool grow = false;
@@ -502,7 +483,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
             l += xsum[(1 - team) * 128 + row];
         }
-        ok = ok && mbar_wait(bar_o, (nch - 1) & 1, abort_flag);
+        ok = ok && mbar_wait(bar_o, (nch - 1) & 1, abort_flag, P.wait_budget);
         tc_fence_after();
         {
             const bool live = valid_q && ok;
@@ -530,9 +511,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
     }
 
+    if (*abort_flag) abort_grace_sleep();       // loads of a wait that gave up may still be landing
     tc_fence_before();
     __syncthreads();
-    if (tr && tid == 0) { tr[120] = t_begin; tr[121] = clock64(); }
     if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
@@ -560,7 +541,6 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
                           !encode_extra_map(&mev, ev, bf16, g.B, g.n_extra, g.Hkv, g.Dv, kChunk)))
         return -2;
     plan.p.status = status_ptr();
-    plan.p.trace = trace_ptr();
     if (!plan.p.status) return -2;
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= plan.p.grp_n[a];     // dilation groups that hold queries
@@ -573,11 +553,7 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
         constexpr bool kBf = decltype(bf)::value;
         constexpr int kInner = decltype(inner)::value;
         using SM = SmemMap<kDh>;
-        static bool once = false;
-        if (!once) {
-            cudaFuncSetAttribute(tc_fwd_kernel<kDh, kBf, kInner>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
-            once = true;
-        }
+        ensure_dynamic_smem((const void*)tc_fwd_kernel<kDh, kBf, kInner>, SM::kTotal);
         tc_fwd_kernel<kDh, kBf, kInner><<<grid, kThreads, SM::kTotal, s>>>(mq, mk, mv, mek, mev, plan.p, (uint16_t*)out, (float*)lse);
     };
     auto by_inner = [&](auto dh, auto bf) {
@@ -599,12 +575,5 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
 static unsigned long long g_tc_launches = 0;
 void tc_count_launch() { ++g_tc_launches; }
 unsigned long long tc_launch_count() { return g_tc_launches; }
-
-int tc_device_status()
-{
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
-    return v;
-}
 
 } // namespace natten

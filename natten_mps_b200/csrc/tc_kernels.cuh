@@ -28,7 +28,13 @@ void tc_count_launch();
 unsigned long long tc_launch_count();
 // 0 = clean; 1 = some kernel gave up on a bounded wait (synchronises the device).
 int tc_device_status();
-// Debug: device buffer (>= 256 long long) that one CTA of each tensor-core kernel fills with clock stamps.
-void tc_set_trace(void* device_buffer);
+// Reset the status word of the current device (synchronises); returns a cudaError_t value.
+int tc_clear_status();
+// Enqueue a copy of the current device's status word into `host_word` (pinned host memory) on stream s.
+int tc_status_async(int* host_word, cudaStream_t s);
+// Test hooks: cycle budget of the barrier waits (<= 0 restores the default) and a fault to inject
+// on the host side of the next launches (0 = none, 1 = the fused forward's first barrier expects
+// more bytes than its loads deliver, so that its wait runs out).
+void tc_debug_wait(long long budget_cycles, int inject);
 
 } // namespace natten

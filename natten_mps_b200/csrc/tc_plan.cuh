@@ -1,6 +1,7 @@
 // Shared by the tensor-core kernels: launch geometry (tile / chunk shapes), tensor-map
 // encoding, eligibility and the per-row mask words.
 #pragma once
+#include "device_cache.cuh"
 #include "geometry.cuh"
 #include "tc_common.cuh"
 
@@ -12,6 +13,8 @@ namespace natten {
 namespace tcplan {
 
 using namespace tc;
+using natten::ensure_dynamic_smem;
+using natten::sm_count;
 
 constexpr int kTileRows = 128;           // rows per CTA     (MMA M)
 constexpr int kChunk = 128;              // columns per chunk (MMA N of S, K of the second MMA)
@@ -32,7 +35,8 @@ struct TcParams {
     const int* extents;
     long long ltot;
     int* status;
-    long long* trace;      // optional device buffer for clock stamps of one CTA (nullptr = off)
+    long long wait_budget; // cycles a barrier wait may take before the CTA gives up
+    int inject;            // test hook: 1 = the forward's first query barrier expects bytes that never arrive
     // Output stride (forward only).  Inside dilation group r of an axis the queries sit at the
     // sub-grid indices x = qx0[axis][r] + qstep[axis] * i, i = 0, 1, ... (qx0 < 0: the group holds no
     // query); with stride 1 that is every index.  Output position = input position / st.
@@ -43,6 +47,10 @@ struct TcParams {
     unsigned grp_mul[3];
     long long otot;
 };
+
+int* status_ptr();   // device address of the library's status word on the current device (tc_status.cu)
+long long debug_wait_budget();   // barrier-wait budget in cycles (test hook; default kWaitBudgetCycles)
+int debug_inject();              // test hook, see TcParams::inject
 
 // n / d with a precomputed multiplier; exact while n * d < 2^32 (checked on the host).
 __device__ __forceinline__ unsigned fast_div(unsigned n, unsigned mul) { return mul ? __umulhi(n, mul) : n; }
@@ -120,6 +128,36 @@ __device__ __forceinline__ uint32_t piece_word(const TcParams& P, const int (&ci
         }
     }
     return w;
+}
+
+// Per-sample extents: a column chunk may reach past the sample's extent into rows that exist in
+// memory (padding up to the tensor's extent) but do not belong to the sample.  The reference never
+// reads them (it slices each sample, src/natten_mps/_core/pure.py:586-599); here their
+// probabilities are zero, but a zero times a non-finite padding value would still poison the
+// accumulating product, so those rows of the staged tiles are overwritten with zeros before the
+// tensor cores read them.  Called by one thread; box0[] = sub-grid coordinate of the chunk's
+// first column per axis; `tiles` = the two [cols x 64*halves] tiles of the stage.
+__device__ __forceinline__ void zero_rows_past_extent(const TcParams& P, const int (&box0)[3], const int (&Lp)[3],
+                                                      int cols, int halves, int half_bytes,
+                                                      uint8_t* tile1, uint8_t* tile2)
+{
+    bool crosses = false;
+#pragma unroll
+    for (int a = 0; a < 3; ++a) crosses = crosses || (box0[a] + P.cb[a] > Lp[a]);
+    if (!crosses) return;
+    for (int j = 0; j < cols; ++j) {
+        const int j2 = j & (P.cb[2] - 1);
+        const int j1 = (j >> P.cb2_log) & (P.cb[1] - 1);
+        const int j0 = j >> (P.cb2_log + P.cb1_log);
+        if (box0[0] + j0 < Lp[0] && box0[1] + j1 < Lp[1] && box0[2] + j2 < Lp[2]) continue;
+        for (int hf = 0; hf < halves; ++hf) {
+            uint4* r1 = reinterpret_cast<uint4*>(tile1 + hf * half_bytes + j * 128);
+            uint4* r2 = reinterpret_cast<uint4*>(tile2 + hf * half_bytes + j * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { r1[i] = make_uint4(0, 0, 0, 0); r2[i] = make_uint4(0, 0, 0, 0); }
+        }
+    }
+    fence_async_smem();          // the tensor cores read shared memory through the async proxy
 }
 
 // Packed 16-bit pair arithmetic (element 0 in the low half).
@@ -278,6 +316,8 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk, bool with_st
     p.scale = (float)g.scale;
     p.extents = g.extents;
     p.ltot = g.ltot;
+    p.wait_budget = debug_wait_budget();
+    p.inject = debug_inject();
     return true;
 }
 
@@ -330,13 +370,7 @@ __device__ __forceinline__ uint32_t low_bits(int n)
 // CTAs of a persistent launch: `per_sm` per multiprocessor, never more than there is work.
 inline unsigned persistent_grid(unsigned work, int per_sm)
 {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    const unsigned cap = (unsigned)(sms * per_sm);
+    const unsigned cap = (unsigned)(sm_count() * per_sm);
     return work < cap ? work : cap;
 }
 
@@ -361,8 +395,6 @@ inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, c
     return true;
 }
 
-int* status_ptr();   // device address of the library's status word (defined in tc_fwd.cu)
-long long* trace_ptr();   // debug clock-stamp buffer set through natten_debug_trace (or nullptr)
 
 
 } // namespace tcplan

@@ -238,16 +238,16 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 }
                 mma_commit(bar_s);
             };
-            bool ok = mbar_wait(bar_x, 0, abort_flag) && mbar_wait(bar_y, 0, abort_flag);
+            bool ok = mbar_wait(bar_x, 0, abort_flag, P.wait_budget) && mbar_wait(bar_y, 0, abort_flag, P.wait_budget);
             if (ok) issue_s(0);
             for (int c = 0; c < nch && ok; ++c) {
-                ok = mbar_wait(bar_s, c & 1, abort_flag);            // the product is done: its Y stage is free
+                ok = mbar_wait(bar_s, c & 1, abort_flag, P.wait_budget);            // the product is done: its Y stage is free
                 if (!ok) break;
                 if (c + kStages < nch) issue_y();
-                ok = mbar_wait(bar_sp, c & 1, abort_flag);           // S(c) read by every thread
+                ok = mbar_wait(bar_sp, c & 1, abort_flag, P.wait_budget);           // S(c) read by every thread
                 if (!ok) break;
                 if (c + 1 < nch) {
-                    ok = mbar_wait(bar_y + 8 * ((c + 1) % kStages), ((c + 1) / kStages) & 1, abort_flag);
+                    ok = mbar_wait(bar_y + 8 * ((c + 1) % kStages), ((c + 1) / kStages) & 1, abort_flag, P.wait_budget);
                     if (!ok) break;
                     issue_s(c + 1);
                 }
@@ -264,7 +264,7 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             for (int pc = 0; pc < 2; ++pc) words[pc] = piece_word(P, ci, 2 * team + pc, f, e);
             // slot of the chunk's first column for this row
             const int base = ((ci[0] * P.cb[0] - fs[0]) * P.K[1] + (ci[1] * P.cb[1] - fs[1])) * P.K[2] + (ci[2] * P.cb[2] - fs[2]);
-            ok = ok && mbar_wait(bar_s, c & 1, abort_flag);
+            ok = ok && mbar_wait(bar_s, c & 1, abort_flag, P.wait_budget);
             tc_fence_after();
             uint16_t* dstp = myrow + base;        // slot 0 of this chunk's first column, for this row
 #pragma unroll
@@ -304,6 +304,7 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
     }
 
+    if (*abort_flag) abort_grace_sleep();       // loads of a wait that gave up may still be landing
     tc_fence_before();
     __syncthreads();
     if (warp == 8) {
@@ -319,13 +320,10 @@ int launch_scores(const Plan& plan, const CUtensorMap& mx, const CUtensorMap& my
 {
     using SM = SmemS<DH>;
     const size_t smem = (size_t)SM::kOut + (size_t)kTileRows * g.ktot * 2;
-    static size_t attr = 0;
-    if (smem > attr) {
-        if (cudaFuncSetAttribute(tc_scores_kernel<DH, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-            cudaGetLastError();
-            return -2;
-        }
-        attr = smem;
+    if (smem > kMaxDynamicSmem) return -2;
+    if (ensure_dynamic_smem((const void*)tc_scores_kernel<DH, BF16>, kMaxDynamicSmem) != cudaSuccess) {
+        cudaGetLastError();
+        return -2;
     }
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= plan.p.grp_n[a];
@@ -443,8 +441,8 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
             constexpr uint32_t idesc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A = P from TMEM, B = Y MN-major
             bool ok = true;
             for (int c = 0; c < nch && ok; ++c) {
-                ok = mbar_wait(bar_y + 8 * (c % kStages), (c / kStages) & 1, abort_flag) &&
-                     mbar_wait(bar_p + 8 * (c & 1), (c >> 1) & 1, abort_flag);
+                ok = mbar_wait(bar_y + 8 * (c % kStages), (c / kStages) & 1, abort_flag, P.wait_budget) &&
+                     mbar_wait(bar_p + 8 * (c & 1), (c >> 1) & 1, abort_flag, P.wait_budget);
                 if (!ok) break;
                 const uint64_t dy0 = smem_desc(sbase + SM::kY + (c % kStages) * SM::kTile, SM::kHalf, 1024);
                 tc_fence_after();
@@ -453,7 +451,7 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
                     mma_ts(tmem + SM::kColO, tmem + SM::kColP + 64 * (c & 1) + 8 * ks, dy0 + 128 * ks, idesc, c > 0 || ks > 0);
                 mma_commit(bar_o + 8 * (c & 1));
                 if (c >= 1 && c + 2 < nch) {             // the product before this one is done: its Y stage is free
-                    ok = mbar_wait(bar_o + 8 * ((c - 1) & 1), ((c - 1) >> 1) & 1, abort_flag);
+                    ok = mbar_wait(bar_o + 8 * ((c - 1) & 1), ((c - 1) >> 1) & 1, abort_flag, P.wait_budget);
                     if (!ok) break;
                     issue_y();
                 }
@@ -486,7 +484,7 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
             const uint16_t* srcp = myrow + base;  // slot 0 of this chunk's first column, for this row
             // P buffer c & 1 was last read by the product of chunk c - 2
             if (c >= 2) {
-                ok = ok && mbar_wait(bar_o + 8 * (c & 1), ((c - 2) >> 1) & 1, abort_flag);
+                ok = ok && mbar_wait(bar_o + 8 * (c & 1), ((c - 2) >> 1) & 1, abort_flag, P.wait_budget);
                 tc_fence_after();
             }
 #pragma unroll
@@ -513,7 +511,7 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
             if (++ci[2] == G.nc[2]) { ci[2] = 0; if (++ci[1] == G.nc[1]) { ci[1] = 0; ++ci[0]; } }
         }
         // ---- every product is in O: scale, write out this thread's channels ----
-        ok = ok && mbar_wait(bar_o + 8 * ((nch - 1) & 1), ((nch - 1) >> 1) & 1, abort_flag);
+        ok = ok && mbar_wait(bar_o + 8 * ((nch - 1) & 1), ((nch - 1) >> 1) & 1, abort_flag, P.wait_budget);
         tc_fence_after();
 #pragma unroll
         for (int part = 0; part < CH / 32; ++part) {
@@ -534,6 +532,7 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
         }
     }
 
+    if (*abort_flag) abort_grace_sleep();       // loads of a wait that gave up may still be landing
     tc_fence_before();
     __syncthreads();
     if (warp == 8) {
@@ -549,13 +548,10 @@ int launch_apply(const Plan& plan, const CUtensorMap& my, const Geo& g, const vo
 {
     using SM = SmemA<DH>;
     const size_t smem = (size_t)SM::kW + (size_t)kTileRows * g.ktot * 2;
-    static size_t attr = 0;
-    if (smem > attr) {
-        if (cudaFuncSetAttribute(tc_apply_kernel<DH, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-            cudaGetLastError();
-            return -2;
-        }
-        attr = smem;
+    if (smem > kMaxDynamicSmem) return -2;
+    if (ensure_dynamic_smem((const void*)tc_apply_kernel<DH, BF16>, kMaxDynamicSmem) != cudaSuccess) {
+        cudaGetLastError();
+        return -2;
     }
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= plan.p.grp_n[a];
@@ -701,8 +697,8 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             constexpr uint32_t idesc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A = P^T from TMEM, B = X MN-major
             bool ok = true;
             for (int c = 0; c < total && ok; ++c) {
-                ok = mbar_wait(bar_x + 8 * (c % kStages), (c / kStages) & 1, abort_flag) &&
-                     mbar_wait(bar_p + 8 * (c & 1), (c >> 1) & 1, abort_flag);
+                ok = mbar_wait(bar_x + 8 * (c % kStages), (c / kStages) & 1, abort_flag, P.wait_budget) &&
+                     mbar_wait(bar_p + 8 * (c & 1), (c >> 1) & 1, abort_flag, P.wait_budget);
                 if (!ok) break;
                 const uint64_t dx0 = smem_desc(sbase + SM::kX + (c % kStages) * SM::kTile, SM::kHalf, 1024);
                 tc_fence_after();
@@ -711,7 +707,7 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     mma_ts(tmem + SM::kColO, tmem + SM::kColP + 64 * (c & 1) + 8 * ks, dx0 + 128 * ks, idesc, c > 0 || ks > 0);
                 mma_commit(bar_o + 8 * (c & 1));
                 if (c >= 1 && c + 2 < total) {           // the product before this one is done: its X stage is free
-                    ok = mbar_wait(bar_o + 8 * ((c - 1) & 1), ((c - 1) >> 1) & 1, abort_flag);
+                    ok = mbar_wait(bar_o + 8 * ((c - 1) & 1), ((c - 1) >> 1) & 1, abort_flag, P.wait_budget);
                     if (!ok) break;
                     issue_x();
                 }
@@ -748,7 +744,7 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 #pragma unroll
             for (int pc = 0; pc < 2; ++pc) words[pc] = piece_word(P, ci, 2 * team + pc, f, e);
             if (c >= 2) {                         // P buffer c & 1 was last read by the product of chunk c - 2
-                ok = ok && mbar_wait(bar_o + 8 * (c & 1), ((c - 2) >> 1) & 1, abort_flag);
+                ok = ok && mbar_wait(bar_o + 8 * (c & 1), ((c - 2) >> 1) & 1, abort_flag, P.wait_budget);
                 tc_fence_after();
             }
 #pragma unroll
@@ -777,7 +773,7 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             if (++ci[2] == nc[2]) { ci[2] = 0; if (++ci[1] == nc[1]) { ci[1] = 0; if (++ci[0] == nc[0]) { ci[0] = 0; ++hc; } } }
         }
         // ---- every product is in the accumulator: scale, write out this thread's channels ----
-        ok = ok && mbar_wait(bar_o + 8 * ((total - 1) & 1), ((total - 1) >> 1) & 1, abort_flag);
+        ok = ok && mbar_wait(bar_o + 8 * ((total - 1) & 1), ((total - 1) >> 1) & 1, abort_flag, P.wait_budget);
         tc_fence_after();
 #pragma unroll
         for (int part = 0; part < CH / 32; ++part) {
@@ -798,6 +794,7 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
     }
 
+    if (*abort_flag) abort_grace_sleep();       // loads of a wait that gave up may still be landing
     tc_fence_before();
     __syncthreads();
     if (warp == 8) {
@@ -812,10 +809,9 @@ int launch_gather(const Plan& plan, const CUtensorMap& mx, const Geo& g, const v
                   cudaStream_t s)
 {
     using SM = SmemG<DH>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(tc_gather_kernel<DH, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
-        attr_done = true;
+    if (ensure_dynamic_smem((const void*)tc_gather_kernel<DH, BF16>, SM::kTotal) != cudaSuccess) {
+        cudaGetLastError();
+        return -2;
     }
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= plan.p.grp_n[a];
@@ -856,7 +852,6 @@ int tc_scores(int dtype, const Geo& g, const void* x, const long long xs[3], con
         !encode_map(&my, y, bf16, plan.p, g.Hkv, g.D, ys, plan.box_kv))
         return -2;
     plan.p.status = status_ptr();
-    plan.p.trace = nullptr;
     if (!plan.p.status) return -2;
     if (plan.p.work_q == 0) return 0;
     if (g.D == 64)
@@ -890,7 +885,6 @@ int tc_apply(int dtype, const Geo& g, const void* w, const void* y, const long l
     CUtensorMap my;
     if (!encode_map(&my, y, bf16, plan.p, g.Hkv, g.D, ys, plan.box_kv)) return -2;
     plan.p.status = status_ptr();
-    plan.p.trace = nullptr;
     if (!plan.p.status) return -2;
     if (plan.p.work_q == 0) return 0;
     if (g.D == 64)
@@ -919,7 +913,6 @@ int tc_gather(int dtype, const Geo& g, const void* w, const void* x, const long 
     CUtensorMap mx;
     if (!encode_map(&mx, x, bf16, plan.p, g.Hq, g.D, xs, plan.box_kv)) return -2;
     plan.p.status = status_ptr();
-    plan.p.trace = nullptr;
     if (!plan.p.status) return -2;
     if (plan.p.work_kv == 0) return 0;
     if (g.D == 64)

@@ -70,6 +70,9 @@ class HostStep:
         key = (tuple(q.shape), tuple(k.shape), tuple(v.shape), q.dtype)
         if key == self._key:
             return
+        # The old buffers were used on the side streams: nothing queued there may still touch them
+        # when the allocator gets them back.
+        self._drain()
         dev = self.device
         rank = self.rank
         osp = tuple(-(-n // s) for n, s in zip(q.shape[1:1 + rank], self.st))
@@ -100,6 +103,23 @@ class HostStep:
         self._ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         self._key = key
 
+    def _drain(self):
+        for st in (self._s_in, self._s_cmp, self._s_out):
+            st.synchronize()
+        self._free, self._copied = [], []
+
+    def close(self):
+        """Wait for queued work and release the device and pinned buffers."""
+        self._drain()
+        self._stage = self._host = self._key = None
+        self._dev_out = self._dev_lse = self._dev_grads = self._ws = None
+
+    def __del__(self):
+        try:
+            self._drain()
+        except Exception:      # interpreter shutdown: the context may already be gone
+            pass
+
     # -- the step -----------------------------------------------------------------------
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dout: torch.Tensor):
         """-> (out or None, dq, dk, dv): pinned host tensors owned by this object (overwritten by the
@@ -111,6 +131,8 @@ class HostStep:
                 raise ValueError(f"{name} must be a host tensor.")
             if t.ndim != self.rank + 3:
                 raise ValueError(f"{name} must have {self.rank + 3} dimensions.")
+            if t.dtype != q.dtype:
+                raise ValueError("query, key, value and dout must share one dtype.")
         if k.shape != v.shape[:-1] + (k.shape[-1],) or q.shape[:-2] != k.shape[:-2]:
             raise ValueError("query, key and value must agree on batch and spatial dimensions.")
         spatial = tuple(q.shape[1:1 + self.rank])
@@ -170,6 +192,8 @@ class HostStep:
                                       _cabi.ptr(lse), _cabi.ptr(go), None, _cabi.ptr(dq), _cabi.ptr(dk), _cabi.ptr(dv),
                                       None, None, _cabi.ptr(self._ws), self._ws.numel(), stream)
             _cabi.check(rc, "natten_fused_bwd")
+        if i == len(self._params) - 1:         # once per step: status word -> pinned host word
+            _cabi.track_status(q)
 
     def wait(self):
         """Make the caller's current stream wait for everything queued so far (the copies out included)."""
@@ -178,9 +202,11 @@ class HostStep:
         cur.wait_stream(self._s_cmp)
 
     def synchronize(self):
-        """Block the host until the results of every call so far are in host memory."""
+        """Block the host until the results of every call so far are in host memory; raises if a
+        kernel reported a timed-out wait."""
         self._s_out.synchronize()
         self._s_cmp.synchronize()
+        _cabi.poll_status(self.device)
 
     # -- traffic, for reports -----------------------------------------------------------
     def bytes_per_step(self, q, k, v, dout):

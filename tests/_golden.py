@@ -43,6 +43,10 @@ def split_cases():
     return manifest()["split"]
 
 
+def module_cases():
+    return manifest().get("modules", [])
+
+
 def varlen_cases():
     return manifest()["varlen"]
 

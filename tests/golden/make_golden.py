@@ -67,6 +67,20 @@ SPLIT = [
     ("qk2d_causal_stride", 2, (8, 9), 1, 2, 8,
      dict(kernel_size=3, stride=(2, 2), is_causal=(False, True), scale=0.5)),
     ("qk3d", 3, (4, 5, 6), 1, 2, 4, dict(kernel_size=3, dilation=(1, 1, 2))),
+    # head dims that reach the vectorised 16-bit kernels and the tensor-core kernels (D_v == D here)
+    ("qk2d_d32", 2, (10, 9), 1, 2, 32, dict(kernel_size=(5, 3)), 32),
+    ("qk2d_d64_dil_scale", 2, (12, 11), 1, 2, 64, dict(kernel_size=3, dilation=(2, 1), scale=0.125), 64),
+]
+
+# Module fixtures: constructor of the reference module, input shape.  The state_dict, the input,
+# the output, the input gradient and every parameter gradient are stored.
+MODULES = [
+    ("mod2d", "NeighborhoodAttention2D", dict(embed_dim=64, num_heads=2, kernel_size=5), (2, 10, 12, 64)),
+    ("mod1d_gqa", "NeighborhoodAttention1D", dict(embed_dim=64, num_heads=4, kernel_size=5, num_kv_heads=2),
+     (2, 20, 64)),
+    ("mod3d_causal_stride", "NeighborhoodAttention3D",
+     dict(embed_dim=32, num_heads=2, kernel_size=(3, 3, 3), stride=(1, 2, 1), is_causal=(True, False, False),
+          qk_scale=0.2), (1, 4, 6, 6, 32)),
 ]
 
 VARLEN = [
@@ -84,7 +98,7 @@ def _randn(g, *shape):
 
 def main():
     arrays = {}
-    manifest = {"fused": [], "split": [], "varlen": [], "window": None}
+    manifest = {"fused": [], "split": [], "varlen": [], "modules": [], "window": None}
     fns = {1: RF.na1d, 2: RF.na2d, 3: RF.na3d}
     qk = {1: RF.na1d_qk, 2: RF.na2d_qk, 3: RF.na3d_qk}
     av = {1: RF.na1d_av, 2: RF.na2d_av, 3: RF.na3d_av}
@@ -122,11 +136,13 @@ def main():
         arrays[f"{name}/gout"] = gout.numpy()
         manifest["fused"].append(dict(name=name, rank=rank, kwargs=kwargs, n_extra=n_extra))
 
-    for seed, (name, rank, spatial, B, H, D, kwargs) in enumerate(SPLIT, start=100):
+    for seed, case in enumerate(SPLIT, start=100):
+        name, rank, spatial, B, H, D, kwargs = case[:7]
+        Dv = case[7] if len(case) > 7 else D + 4                 # D_v != D_qk is legal here
         g = torch.Generator().manual_seed(seed)
         q = _randn(g, B, *spatial, H, D).requires_grad_()
         k = _randn(g, B, *spatial, H, D).requires_grad_()
-        v = _randn(g, B, *spatial, H, D + 4).requires_grad_()   # D_v != D_qk is legal here
+        v = _randn(g, B, *spatial, H, Dv).requires_grad_()
         logits = qk[rank](q, k, **kwargs)
         glog = _randn(g, *logits.shape)
         finite = torch.isfinite(logits)
@@ -154,6 +170,24 @@ def main():
             arrays[f"{name}/{nm}"] = t.detach().numpy()
         manifest["varlen"].append(dict(name=name, rank=rank, kwargs=kwargs, sizes=sizes))
 
+    for seed, (name, cls, ctor, xshape) in enumerate(MODULES, start=300):
+        torch.manual_seed(seed)
+        m = getattr(natten_mps, cls)(**ctor).double()            # float32-initialised parameters, float64 maths
+        g = torch.Generator().manual_seed(seed)
+        x = _randn(g, *xshape).requires_grad_()
+        y = m(x)
+        gout = _randn(g, *y.shape)
+        params = dict(m.named_parameters())
+        grads = torch.autograd.grad((y * gout).sum(), [x] + list(params.values()))
+        arrays[f"{name}/x"] = x.detach().numpy()
+        arrays[f"{name}/gout"] = gout.numpy()
+        arrays[f"{name}/y"] = y.detach().numpy()
+        arrays[f"{name}/dx"] = grads[0].numpy()
+        for (pn, pt), gt in zip(params.items(), grads[1:]):
+            arrays[f"{name}/p.{pn}"] = pt.detach().numpy()
+            arrays[f"{name}/dp.{pn}"] = gt.numpy()
+        manifest["modules"].append(dict(name=name, cls=cls, ctor=ctor))
+
     # integer spec: every legal (L, K, dilation) with L <= 40, K <= 11, dilation <= 4
     rows = []
     for L in range(1, 41):
@@ -172,12 +206,12 @@ def main():
             return list(o)
         raise TypeError(type(o))
 
-    inputs = {"q", "k", "v", "ek", "ev", "gout", "glse", "glog", "attn"}
+    inputs = {"q", "k", "v", "ek", "ev", "gout", "glse", "glog", "attn", "x"}
 
     def _store(key, a):
         if a.dtype == np.int16:
             return a
-        if key.split("/")[1] in inputs:
+        if key.split("/")[1] in inputs or key.split("/")[1].startswith("p."):
             assert np.array_equal(a.astype(np.float32).astype(np.float64), a)
             return a.astype(np.float32)
         return a.astype(np.float64)

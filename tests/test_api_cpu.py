@@ -182,3 +182,14 @@ def test_host_step_needs_cuda_and_validates():
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError):
             HostStep(2, 3)
+
+
+def test_module_state_dict_names_and_shapes_match_the_reference_fixture():
+    """The fixture stores the reference modules' parameters; the modules here must accept them."""
+    for case in G.module_cases():
+        a = G.arrays(case["name"])
+        ctor = {k: (tuple(v) if isinstance(v, list) else v) for k, v in case["ctor"].items()}
+        m = getattr(nb, case["cls"])(**ctor)
+        state = {k[2:]: torch.as_tensor(v) for k, v in a.items() if k.startswith("p.")}
+        assert {k: tuple(v.shape) for k, v in state.items()} == {k: tuple(v.shape) for k, v in m.state_dict().items()}
+        m.load_state_dict(state)

@@ -1,9 +1,6 @@
-"""The five benchmark configurations at full size (config 5 at two of its eight
-samples by default) against the CPU oracle, with the contract's tolerances:
+"""The five benchmark configurations at full size against the CPU oracle, with the contract's tolerances:
 1e-5 relative in float32, 2e-2 absolute for bf16/fp16 outputs and gradients
 against a float32 reference on the same rounded inputs."""
-import os
-
 import numpy as np
 import pytest
 import torch
@@ -68,7 +65,7 @@ def test_config4_na3d_bf16_causal_depth():
 
 
 def test_config5_na1d_fp16_gqa_varlen_extra_tokens():
-    B = 8 if os.environ.get("NATTEN_TEST_FULL_C5") else 2
+    B = 8
     g = torch.Generator(device="cpu").manual_seed(0)
     L, Hq, Hkv, D, K, Ne = 16384, 16, 4, 128, 255, 16
     q = torch.randn((B, L, Hq, D), generator=g).half()
