@@ -33,6 +33,22 @@ namespace natten {
 using namespace tc;
 using namespace tcplan;
 
+// Optional clock stamps of one CTA's pipeline events (development builds only: -DNATTEN_TRACE).
+#ifdef NATTEN_TRACE
+__device__ long long g_trace_bwd[2 * 16 * 512];
+#define STAMP(id)                                                                                   \
+    do {                                                                                            \
+        if (blockIdx.x == 7 && lane == 0 && tn < 255) {                                             \
+            long long* tr_ = g_trace_bwd + (kKeySide ? 16 * 512 : 0) + warp * 512;                  \
+            tr_[2 * tn] = (id);                                                                     \
+            tr_[2 * tn + 1] = clock64();                                                            \
+            ++tn;                                                                                   \
+        }                                                                                           \
+    } while (0)
+#else
+#define STAMP(id) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kCols = 64;                   // columns per chunk
@@ -147,6 +163,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     constexpr uint32_t kTmemCols = Smem::kTmemCols, kColA2 = Smem::kColA2;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef NATTEN_TRACE
+    int tn = 0;
+#endif
     const int quad = warp & 3, piece = (warp >> 2) & 1;      // compute warps: TMEM lane quadrant, 32-column piece
     const int prior_abort = *reinterpret_cast<volatile int*>(P.status);   // loaded early, used at barrier set-up
     const unsigned nwork = kKeySide ? P.work_kv : P.work_q;
@@ -329,8 +348,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                         wnext = next_active(work + gridDim.x, Tn);
                         if (wnext < nwork) prefetch_rows(Tn);
                     }
+                    STAMP(200 + cc);
                     ok = mbar_wait(bar_sp, g & 1, abort_flag, P.wait_budget);               // S/dP consumed, P/dS stored
                     if (!ok) break;
+                    STAMP(210);
                     issue_acc(g, cc > 0);                                    // reads P/dS ...
                     if (!last) {
                         ok = mbar_wait(bar_col + 8 * ((g + 1) % kStages), ((g + 1) / kStages) & 1, abort_flag, P.wait_budget);
@@ -339,8 +360,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                     } else if (wnext < nwork) {
                         issue_rows(Tn);        // every S/dP product of this tile has finished: its rows are free
                     }
+                    STAMP(220);
                     ok = mbar_wait(bar_acc, g & 1, abort_flag, P.wait_budget);              // stage g % kStages is free again
                     if (!ok) break;
+                    STAMP(230);
                     issue_cols();
                 }
                 T = Tn;
@@ -472,6 +495,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             const unsigned slot = item & 1;
             ok = mbar_wait(bar_tab_full + 8 * slot, (item >> 1) & 1, abort_flag, P.wait_budget) && ok;
             const uint8_t* tab = smem + Smem::kTab + slot * Smem::kTabBytes;
+            STAMP(300);
             const RowEntry en = reinterpret_cast<const RowEntry*>(tab)[quad * 32 + lane];
             const TileHead T = *reinterpret_cast<const TileHead*>(tab + 128 * 32);
             mbar_arrive(bar_tab_empty + 8 * slot);
@@ -531,9 +555,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 const bool any = __any_sync(0xffffffffu, mine);
                 const bool separable = kInner > 0 && !extra;
                 const bool full = !separable && __all_sync(0xffffffffu, word == 0xffffffffu);
+                STAMP(310 + (any ? 1 : 0));
                 ok = ok && mbar_wait(bar_s, g & 1, abort_flag, P.wait_budget);      // also: the previous chunk's P/dS were consumed
                 if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (g % kStages), (g / kStages) & 1, abort_flag, P.wait_budget);
                 tc_fence_after();
+                STAMP(320);
                 if (any) {
                     const float* stp = stats + (g % kStages) * 128 + 32 * piece;
                     const float4* st4 = reinterpret_cast<const float4*>(stp);
@@ -608,6 +634,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(bar_sp);
+                STAMP(330);
                 // next chunk (innermost axis fastest; wraps to the next query head on the key side)
                 if (++ci[2] == T.nc[2]) {
                     ci[2] = 0;
@@ -619,8 +646,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             }
 
             // ---- accumulators -> global: this warp owns 32 of the 64 channels ----
+            STAMP(340);
             ok = ok && mbar_wait(bar_acc, (g - 1) & 1, abort_flag, P.wait_budget);
             tc_fence_after();
+            STAMP(350);
             // The TMEM loads are warp-collective: every lane takes part, only the stores are per row.
             const bool live = valid_row && ok;
 #pragma unroll
@@ -645,6 +674,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             }
             // the next tile's first accumulating MMA is issued only after every thread has passed here
             tc_fence_before();
+            STAMP(360);
         }
     }
 
@@ -787,5 +817,17 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
 }
 
 size_t tc_bwd_workspace_bytes(int, const Geo&) { return 0; }
+
+#ifdef NATTEN_TRACE
+extern "C" int natten_trace_read_bwd(long long* host, int clear)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(host, g_trace_bwd, sizeof(g_trace_bwd));
+    if (e == cudaSuccess && clear) {
+        static long long zeros[2 * 16 * 512] = {0};
+        e = cudaMemcpyToSymbol(g_trace_bwd, zeros, sizeof(g_trace_bwd));
+    }
+    return (int)e;
+}
+#endif
 
 } // namespace natten

@@ -35,6 +35,11 @@ struct TcParams {
     const int* extents;
     long long ltot;
     int* status;
+    // Interleaved chunks (forward only): along an axis with il > 1 chunk ci holds the box columns
+    // ci, ci + il, ci + 2*il, ... instead of a contiguous block, so that every chunk carries a share of
+    // every row's window.  il == 1: blocked (chunk ci = columns [ci*cb, (ci+1)*cb)).
+    int il[3];
+    unsigned il_mul[3], group_mul;       // fast_div multipliers of il[] and of the GQA group size
     long long wait_budget; // cycles a barrier wait may take before the CTA gives up
     int inject;            // test hook: 1 = the forward's first query barrier expects bytes that never arrive
     // Output stride (forward only).  Inside dilation group r of an axis the queries sit at the
@@ -84,6 +89,7 @@ __device__ __forceinline__ bool cta_geometry(const TcParams& P, unsigned bx, int
 // Chunks needed to cover `extent` columns along axis a (chunk extents are powers of two).
 __device__ __forceinline__ int chunks_along(const TcParams& P, int a, int extent)
 {
+    if (P.il[a] > 1) return extent < P.il[a] ? extent : P.il[a];      // interleaved: chunk ci starts at column ci
     const int lg = a == 0 ? P.cb0_log : (a == 1 ? P.cb1_log : P.cb2_log);
     return (extent + P.cb[a] - 1) >> lg;
 }
@@ -141,15 +147,16 @@ __device__ __forceinline__ void zero_rows_past_extent(const TcParams& P, const i
                                                       int cols, int halves, int half_bytes,
                                                       uint8_t* tile1, uint8_t* tile2)
 {
+    // box0[] is the coordinate of column 0; successive columns are il apart (1 when blocked)
     bool crosses = false;
 #pragma unroll
-    for (int a = 0; a < 3; ++a) crosses = crosses || (box0[a] + P.cb[a] > Lp[a]);
+    for (int a = 0; a < 3; ++a) crosses = crosses || (box0[a] + (P.cb[a] - 1) * P.il[a] + 1 > Lp[a]);
     if (!crosses) return;
     for (int j = 0; j < cols; ++j) {
         const int j2 = j & (P.cb[2] - 1);
         const int j1 = (j >> P.cb2_log) & (P.cb[1] - 1);
         const int j0 = j >> (P.cb2_log + P.cb1_log);
-        if (box0[0] + j0 < Lp[0] && box0[1] + j1 < Lp[1] && box0[2] + j2 < Lp[2]) continue;
+        if (box0[0] + j0 * P.il[0] < Lp[0] && box0[1] + j1 * P.il[1] < Lp[1] && box0[2] + j2 * P.il[2] < Lp[2]) continue;
         for (int hf = 0; hf < halves; ++hf) {
             uint4* r1 = reinterpret_cast<uint4*>(tile1 + hf * half_bytes + j * 128);
             uint4* r2 = reinterpret_cast<uint4*>(tile2 + hf * half_bytes + j * 128);
@@ -158,6 +165,49 @@ __device__ __forceinline__ void zero_rows_past_extent(const TcParams& P, const i
         }
     }
     fence_async_smem();          // the tensor cores read shared memory through the async proxy
+}
+
+// Columns j of chunk ci (along axis a) that fall inside the box range [f, e): j in [jl, jh), clamped to the chunk.
+__device__ __forceinline__ void chunk_range(const TcParams& P, int a, int ci, int f, int e, int& jl, int& jh)
+{
+    if (P.il[a] == 1) {
+        jl = f - ci * P.cb[a];
+        jh = e - ci * P.cb[a];
+    } else {                                     // column j sits at box coordinate ci + il * j
+        const int x = f - ci + P.il[a] - 1, y = e - ci + P.il[a] - 1;
+        jl = x > 0 ? (int)fast_div((unsigned)x, P.il_mul[a]) : 0;
+        jh = y > 0 ? (int)fast_div((unsigned)y, P.il_mul[a]) : 0;
+    }
+    jl = jl > 0 ? jl : 0;
+    jh = jh < P.cb[a] ? jh : P.cb[a];
+}
+
+// Box coordinate (relative to the box origin) of column j of chunk ci along axis a.
+__device__ __forceinline__ int chunk_coord(const TcParams& P, int a, int ci, int j)
+{
+    return P.il[a] == 1 ? ci * P.cb[a] + j : ci + P.il[a] * j;
+}
+
+// Validity bits of one 32-column piece from per-axis column ranges [jl, jh) (see chunk_range).
+__device__ __forceinline__ uint32_t piece_word_ranges(const TcParams& P, int pc, const int (&jl)[3], const int (&jh)[3])
+{
+    const int seg = P.cb[2] < 32 ? P.cb[2] : 32;
+    const int nseg = 32 / seg;
+    uint32_t w = 0;
+    for (int sg = 0; sg < nseg; ++sg) {
+        const int jj = 32 * pc + sg * seg;
+        const int j2 = jj & (P.cb[2] - 1);
+        const int j1 = (jj >> P.cb2_log) & (P.cb[1] - 1);
+        const int j0 = jj >> (P.cb2_log + P.cb1_log);
+        int lo2 = jl[2] - j2, hi2 = jh[2] - j2;
+        lo2 = lo2 > 0 ? lo2 : 0;
+        hi2 = hi2 < seg ? hi2 : seg;
+        if (j0 >= jl[0] && j0 < jh[0] && j1 >= jl[1] && j1 < jh[1] && hi2 > lo2) {
+            const uint32_t run = (hi2 - lo2 >= 32) ? 0xffffffffu : ((1u << (hi2 - lo2)) - 1u);
+            w |= (run << lo2) << (sg * seg);
+        }
+    }
+    return w;
 }
 
 // Packed 16-bit pair arithmetic (element 0 in the low half).
@@ -224,7 +274,7 @@ struct Plan {
 };
 
 // Pick the row-tile shape (128 rows) whose column box needs the fewest chunks of `chunk` columns.
-inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk, bool with_stride = false)
+inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk, bool with_stride = false, bool interleave = false)
 {
     TcParams& p = plan.p;
     const int pad = 3 - g.rank;
@@ -304,6 +354,22 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk, bool with_st
         for (int a = 0; a < 3; ++a) { blocks *= p.grp_n[a]; dmax = p.dil[a] > dmax ? p.dil[a] : dmax; dmax = p.ntile[a] > dmax ? p.ntile[a] : dmax; }
         if (blocks * dmax >= (1ll << 32) || (long long)(p.L[0] + p.L[1] + p.L[2] + dmax) * dmax >= (1ll << 32)) return false;
     }
+    for (int a = 0; a < 3; ++a) { p.il[a] = 1; p.il_mul[a] = 0u; }
+    if (interleave) {
+        // the first (slowest) axis that needs several chunks is the one along which the warps of a
+        // tile differ; tensor maps take element strides up to 8
+        for (int a = 0; a < 3; ++a) {
+            if (p.nchunk[a] <= 1) continue;
+            const int il = p.nchunk[a];
+            if (p.dil[a] * il <= 8 && p.cb[a] * p.dil[a] * il <= 256) {
+                p.il[a] = il;
+                p.il_mul[a] = (unsigned)((0x100000000ull + il - 1) / il);
+                plan.box_kv[a] = p.cb[a] * p.dil[a] * il;
+            }
+            break;
+        }
+    }
+    p.group_mul = g.group >= 2 ? (unsigned)((0x100000000ull + g.group - 1) / g.group) : 0u;
     p.rank = g.rank; p.B = g.B; p.Hq = g.Hq; p.Hkv = g.Hkv; p.group = g.group;
     p.n_extra = g.n_extra;
     p.ngroups = 1;
@@ -323,7 +389,7 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk, bool with_st
 
 // 5-D map over [B, X0, X1, X2, heads*D] (innermost first in the arrays below).
 inline bool encode_map(CUtensorMap* map, const void* base, bool bf16, const TcParams& p, int heads, int dh,
-                const long long strides[3], const int box[3], bool query_lattice = false)
+                const long long strides[3], const int box[3], bool query_lattice = false, bool interleaved = false)
 {
     EncodeFn enc = get_encode();
     if (!enc) return false;
@@ -334,6 +400,8 @@ inline bool encode_map(CUtensorMap* map, const void* base, bool bf16, const TcPa
     cuuint32_t es[5] = {1, (cuuint32_t)p.dil[2], (cuuint32_t)p.dil[1], (cuuint32_t)p.dil[0], 1};
     if (query_lattice)                                           // strided output: only every qstep-th sub-grid position is a query
         for (int a = 0; a < 3; ++a) es[3 - a] *= (cuuint32_t)p.qstep[a];
+    if (interleaved)                                             // chunk columns are il sub-grid positions apart
+        for (int a = 0; a < 3; ++a) es[3 - a] *= (cuuint32_t)p.il[a];
     for (int i = 1; i < 4; ++i)
         if (es[i] > 8) return false;
     if (dims[4] == 0) return false;
