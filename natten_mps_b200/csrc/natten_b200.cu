@@ -96,9 +96,8 @@ int natten_fused_fwd(const natten_params_t* p, const void* q, const void* k, con
     set_vec_ok(g, p->dtype, true, true, true, {q, k, v, extra_k, extra_v});
     cudaStream_t s = (cudaStream_t)stream;
     if (!(p->flags & NATTEN_FLAG_FORCE_SIMT)) {
-        // Per-sample extents leave many tiles without work: the persistent kernel (head dim 64) skips them
-        // cheaply and balances the rest; dense problems are served by the one-tile-per-CTA kernel.
-        rc = g.extents ? tc_fused_fwd_pipe(p->dtype, g, q, k, v, extra_k, extra_v, out, lse, s) : NATTEN_E_UNSUPPORTED;
+        // head dim 64: small persistent CTAs (four per SM); head dim 128: one tile per CTA
+        rc = tc_fused_fwd_small(p->dtype, g, q, k, v, extra_k, extra_v, out, lse, s);
         if (rc == NATTEN_E_UNSUPPORTED) rc = tc_fused_fwd(p->dtype, g, q, k, v, extra_k, extra_v, out, lse, s);
         if (rc != NATTEN_E_UNSUPPORTED) { t_last_path = NATTEN_PATH_TCGEN05; return rc; }
     }

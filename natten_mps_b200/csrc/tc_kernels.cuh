@@ -8,9 +8,9 @@ namespace natten {
 
 int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const void* v,
                  const void* ek, const void* ev, void* out, void* lse, cudaStream_t s);
-// The same for head dim 64: persistent kernel with two query tiles in flight per SM.
-int tc_fused_fwd_pipe(int dtype, const Geo& g, const void* q, const void* k, const void* v,
-                      const void* ek, const void* ev, void* out, void* lse, cudaStream_t s);
+// The same for head dim 64 from small persistent CTAs (four per SM, 64-key chunks, interleaved chunk rows).
+int tc_fused_fwd_small(int dtype, const Geo& g, const void* q, const void* k, const void* v,
+                       const void* ek, const void* ev, void* out, void* lse, cudaStream_t s);
 int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const void* v,
                  const void* ek, const void* ev, const void* out, const void* lse, const void* dout,
                  const void* dlse, void* dq, void* dk, void* dv, void* dek, void* dev,
