@@ -276,18 +276,18 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 mbar_expect_tx(bar_row, 2 * kTile);
 #pragma unroll
                 for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                    tma_load_5d(sbase + Smem::kR1 + hf * kRowHalf, &tmR1, bar_row, hx + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
+                    tma_load_heads(sbase + Smem::kR1 + hf * kRowHalf, &tmR1, bar_row, P, DH, hx + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
                                 X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
-                    tma_load_5d(sbase + Smem::kR2 + hf * kRowHalf, &tmR2, bar_row, hx + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
+                    tma_load_heads(sbase + Smem::kR2 + hf * kRowHalf, &tmR2, bar_row, P, DH, hx + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
                                 X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
                 }
             };
             auto prefetch_rows = [&](const BwdTile& X) {
 #pragma unroll
                 for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                    tma_prefetch_l2_5d(&tmR1, X.hy * DH + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
+                    tma_prefetch_heads(&tmR1, P, DH, X.hy * DH + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
                                        X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
-                    tma_prefetch_l2_5d(&tmR2, X.hy * DH + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
+                    tma_prefetch_heads(&tmR2, P, DH, X.hy * DH + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
                                        X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
                 }
             };
@@ -309,16 +309,16 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                     const int hx = (kKeySide ? Tl.hy * P.group + ld_head : head_kv) * DH;
 #pragma unroll
                     for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                        tma_load_5d(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmC1, bar, hx + 64 * hf, X[2], X[1], X[0], Tl.b);
-                        tma_load_5d(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmC2, bar, hx + 64 * hf, X[2], X[1], X[0], Tl.b);
+                        tma_load_heads(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmC1, bar, P, DH, hx + 64 * hf, X[2], X[1], X[0], Tl.b);
+                        tma_load_heads(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmC2, bar, P, DH, hx + 64 * hf, X[2], X[1], X[0], Tl.b);
                     }
                     if (++ld[2] == Tl.nc[2]) { ld[2] = 0; if (++ld[1] == Tl.nc[1]) { ld[1] = 0; if (++ld[0] == Tl.nc[0]) { ld[0] = 0; ++ld_head; } } }
                 } else {                                 // additional tokens (rows past n_extra are zero-filled)
                     const int e0 = (ld_in_tile - Tl.nbox) * kCols;
 #pragma unroll
                     for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                        tma_load_5d(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmE1, bar, head_kv * DH + 64 * hf, e0, 0, 0, Tl.b);
-                        tma_load_5d(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmE2, bar, head_kv * DH + 64 * hf, e0, 0, 0, Tl.b);
+                        tma_load_heads(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmE1, bar, P, DH, head_kv * DH + 64 * hf, e0, 0, 0, Tl.b);
+                        tma_load_heads(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmE2, bar, P, DH, head_kv * DH + 64 * hf, e0, 0, 0, Tl.b);
                     }
                 }
                 ++loaded;
@@ -507,9 +507,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 if (in_tensor) {
 #pragma unroll
                     for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
-                        uint4* o = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * DH + piece * CH);
+                        uint4* o = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * P.dreal + piece * CH);
 #pragma unroll
-                        for (int i = 0; i < CH / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
+                        for (int i = 0; i < CH / 8; ++i)
+                            if (piece * CH + 8 * i < P.dreal) o[i] = make_uint4(0, 0, 0, 0);
                     }
                 }
                 continue;
@@ -660,9 +661,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                     tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + CH * piece + 32 * part, a);
                     tmem_ld_wait();
                     if (in_tensor) {
-                        uint4* d4 = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * DH + piece * CH + 32 * part);
+                        uint4* d4 = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * P.dreal + piece * CH + 32 * part);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
+                            if (piece * CH + 32 * part + 8 * i >= P.dreal) break;     // padded channels are not part of the output
                             uint32_t w[4];
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
@@ -688,27 +690,28 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     }
 }
 
-// delta[row] = sum_d out[row,d]*dout[row,d] - dlse[row]      (DH/8 threads per row, 16 bytes each;
-// every thread takes kDeltaRows rows a grid-width apart, so that eight 16-byte loads are in flight)
+// delta[row] = sum_d out[row,d]*dout[row,d] - dlse[row]      (kPer threads per row, 16 bytes each, kPer the
+// power of two >= D/8; every thread takes kDeltaRows rows a grid-width apart, so that eight 16-byte loads
+// are in flight)
 constexpr int kDeltaRows = 4;
-template <int DH, bool BF16>
+template <int kPer, bool BF16>
 __global__ void __launch_bounds__(256)
 tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ dout,
-                const float* __restrict__ dlse, float* __restrict__ delta, long long rows, long long row_step)
+                const float* __restrict__ dlse, float* __restrict__ delta, long long rows, long long row_step, int D)
 {
-    constexpr int kPer = DH / 8;
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long row0 = t / kPer;
     const int part = (int)(t % kPer);
+    const bool mine = 8 * part < D;
     uint4 a[kDeltaRows], g[kDeltaRows];
 #pragma unroll
     for (int r = 0; r < kDeltaRows; ++r) {
         const long long row = row0 + r * row_step;
         a[r] = make_uint4(0, 0, 0, 0);
         g[r] = make_uint4(0, 0, 0, 0);
-        if (row < rows) {
-            a[r] = reinterpret_cast<const uint4*>(out + row * DH)[part];
-            g[r] = reinterpret_cast<const uint4*>(dout + row * DH)[part];
+        if (row < rows && mine) {
+            a[r] = reinterpret_cast<const uint4*>(out + row * D)[part];
+            g[r] = reinterpret_cast<const uint4*>(dout + row * D)[part];
         }
     }
 #pragma unroll
@@ -743,10 +746,16 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
     const long long qrows = (long long)g.B * g.ltot * g.Hq;
     {
         // rows handled per pass of the grid: a whole number of blocks, a quarter of the rows each
-        const long long rows_per_block = 256 / (DH / 8);
-        const long long blocks = ((qrows + kDeltaRows - 1) / kDeltaRows + rows_per_block - 1) / rows_per_block;
-        tc_delta_kernel<DH, BF16><<<(unsigned)blocks, 256, 0, s>>>(
-            (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, qrows, blocks * rows_per_block);
+        auto run_delta = [&](auto per) {
+            constexpr int kPer = decltype(per)::value;
+            const long long rows_per_block = 256 / kPer;
+            const long long blocks = ((qrows + kDeltaRows - 1) / kDeltaRows + rows_per_block - 1) / rows_per_block;
+            tc_delta_kernel<kPer, BF16><<<(unsigned)blocks, 256, 0, s>>>(
+                (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, qrows, blocks * rows_per_block, g.D);
+        };
+        if (g.D <= 32) run_delta(std::integral_constant<int, 4>{});
+        else if (g.D <= 64) run_delta(std::integral_constant<int, 8>{});
+        else run_delta(std::integral_constant<int, 16>{});
     }
     tc_count_launch();
 
@@ -754,18 +763,18 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
     CUtensorMap q_tile, do_tile, k_chunk, v_chunk, k_tile, v_tile, q_chunk, do_chunk, ek_chunk, ev_chunk;
     const bool bf = BF16;
     using Smem = SmemB<DH>;
-    if (!encode_map(&q_tile, q, bf, p, g.Hq, DH, g.qs, plan.box_q) ||
-        !encode_map(&do_tile, dout, bf, p, g.Hq, DH, dos, plan.box_q) ||
-        !encode_map(&k_chunk, k, bf, p, g.Hkv, DH, g.ks, plan.box_kv) ||
-        !encode_map(&v_chunk, v, bf, p, g.Hkv, DH, g.vs, plan.box_kv) ||
-        !encode_map(&k_tile, k, bf, p, g.Hkv, DH, g.ks, plan.box_q) ||
-        !encode_map(&v_tile, v, bf, p, g.Hkv, DH, g.vs, plan.box_q) ||
-        !encode_map(&q_chunk, q, bf, p, g.Hq, DH, g.qs, plan.box_kv) ||
-        !encode_map(&do_chunk, dout, bf, p, g.Hq, DH, dos, plan.box_kv))
+    if (!encode_map(&q_tile, q, bf, p, g.Hq, g.D, g.qs, plan.box_q) ||
+        !encode_map(&do_tile, dout, bf, p, g.Hq, g.D, dos, plan.box_q) ||
+        !encode_map(&k_chunk, k, bf, p, g.Hkv, g.D, g.ks, plan.box_kv) ||
+        !encode_map(&v_chunk, v, bf, p, g.Hkv, g.D, g.vs, plan.box_kv) ||
+        !encode_map(&k_tile, k, bf, p, g.Hkv, g.D, g.ks, plan.box_q) ||
+        !encode_map(&v_tile, v, bf, p, g.Hkv, g.D, g.vs, plan.box_q) ||
+        !encode_map(&q_chunk, q, bf, p, g.Hq, g.D, g.qs, plan.box_kv) ||
+        !encode_map(&do_chunk, dout, bf, p, g.Hq, g.D, dos, plan.box_kv))
         return -2;
     ek_chunk = k_chunk; ev_chunk = v_chunk;      // placeholders when there are no additional tokens
-    if (g.n_extra > 0 && (!encode_extra_map(&ek_chunk, ek, bf, g.B, g.n_extra, g.Hkv, DH, kCols) ||
-                          !encode_extra_map(&ev_chunk, ev, bf, g.B, g.n_extra, g.Hkv, DH, kCols)))
+    if (g.n_extra > 0 && (!encode_extra_map(&ek_chunk, ek, bf, g.B, g.n_extra, g.Hkv, g.D, kCols, p.split_heads) ||
+                          !encode_extra_map(&ev_chunk, ev, bf, g.B, g.n_extra, g.Hkv, g.D, kCols, p.split_heads)))
         return -2;
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= p.dil[a];
@@ -809,7 +818,7 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     if (g.B == 0) return 0;
     if (g.Hq > 65535 || g.B > 65535) return -2;
     float* delta = reinterpret_cast<float*>(workspace);
-    if (g.D == 64)
+    if (g.D <= 64)
         return dtype == 2 ? launch_bwd<64, true>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s)
                           : launch_bwd<64, false>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s);
     return dtype == 2 ? launch_bwd<128, true>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s)

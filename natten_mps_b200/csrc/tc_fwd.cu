@@ -125,9 +125,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
             if (inside) {
                 const long long orow = ((long long)b * P.otot + oflat) * P.Hq + h;
-                uint4* o4 = reinterpret_cast<uint4*>(out + orow * DH + team * CH);
+                uint4* o4 = reinterpret_cast<uint4*>(out + orow * P.dreal + team * CH);
 #pragma unroll
-                for (int i = 0; i < CH / 8; ++i) o4[i] = make_uint4(0, 0, 0, 0);
+                for (int i = 0; i < CH / 8; ++i)
+                    if (team * CH + 8 * i < P.dreal) o4[i] = make_uint4(0, 0, 0, 0);
                 if (team == 0) lse[orow] = 0.f;
             }
         }
@@ -160,16 +161,16 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             for (int a = 0; a < 3; ++a) X[a] = rg[a] + P.dil[a] * (lo[a] + ld[a] * P.cb[a]);
 #pragma unroll
             for (int hf = 0; hf < SM::kHalves; ++hf) {
-                tma_load_5d(sbase + SM::kK + s * SM::kTile + hf * SM::kHalf, &tmK, bar, hk * DH + 64 * hf, X[2], X[1], X[0], b);
-                tma_load_5d(sbase + SM::kV + s * SM::kTile + hf * SM::kHalf, &tmV, bar, hk * DH + 64 * hf, X[2], X[1], X[0], b);
+                tma_load_heads(sbase + SM::kK + s * SM::kTile + hf * SM::kHalf, &tmK, bar, P, DH, hk * DH + 64 * hf, X[2], X[1], X[0], b);
+                tma_load_heads(sbase + SM::kV + s * SM::kTile + hf * SM::kHalf, &tmV, bar, P, DH, hk * DH + 64 * hf, X[2], X[1], X[0], b);
             }
             if (++ld[2] == nc[2]) { ld[2] = 0; if (++ld[1] == nc[1]) { ld[1] = 0; ++ld[0]; } }
         } else {                                 // additional tokens (rows past n_extra are zero-filled)
             const int e0 = (loaded - nnb) * kChunk;
 #pragma unroll
             for (int hf = 0; hf < SM::kHalves; ++hf) {
-                tma_load_5d(sbase + SM::kK + s * SM::kTile + hf * SM::kHalf, &tmEK, bar, hk * DH + 64 * hf, e0, 0, 0, b);
-                tma_load_5d(sbase + SM::kV + s * SM::kTile + hf * SM::kHalf, &tmEV, bar, hk * DH + 64 * hf, e0, 0, 0, b);
+                tma_load_heads(sbase + SM::kK + s * SM::kTile + hf * SM::kHalf, &tmEK, bar, P, DH, hk * DH + 64 * hf, e0, 0, 0, b);
+                tma_load_heads(sbase + SM::kV + s * SM::kTile + hf * SM::kHalf, &tmEV, bar, P, DH, hk * DH + 64 * hf, e0, 0, 0, b);
             }
         }
         ++loaded;
@@ -190,7 +191,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 mbar_expect_tx(bar_q, SM::kTile + (P.inject == 1 ? 16u : 0u));
 #pragma unroll
                 for (int hf = 0; hf < SM::kHalves; ++hf)
-                    tma_load_5d(sbase + SM::kQ + hf * SM::kHalf, &tmQ, bar_q, h * DH + 64 * hf,
+                    tma_load_heads(sbase + SM::kQ + hf * SM::kHalf, &tmQ, bar_q, P, DH, h * DH + 64 * hf,
                                 rg[2] + P.dil[2] * (x0[2] + sx[2] * origin[2]), rg[1] + P.dil[1] * (x0[1] + sx[1] * origin[1]),
                                 rg[0] + P.dil[0] * (x0[0] + sx[0] * origin[0]), b);
                 for (int c = 0; c < nch && c < kStages; ++c) issue_kv();
@@ -494,9 +495,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tmem_ld_wait();
                 const float inv = (live && l > 0.f) ? 1.f / l : 0.f;
                 if (in_tensor) {
-                    uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH + team * CH + 32 * part);
+                    uint4* o4 = reinterpret_cast<uint4*>(out + out_row * P.dreal + team * CH + 32 * part);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
+                        if (team * CH + 32 * part + 8 * i >= P.dreal) break;      // padded channels are not part of the output
                         uint32_t w[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
@@ -537,8 +539,8 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
         !encode_map(&mv, v, bf16, plan.p, g.Hkv, g.Dv, g.vs, plan.box_kv))
         return -2;
     mek = mk; mev = mv;                      // placeholders when there are no additional tokens
-    if (g.n_extra > 0 && (!encode_extra_map(&mek, ek, bf16, g.B, g.n_extra, g.Hkv, g.D, kChunk) ||
-                          !encode_extra_map(&mev, ev, bf16, g.B, g.n_extra, g.Hkv, g.Dv, kChunk)))
+    if (g.n_extra > 0 && (!encode_extra_map(&mek, ek, bf16, g.B, g.n_extra, g.Hkv, g.D, kChunk, plan.p.split_heads) ||
+                          !encode_extra_map(&mev, ev, bf16, g.B, g.n_extra, g.Hkv, g.Dv, kChunk, plan.p.split_heads)))
         return -2;
     plan.p.status = status_ptr();
     if (!plan.p.status) return -2;
@@ -565,7 +567,7 @@ int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const vo
         if (bf16) by_inner(dh, std::true_type{});
         else by_inner(dh, std::false_type{});
     };
-    if (g.D == 64) by_type(std::integral_constant<int, 64>{});
+    if (g.D <= 64) by_type(std::integral_constant<int, 64>{});
     else by_type(std::integral_constant<int, 128>{});
     err = cudaGetLastError();
     tc_count_launch();

@@ -143,9 +143,10 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         bool valid_q, in_tensor;
                         const long long out_row = row_geometry(P, Tn, r, f, e, valid_q, in_tensor);
                         if (in_tensor) {
-                            uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH);
+                            uint4* o4 = reinterpret_cast<uint4*>(out + out_row * P.dreal);
 #pragma unroll
-                            for (int i = 0; i < DH / 8; ++i) o4[i] = make_uint4(0, 0, 0, 0);
+                            for (int i = 0; i < DH / 8; ++i)
+                                if (8 * i < P.dreal) o4[i] = make_uint4(0, 0, 0, 0);
                             lse[out_row] = 0.f;
                         }
                     }
@@ -173,7 +174,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     if (!ok) return false;
                     if (lane == 0) {
                         mbar_expect_tx(bar_q, kQBytes + ((P.inject == 1 && tl == 0) ? 16u : 0u));
-                        tma_load_5d(sbase + kOffQ, &tmQ, bar_q, H->h * DH,
+                        tma_load_heads(sbase + kOffQ, &tmQ, bar_q, P, DH, H->h * DH,
                                     H->rg[2] + P.dil[2] * (H->x0[2] + H->sx[2] * H->origin[2]),
                                     H->rg[1] + P.dil[1] * (H->x0[1] + H->sx[1] * H->origin[1]),
                                     H->rg[0] + P.dil[0] * (H->x0[0] + H->sx[0] * H->origin[0]), H->b);
@@ -193,12 +194,12 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         const int X0 = H->rg[0] + P.dil[0] * (H->lo[0] + chunk_coord(P, 0, ldc[0], 0));
                         const int X1 = H->rg[1] + P.dil[1] * (H->lo[1] + chunk_coord(P, 1, ldc[1], 0));
                         const int X2 = H->rg[2] + P.dil[2] * (H->lo[2] + chunk_coord(P, 2, ldc[2], 0));
-                        tma_load_5d(sbase + kOffK + s * kKVBytes, &tmK, bar, H->hk * DH, X2, X1, X0, H->b);
-                        tma_load_5d(sbase + kOffV + s * kKVBytes, &tmV, bar, H->hk * DH, X2, X1, X0, H->b);
+                        tma_load_heads(sbase + kOffK + s * kKVBytes, &tmK, bar, P, DH, H->hk * DH, X2, X1, X0, H->b);
+                        tma_load_heads(sbase + kOffV + s * kKVBytes, &tmV, bar, P, DH, H->hk * DH, X2, X1, X0, H->b);
                     } else {                     // additional tokens (rows past n_extra are zero-filled)
                         const int e0 = (cl - H->nnb) * kKeys;
-                        tma_load_5d(sbase + kOffK + s * kKVBytes, &tmEK, bar, H->hk * DH, e0, 0, 0, H->b);
-                        tma_load_5d(sbase + kOffV + s * kKVBytes, &tmEV, bar, H->hk * DH, e0, 0, 0, H->b);
+                        tma_load_heads(sbase + kOffK + s * kKVBytes, &tmEK, bar, P, DH, H->hk * DH, e0, 0, 0, H->b);
+                        tma_load_heads(sbase + kOffV + s * kKVBytes, &tmEV, bar, P, DH, H->hk * DH, e0, 0, 0, H->b);
                     }
                 }
                 if (cl < H->nnb) { if (++ldc[2] == H->nc[2]) { ldc[2] = 0; if (++ldc[1] == H->nc[1]) { ldc[1] = 0; ++ldc[0]; } } }
@@ -509,15 +510,17 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         {
             const bool live = valid_q && ok;
             const float inv = (live && l > 0.f) ? 1.f / l : 0.f;
-            uint4* o4 = reinterpret_cast<uint4*>(out + out_row * DH);
+            uint4* o4 = reinterpret_cast<uint4*>(out + out_row * P.dreal);
 #pragma unroll
             for (int part = 0; part < DH / 32; ++part) {
+                if (32 * part >= P.dreal) break;             // padded channels are not part of the output
                 uint32_t o[32];
                 tmem_ld32(trow + kColO + 32 * part, o);
                 tmem_ld_wait();
                 if (in_tensor) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
+                        if (32 * part + 8 * i >= P.dreal) break;
                         uint32_t wv[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
@@ -551,7 +554,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 int tc_fused_fwd_small(int dtype, const Geo& g, const void* q, const void* k, const void* v, const void* ek,
                        const void* ev, void* out, void* lse, cudaStream_t s)
 {
-    if (g.D != 64) return -2;
+    if (g.D > 64) return -2;
     if (!tc_eligible(dtype, g, q, k, v, /*allow_stride=*/true)) return -2;
     if (g.n_extra > 0 && ((reinterpret_cast<uintptr_t>(ek) | reinterpret_cast<uintptr_t>(ev)) & 15u)) return -2;
     Plan plan;
@@ -563,8 +566,8 @@ int tc_fused_fwd_small(int dtype, const Geo& g, const void* q, const void* k, co
         !encode_map(&mv, v, bf16, plan.p, g.Hkv, g.Dv, g.vs, plan.box_kv, false, /*interleaved=*/true))
         return -2;
     mek = mk; mev = mv;                      // placeholders when there are no additional tokens
-    if (g.n_extra > 0 && (!encode_extra_map(&mek, ek, bf16, g.B, g.n_extra, g.Hkv, g.D, kKeys) ||
-                          !encode_extra_map(&mev, ev, bf16, g.B, g.n_extra, g.Hkv, g.Dv, kKeys)))
+    if (g.n_extra > 0 && (!encode_extra_map(&mek, ek, bf16, g.B, g.n_extra, g.Hkv, g.D, kKeys, plan.p.split_heads) ||
+                          !encode_extra_map(&mev, ev, bf16, g.B, g.n_extra, g.Hkv, g.Dv, kKeys, plan.p.split_heads)))
         return -2;
     plan.p.status = status_ptr();
     if (!plan.p.status) return -2;

@@ -40,6 +40,10 @@ struct TcParams {
     // every row's window.  il == 1: blocked (chunk ci = columns [ci*cb, (ci+1)*cb)).
     int il[3];
     unsigned il_mul[3], group_mul;       // fast_div multipliers of il[] and of the GQA group size
+    // Head dims other than 64 / 128 run on the next larger kernel with zero-padded channels: the tensor
+    // maps then carry the head as an axis of its own ([D, H, X2, X1, B]; ranks 1 and 2) and a 64-channel
+    // box reads zeros past the real head dim `dreal`.  Outputs are written `dreal` channels wide.
+    int dreal, split_heads;
     long long wait_budget; // cycles a barrier wait may take before the CTA gives up
     int inject;            // test hook: 1 = the forward's first query barrier expects bytes that never arrive
     // Output stride (forward only).  Inside dilation group r of an axis the queries sit at the
@@ -84,6 +88,21 @@ __device__ __forceinline__ bool cta_geometry(const TcParams& P, unsigned bx, int
         if (origin[a] >= Lp[a]) active = false;
     }
     return active;
+}
+
+// Tile load whose first coordinate is head * dh + channel block: with a head axis of its own in the map
+// (split_heads) the two are separated again.  dh is the kernel's (padded) head dim, a power of two.
+__device__ __forceinline__ void tma_load_heads(uint32_t dst, const CUtensorMap* map, uint32_t bar, const TcParams& P,
+                                               int dh, int c0, int c1, int c2, int c3, int c4)
+{
+    if (P.split_heads) tma_load_5d(dst, map, bar, c0 & (dh - 1), c0 / dh, c1, c2, c4);
+    else tma_load_5d(dst, map, bar, c0, c1, c2, c3, c4);
+}
+__device__ __forceinline__ void tma_prefetch_heads(const CUtensorMap* map, const TcParams& P, int dh, int c0, int c1,
+                                                   int c2, int c3, int c4)
+{
+    if (P.split_heads) tma_prefetch_l2_5d(map, c0 & (dh - 1), c0 / dh, c1, c2, c4);
+    else tma_prefetch_l2_5d(map, c0, c1, c2, c3, c4);
 }
 
 // Chunks needed to cover `extent` columns along axis a (chunk extents are powers of two).
@@ -369,6 +388,8 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk, bool with_st
             break;
         }
     }
+    p.dreal = g.D;
+    p.split_heads = (g.D != 64 && g.D != 128) ? 1 : 0;
     p.group_mul = g.group >= 2 ? (unsigned)((0x100000000ull + g.group - 1) / g.group) : 0u;
     p.rank = g.rank; p.B = g.B; p.Hq = g.Hq; p.Hkv = g.Hkv; p.group = g.group;
     p.n_extra = g.n_extra;
@@ -402,6 +423,14 @@ inline bool encode_map(CUtensorMap* map, const void* base, bool bf16, const TcPa
         for (int a = 0; a < 3; ++a) es[3 - a] *= (cuuint32_t)p.qstep[a];
     if (interleaved)                                             // chunk columns are il sub-grid positions apart
         for (int a = 0; a < 3; ++a) es[3 - a] *= (cuuint32_t)p.il[a];
+    if (p.split_heads) {                                         // [D, H, X2, X1, B]; the leading spatial axis has extent 1
+        if (p.L[0] != 1) return false;
+        dims[0] = (cuuint64_t)dh; dims[1] = (cuuint64_t)heads; dims[2] = (cuuint64_t)p.L[2]; dims[3] = (cuuint64_t)p.L[1];
+        gstr[0] = (cuuint64_t)strides[2] * 2; gstr[1] = tok; gstr[2] = tok * p.L[2];
+        bx[1] = 1; bx[2] = (cuuint32_t)box[2]; bx[3] = (cuuint32_t)box[1];
+        const cuuint32_t e2 = es[1], e1 = es[2];
+        es[1] = 1; es[2] = e2; es[3] = e1;
+    }
     for (int i = 1; i < 4; ++i)
         if (es[i] > 8) return false;
     if (dims[4] == 0) return false;
@@ -414,7 +443,7 @@ inline bool encode_map(CUtensorMap* map, const void* base, bool bf16, const TcPa
 
 // Map over the additional tokens [B, Ne, heads, dh]: same 5-D form, one spatial axis of extent Ne.
 inline bool encode_extra_map(CUtensorMap* map, const void* base, bool bf16, int B, int n_extra, int heads,
-                             int dh, int box_cols)
+                             int dh, int box_cols, bool split_heads = false)
 {
     EncodeFn enc = get_encode();
     if (!enc || n_extra <= 0) return false;
@@ -423,6 +452,11 @@ inline bool encode_extra_map(CUtensorMap* map, const void* base, bool bf16, int 
     cuuint64_t gstr[4] = {tok, tok * n_extra, tok * n_extra, tok * n_extra};
     cuuint32_t bx[5] = {64, (cuuint32_t)box_cols, 1, 1, 1};
     cuuint32_t es[5] = {1, 1, 1, 1, 1};
+    if (split_heads) {                                           // [D, H, Ne, 1, B]
+        dims[0] = (cuuint64_t)dh; dims[1] = (cuuint64_t)heads; dims[2] = (cuuint64_t)n_extra;
+        gstr[0] = (cuuint64_t)dh * 2; gstr[1] = tok; gstr[2] = tok * n_extra;
+        bx[1] = 1; bx[2] = (cuuint32_t)box_cols;
+    }
     return enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
                const_cast<void*>(base), dims, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -445,7 +479,9 @@ inline unsigned persistent_grid(unsigned work, int per_sm)
 inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, const void* v, bool allow_stride = false)
 {
     if (dtype != 1 && dtype != 2) return false;                 // f16 / bf16
-    if ((g.D != 64 && g.D != 128) || g.Dv != g.D) return false;
+    if (g.D < 8 || g.D > 128 || g.D % 8 != 0 || g.Dv != g.D) return false;
+    const bool padded = g.D != 64 && g.D != 128;              // zero-padded channels need the head as a map axis of its own
+    if (padded && g.rank > 2) return false;
     if (!(g.scale > 0.0)) return false;
     for (int a = 0; a < g.rank; ++a) {
         if (g.st[a] != 1 && !allow_stride) return false;
@@ -453,7 +489,8 @@ inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, c
         if (g.extents && g.dil[a] != 1) return false;
     }
     // heads must be adjacent so that (head, channel) folds into one map dimension
-    if (g.qs[2] != g.D || g.ks[2] != g.D || g.vs[2] != g.Dv) return false;
+    if (!padded && (g.qs[2] != g.D || g.ks[2] != g.D || g.vs[2] != g.Dv)) return false;
+    if (padded && (g.qs[2] % 8 != 0 || g.ks[2] % 8 != 0 || g.vs[2] % 8 != 0)) return false;
     const long long strs[6] = {g.qs[0], g.qs[1], g.ks[0], g.ks[1], g.vs[0], g.vs[1]};
     for (long long s : strs)
         if (s % 8 != 0) return false;                           // 16-byte global strides

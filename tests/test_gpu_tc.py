@@ -29,6 +29,12 @@ CASES = [
     ((600,), 2, 4, 1, (255,), (1,), (False,), [[600], [300]], 128),
     ((5, 9, 17), 1, 2, 2, (3, 5, 7), (1, 1, 1), (True, False, False), None, 128),
     ((26, 30), 1, 2, 2, (5, 5), (2, 2), (False, False), None, 128),
+    # head dims that run zero-padded on the 64 / 128 kernels (ranks 1 and 2)
+    ((28, 28), 2, 4, 2, (7, 7), (1, 1), (False, False), None, 32),
+    ((24, 24), 2, 2, 2, (5, 5), (1, 1), (False, False), [[24, 24], [9, 17]], 32),
+    ((400,), 2, 4, 2, (63,), (1,), (False,), [[400], [123]], 48),
+    ((20, 19), 1, 2, 1, (5, 5), (2, 1), (True, False), None, 96),
+    ((300,), 1, 2, 2, (31,), (1,), (False,), None, 8),
 ]
 
 
