@@ -118,6 +118,17 @@ int natten_qk_fwd(const natten_params_t* params, const void* q, const void* k, v
 int natten_qk_bwd(const natten_params_t* params, const void* q, const void* k,
                   const void* dlogits, void* dq, void* dk, void* stream);
 
+/* Split QK with a relative position bias: logits += rpb[h, bias index of (position, slot)], rpb of
+ * shape [Hq, 2*K_0-1, (2*K_1-1, (2*K_2-1))] in the tensors' dtype; the backward also returns
+ * d_rpb (same shape, every entry written).  Stands in for natten1dqkrpb / natten2dqkrpb of
+ * src/natten_mps/compat/v014.py:66-183 (bias window start: src/natten_mps/utils/window.py:119-135)
+ * and their autograd.  Unit stride, non-causal, heads_q == heads_kv; anything else returns
+ * NATTEN_E_UNSUPPORTED after the plain QK part has been computed.                               */
+int natten_qk_rpb_fwd(const natten_params_t* params, const void* q, const void* k, const void* rpb,
+                      void* logits, void* stream);
+int natten_qk_rpb_bwd(const natten_params_t* params, const void* q, const void* k,
+                      const void* dlogits, void* dq, void* dk, void* d_rpb, void* stream);
+
 /* Split AV forward / backward: na{R}d_av_forward / na{R}d_av_backward
  * (src/natten_mps/_core/ops.py:112-124, 140-152; oracle _core/pure.py:257-291,
  * 520-565, 474-517).  heads_q/dim describe attn's head count; dim is unused.     */

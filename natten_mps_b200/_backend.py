@@ -194,3 +194,52 @@ def av_backward(dout, attn, v, kernel_size, dilation, stride, is_causal):
     _cabi.check(rc, "natten_av_bwd")
     _cabi.track_status(v)
     return dattn, dv
+
+
+def qk_rpb_forward(q, k, rpb, kernel_size, dilation, scale: Optional[float]):
+    """Logits with a relative position bias; ``rpb [H, 2*K_0-1, ...]``."""
+    _require_cuda(q, k, rpb)
+    rank = q.ndim - 3
+    spatial = tuple(q.shape[1:1 + rank])
+    B, Hq, D = q.shape[0], q.shape[-2], q.shape[-1]
+    q, qs = _cabi.as_strided_input(q, rank)
+    k, ks_ = _cabi.as_strided_input(k, rank)
+    rpb = rpb.to(q.dtype).contiguous()
+    ktot = 1
+    for x in kernel_size:
+        ktot *= x
+    ones, no = (1,) * rank, (False,) * rank
+    logits = torch.empty((B, *spatial, Hq, ktot), dtype=q.dtype, device=q.device)
+    p = _cabi.make_params(rank, q.dtype, B, Hq, k.shape[-2], D, D, spatial, kernel_size, ones, dilation, no,
+                          scale, 0, qs, ks_, ks_)
+    _cabi.poll_status(q.device)
+    with torch.cuda.device(q.device):
+        rc = _cabi.lib().natten_qk_rpb_fwd(p, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(rpb), _cabi.ptr(logits),
+                                           _cabi.stream_of(q))
+    _cabi.check(rc, "natten_qk_rpb_fwd")
+    _cabi.track_status(q)
+    return logits
+
+
+def qk_rpb_backward(dlogits, q, k, rpb_shape, kernel_size, dilation, scale: Optional[float]):
+    """-> (dq, dk, d_rpb)."""
+    _require_cuda(dlogits, q, k)
+    rank = q.ndim - 3
+    spatial = tuple(q.shape[1:1 + rank])
+    B, Hq, D = q.shape[0], q.shape[-2], q.shape[-1]
+    q, qs = _cabi.as_strided_input(q, rank)
+    k, ks_ = _cabi.as_strided_input(k, rank)
+    dlogits = dlogits.to(q.dtype).contiguous()
+    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    dk = torch.empty(k.shape, dtype=k.dtype, device=q.device)
+    drpb = torch.empty(tuple(rpb_shape), dtype=q.dtype, device=q.device)
+    ones, no = (1,) * rank, (False,) * rank
+    p = _cabi.make_params(rank, q.dtype, B, Hq, k.shape[-2], D, D, spatial, kernel_size, ones, dilation, no,
+                          scale, 0, qs, ks_, ks_)
+    _cabi.poll_status(q.device)
+    with torch.cuda.device(q.device):
+        rc = _cabi.lib().natten_qk_rpb_bwd(p, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(dlogits), _cabi.ptr(dq),
+                                           _cabi.ptr(dk), _cabi.ptr(drpb), _cabi.stream_of(q))
+    _cabi.check(rc, "natten_qk_rpb_bwd")
+    _cabi.track_status(q)
+    return dq, dk, drpb

@@ -21,7 +21,7 @@ PATH_NAMES = {0: "none", 1: "simt", 2: "tcgen05"}
 
 EXPORTS = (
     "natten_fused_fwd", "natten_fused_bwd", "natten_workspace_bytes", "natten_qk_fwd",
-    "natten_qk_bwd", "natten_av_fwd", "natten_av_bwd", "natten_strerror",
+    "natten_qk_bwd", "natten_qk_rpb_fwd", "natten_qk_rpb_bwd", "natten_av_fwd", "natten_av_bwd", "natten_strerror",
     "natten_abi_version", "natten_last_path", "natten_launch_count", "natten_device_status",
     "natten_clear_status", "natten_status_async", "natten_debug_wait",
     "natten_fused_bwd_static", "natten_static_scratch_bytes",
@@ -70,6 +70,8 @@ def lib():
         L.natten_workspace_bytes.restype = ctypes.c_size_t
         L.natten_qk_fwd.argtypes = [pp] + [vp] * 4
         L.natten_qk_bwd.argtypes = [pp] + [vp] * 6
+        L.natten_qk_rpb_fwd.argtypes = [pp] + [vp] * 5
+        L.natten_qk_rpb_bwd.argtypes = [pp] + [vp] * 7
         L.natten_av_fwd.argtypes = [pp] + [vp] * 4
         L.natten_av_bwd.argtypes = [pp] + [vp] * 6
         L.natten_strerror.argtypes = [ctypes.c_int]

@@ -2,6 +2,7 @@
 // and dispatch between the tcgen05 kernels and the SIMT kernels.
 #include "../../include/natten_b200.h"
 
+#include "rpb.cuh"
 #include "simt_kernels.cuh"
 #include "tc_kernels.cuh"
 
@@ -192,6 +193,33 @@ int natten_qk_bwd(const natten_params_t* p, const void* q, const void* k, const 
     }
     return from_cuda(simt_qk_bwd(p->dtype, g, q, k, dlogits, dq_done ? nullptr : dq, dk_done ? nullptr : dk,
                                  (cudaStream_t)stream));
+}
+
+int natten_qk_rpb_fwd(const natten_params_t* p, const void* q, const void* k, const void* rpb, void* logits,
+                      void* stream)
+{
+    if (!rpb) return NATTEN_E_INVALID;
+    int rc = natten_qk_fwd(p, q, k, logits, stream);
+    if (rc) return rc;
+    Geo g;
+    rc = make_geo(p, g);
+    if (rc) return rc;
+    if (g.B == 0) return NATTEN_OK;
+    simt_count_launch(1);
+    return rpb_add(p->dtype, g, rpb, logits, (cudaStream_t)stream);
+}
+
+int natten_qk_rpb_bwd(const natten_params_t* p, const void* q, const void* k, const void* dlogits,
+                      void* dq, void* dk, void* drpb, void* stream)
+{
+    if (!drpb) return NATTEN_E_INVALID;
+    int rc = natten_qk_bwd(p, q, k, dlogits, dq, dk, stream);
+    if (rc) return rc;
+    Geo g;
+    rc = make_geo(p, g);
+    if (rc) return rc;
+    simt_count_launch(1);
+    return rpb_grad(p->dtype, g, dlogits, drpb, (cudaStream_t)stream);
 }
 
 int natten_av_fwd(const natten_params_t* p, const void* attn, const void* v, void* out, void* stream)

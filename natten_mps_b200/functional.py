@@ -230,6 +230,60 @@ def na3d_qk(query, key, kernel_size: IntOrTuple, dilation: IntOrTuple = 1, *,
     return _na_qk(3, query, key, kernel_size, dilation, stride, is_causal, scale)
 
 
+class _QKRPB(torch.autograd.Function):
+    """Split QK with a relative position bias (``src/natten_mps/compat/v014.py:66-183``)."""
+
+    @staticmethod
+    def forward(ctx, query, key, rpb, ks, dil, scale):
+        from . import _backend
+        ctx.save_for_backward(query, key)
+        ctx.geo = (ks, dil, scale, tuple(rpb.shape), rpb.dtype)
+        return _backend.qk_rpb_forward(query, key, rpb, ks, dil, scale)
+
+    @staticmethod
+    def backward(ctx, grad_logits):
+        from . import _backend
+        query, key = ctx.saved_tensors
+        ks, dil, scale, rpb_shape, rpb_dtype = ctx.geo
+        dq, dk, drpb = _backend.qk_rpb_backward(grad_logits, query, key, rpb_shape, ks, dil, scale)
+        return dq, dk, drpb.to(rpb_dtype), None, None, None
+
+
+def _na_qk_rpb(rank, query, key, rpb, kernel_size, dilation, scale):
+    if query.ndim != rank + 3 or key.ndim != rank + 3:
+        raise ValueError(f"na{rank}d_qk_rpb expects query/key with shape {_LAYOUT[rank]}.")
+    if query.shape != key.shape:
+        raise ValueError("query and key must have identical shapes.")
+    ks = normalize_kernel_size(kernel_size, rank)
+    dil = normalize_tuple_param(dilation, rank, "dilation")
+    spatial = tuple(query.shape[1:1 + rank])
+    check_kernel_size_vs_input(ks, spatial)
+    check_dilation_kernel_vs_input(dil, ks, spatial)
+    want = (query.shape[-2], *[2 * x - 1 for x in ks])
+    if tuple(rpb.shape) != want:
+        raise ValueError(f"rpb must have shape {list(want)} for {rank}D.")
+    return _QKRPB.apply(query, key, rpb, ks, dil, None if scale is None else float(scale))
+
+
+def na1d_qk_rpb(query, key, rpb, kernel_size: IntOrTuple, dilation: IntOrTuple = 1, *,
+                scale: Optional[float] = None):
+    """``na1d_qk`` plus a relative position bias ``rpb [H, 2K-1]``: slot ``j`` of position ``i`` adds
+    ``rpb[h, get_pb_start(i) + j]`` (heads-last form of the reference's ``natten1dqkrpb``)."""
+    return _na_qk_rpb(1, query, key, rpb, kernel_size, dilation, scale)
+
+
+def na2d_qk_rpb(query, key, rpb, kernel_size: IntOrTuple, dilation: IntOrTuple = 1, *,
+                scale: Optional[float] = None):
+    """``na2d_qk`` plus ``rpb [H, 2Kh-1, 2Kw-1]`` (heads-last form of ``natten2dqkrpb``)."""
+    return _na_qk_rpb(2, query, key, rpb, kernel_size, dilation, scale)
+
+
+def na3d_qk_rpb(query, key, rpb, kernel_size: IntOrTuple, dilation: IntOrTuple = 1, *,
+                scale: Optional[float] = None):
+    """``na3d_qk`` plus ``rpb [H, 2Kd-1, 2Kh-1, 2Kw-1]``."""
+    return _na_qk_rpb(3, query, key, rpb, kernel_size, dilation, scale)
+
+
 def na1d_av(attn, value, kernel_size: IntOrTuple, dilation: IntOrTuple = 1, *,
             stride: IntOrTuple = 1, is_causal: BoolOrTuple = False):
     """Weighted sum of neighbourhood values: ``attn [B, L_out, H, K]``, ``value [B, L, H, Dv]``."""
@@ -334,6 +388,7 @@ def na3d_varlen(query, key, value, spatial_sizes: torch.Tensor, kernel_size: Int
 
 
 __all__ = [
+    "na1d_qk_rpb", "na2d_qk_rpb", "na3d_qk_rpb",
     "na1d", "na2d", "na3d", "na1d_qk", "na1d_av", "na2d_qk", "na2d_av", "na3d_qk", "na3d_av",
     "na1d_varlen", "na2d_varlen", "na3d_varlen",
 ]

@@ -50,3 +50,35 @@ def get_window_start_vectorized(indices: torch.Tensor, length: int, kernel_size:
                         full + phase - kernel_size * dilation)
     out = torch.where(idx + reach >= length, right, idx - reach)
     return torch.where(idx - reach < 0, phase, out)
+
+
+def get_pb_start(index: int, length: int, kernel_size: int, dilation: int) -> int:
+    """First entry of the relative-position-bias window of ``index``: slot ``j`` of the position's
+    neighbourhood reads bias entry ``get_pb_start(...) + j`` of a table with ``2 * kernel_size - 1``
+    entries per axis (reference: ``src/natten_mps/utils/window.py:119-135``)."""
+    half = kernel_size // 2
+    if dilation <= 1:
+        if index < half:
+            return half + (half - index)
+        if index + half >= length:
+            return half + (length - index - 1 - half)
+        return half
+    if index - half * dilation < 0:
+        return kernel_size - 1 - index // dilation
+    if index + half * dilation >= length:
+        return (length - index - 1) // dilation
+    return half
+
+
+def get_pb_start_vectorized(indices: torch.Tensor, length: int, kernel_size: int,
+                            dilation: int) -> torch.Tensor:
+    """Tensor form of :func:`get_pb_start` (reference: ``src/natten_mps/utils/window.py:49-83``)."""
+    idx = indices.to(torch.long)
+    half = kernel_size // 2
+    mid = torch.full_like(idx, half)
+    if dilation <= 1:
+        left = torch.where(idx < half, half - idx, torch.zeros_like(idx))
+        right = torch.where(idx + half >= length, length - idx - 1 - half, torch.zeros_like(idx))
+        return mid + left + right
+    out = torch.where(idx + half * dilation >= length, torch.div(length - idx - 1, dilation, rounding_mode="floor"), mid)
+    return torch.where(idx - half * dilation < 0, kernel_size - 1 - torch.div(idx, dilation, rounding_mode="floor"), out)

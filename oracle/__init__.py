@@ -65,6 +65,14 @@ def _load():
     return _lib
 
 
+def pb_start(index: int, length: int, kernel_size: int, dilation: int) -> int:
+    """``get_pb_start`` of ``utils/window.py:119-135``."""
+    lib = _load()
+    lib.ora_pb_start.restype = ctypes.c_int
+    lib.ora_pb_start.argtypes = [ctypes.c_int] * 4
+    return int(lib.ora_pb_start(index, length, kernel_size, dilation))
+
+
 def window_start(index: int, length: int, kernel_size: int, dilation: int) -> int:
     """``get_window_start`` of ``utils/window.py:91-111``."""
     return int(_load().ora_window_start(index, length, kernel_size, dilation))
@@ -225,3 +233,28 @@ def na_av_backward(attn, v, dout, kernel_size, dilation=1, stride=1, is_causal=F
     fn.restype = None
     fn(ctypes.byref(c.p), _ptr(attn), _ptr(v), _ptr(dout), _ptr(dattn), _ptr(dv))
     return dattn, dv
+
+
+def na_qk_rpb(q, k, rpb, kernel_size, dilation=1, scale=None, dtype=np.float64):
+    """Split QK plus relative position bias (``compat/v014.py:66-183``, heads-last layout)."""
+    logits = na_qk(q, k, kernel_size, dilation=dilation, scale=scale, dtype=dtype)
+    rank = q.ndim - 3
+    (rpb,) = _prep(dtype, rpb)
+    c = _Call(rank, q.shape, k.shape[-2], q.shape[-1], kernel_size, 1, dilation, False, 1.0, 0, None, 0)
+    fn = getattr(_load(), "ora_rpb_add" + _suffix(dtype))
+    fn.restype = None
+    fn(ctypes.byref(c.p), _ptr(rpb), _ptr(logits))
+    return logits
+
+
+def na_qk_rpb_backward(q, k, rpb, dlogits, kernel_size, dilation=1, scale=None, dtype=np.float64):
+    """-> ``(dq, dk, d_rpb)``."""
+    dq, dk = na_qk_backward(q, k, dlogits, kernel_size, dilation=dilation, scale=scale, dtype=dtype)
+    rank = q.ndim - 3
+    (dl,) = _prep(dtype, dlogits)
+    c = _Call(rank, q.shape, k.shape[-2], q.shape[-1], kernel_size, 1, dilation, False, 1.0, 0, None, 0)
+    drpb = np.empty(np.asarray(rpb).shape, dtype=dtype)
+    fn = getattr(_load(), "ora_rpb_grad" + _suffix(dtype))
+    fn.restype = None
+    fn(ctypes.byref(c.p), _ptr(dl), _ptr(drpb))
+    return dq, dk, drpb

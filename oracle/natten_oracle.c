@@ -56,6 +56,22 @@ int ora_window_start(int index, int length, int kernel_size, int dilation)
     return start;
 }
 
+/* First bias-table entry of a position's window on one axis.  Literal restatement of
+ * utils/window.py:119-135 (get_pb_start); slot kk reads entry ora_pb_start(...) + kk.      */
+int ora_pb_start(int index, int length, int kernel_size, int dilation)
+{
+    const int nh = kernel_size / 2;
+    if (dilation <= 1) {
+        int pb = nh;
+        if (index < nh) pb += nh - index;
+        else if (index + nh >= length) pb += length - index - 1 - nh;
+        return pb;
+    }
+    if (index - nh * dilation < 0) return kernel_size - 1 - index / dilation;
+    if (index + nh * dilation >= length) return (length - index - 1) / dilation;
+    return nh;
+}
+
 /* Key position of slot kk on one axis, or -1 when the slot is masked.
  * Non-causal: start + kk*dilation (_core/pure.py:27-41).  Causal:
  * p - (K-1-kk)*dilation, valid iff >= 0 (_core/pure.py:44-56).  A position

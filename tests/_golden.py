@@ -47,6 +47,25 @@ def module_cases():
     return manifest().get("modules", [])
 
 
+def rpb_cases():
+    return manifest().get("rpb", [])
+
+
+def pb_rows():
+    """Yield (index, length, kernel, dilation, pb_start) in the order of the window table."""
+    vals = arrays("window")["pb_start"]
+    n = 0
+    for L in range(1, 41):
+        for K in range(1, 12):
+            for dil in range(1, 5):
+                if K * dil > L:
+                    continue
+                for i in range(L):
+                    yield i, L, K, dil, int(vals[n])
+                    n += 1
+    assert n == len(vals)
+
+
 def varlen_cases():
     return manifest()["varlen"]
 

@@ -83,6 +83,14 @@ MODULES = [
           qk_scale=0.2), (1, 4, 6, 6, 32)),
 ]
 
+# Relative position bias (compat.v014 operators, heads-first there; stored heads-last here).
+RPB = [
+    ("rpb1d", 1, (19,), 2, 2, 8, dict(kernel_size=5, dilation=1)),
+    ("rpb1d_dil", 1, (23,), 1, 3, 4, dict(kernel_size=3, dilation=3)),
+    ("rpb2d", 2, (9, 8), 1, 2, 8, dict(kernel_size=(3, 5), dilation=(1, 1))),
+    ("rpb2d_dil_d32", 2, (14, 12), 1, 2, 32, dict(kernel_size=(5, 3), dilation=(2, 3))),
+]
+
 VARLEN = [
     ("var1d", 1, (20,), 3, 2, 8, dict(kernel_size=5), [[20], [7], [12]]),
     ("var1d_dil", 1, (24,), 2, 2, 8, dict(kernel_size=3, dilation=2), [[24], [9]]),
@@ -98,7 +106,7 @@ def _randn(g, *shape):
 
 def main():
     arrays = {}
-    manifest = {"fused": [], "split": [], "varlen": [], "modules": [], "window": None}
+    manifest = {"fused": [], "split": [], "varlen": [], "modules": [], "rpb": [], "window": None}
     fns = {1: RF.na1d, 2: RF.na2d, 3: RF.na3d}
     qk = {1: RF.na1d_qk, 2: RF.na2d_qk, 3: RF.na3d_qk}
     av = {1: RF.na1d_av, 2: RF.na2d_av, 3: RF.na3d_av}
@@ -188,6 +196,35 @@ def main():
             arrays[f"{name}/dp.{pn}"] = gt.numpy()
         manifest["modules"].append(dict(name=name, cls=cls, ctor=ctor))
 
+    from natten_mps.compat import v014 as C14
+    from natten_mps.utils.window import get_pb_start
+    for seed, (name, rank, spatial, B, H, D, kwargs) in enumerate(RPB, start=400):
+        g = torch.Generator().manual_seed(seed)
+        ks = kwargs["kernel_size"] if isinstance(kwargs["kernel_size"], tuple) else (kwargs["kernel_size"],)
+        q = _randn(g, B, *spatial, H, D).requires_grad_()
+        k = _randn(g, B, *spatial, H, D).requires_grad_()
+        rpb = _randn(g, H, *[2 * x - 1 for x in ks]).requires_grad_()
+        if rank == 1:
+            logits = C14.natten1dqkrpb(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), rpb,
+                                       kwargs["kernel_size"], kwargs["dilation"]).permute(0, 2, 1, 3)
+        else:
+            logits = C14.natten2dqkrpb(q.permute(0, 3, 1, 2, 4), k.permute(0, 3, 1, 2, 4), rpb,
+                                       kwargs["kernel_size"], kwargs["dilation"]).permute(0, 2, 3, 1, 4)
+        glog = _randn(g, *logits.shape)
+        dq, dk, drpb = torch.autograd.grad((logits * glog).sum(), [q, k, rpb])
+        for nm, t in dict(q=q, k=k, rpb=rpb, logits=logits, glog=glog, dq=dq, dk=dk, drpb=drpb).items():
+            arrays[f"{name}/{nm}"] = t.detach().contiguous().numpy()
+        manifest["rpb"].append(dict(name=name, rank=rank, kwargs=kwargs))
+    pb_rows = []
+    for L in range(1, 41):
+        for K in range(1, 12):
+            for dil in range(1, 5):
+                if K * dil > L:
+                    continue
+                for i in range(L):
+                    pb_rows.append(get_pb_start(i, L, K, dil))
+    arrays["window/pb_start"] = np.asarray(pb_rows, dtype=np.int16)
+
     # integer spec: every legal (L, K, dilation) with L <= 40, K <= 11, dilation <= 4
     rows = []
     for L in range(1, 41):
@@ -206,7 +243,7 @@ def main():
             return list(o)
         raise TypeError(type(o))
 
-    inputs = {"q", "k", "v", "ek", "ev", "gout", "glse", "glog", "attn", "x"}
+    inputs = {"q", "k", "v", "ek", "ev", "gout", "glse", "glog", "attn", "x", "rpb"}
 
     def _store(key, a):
         if a.dtype == np.int16:

@@ -1,0 +1,77 @@
+"""Relative position bias of the split QK operator on the GPU: against the fixtures produced by the
+reference's ``compat.v014`` operators (``natten1dqkrpb`` / ``natten2dqkrpb``) and against the oracle,
+through the heads-last functions and through the heads-first compat wrappers."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from natten_mps_b200 import functional as F
+from natten_mps_b200.compat import v014
+from tests import _golden as G
+from tests._gpu_util import TOL, dev, rounded
+
+pytestmark = pytest.mark.gpu
+FN = {1: F.na1d_qk_rpb, 2: F.na2d_qk_rpb}
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32, torch.bfloat16, torch.float16],
+                         ids=lambda d: str(d).split(".")[-1])
+@pytest.mark.parametrize("case", G.rpb_cases(), ids=lambda c: c["name"])
+def test_rpb_against_golden_and_oracle(case, dtype):
+    a = G.arrays(case["name"])
+    kw = G.kw(case)
+    rank = case["rank"]
+    q, k, rpb = dev(a["q"], dtype, True), dev(a["k"], dtype, True), dev(a["rpb"], dtype, True)
+    logits = FN[rank](q, k, rpb, **kw)
+    dq, dk, drpb = torch.autograd.grad((logits.double() * dev(a["glog"], torch.float64)).sum(), [q, k, rpb])
+    r = lambda x: rounded(x, dtype)
+    want = oracle.na_qk_rpb(r(a["q"]), r(a["k"]), r(a["rpb"]), **kw)
+    wdq, wdk, wdrpb = oracle.na_qk_rpb_backward(r(a["q"]), r(a["k"]), r(a["rpb"]), a["glog"], **kw)
+    for name, got, ref in (("logits", logits, want), ("dq", dq, wdq), ("dk", dk, wdk), ("drpb", drpb, wdrpb)):
+        g = got.detach().double().cpu().numpy()
+        err = np.abs(g - ref).max()
+        bound = TOL[dtype] * max(1.0, np.abs(ref).max())       # raw dot products / sums: relative to the tensor
+        assert err <= bound, (name, err, bound)
+    if dtype == torch.float64:                                  # the reference's own numbers
+        for name, got in (("logits", logits), ("dq", dq), ("dk", dk), ("drpb", drpb)):
+            assert np.abs(got.detach().cpu().numpy() - a[name]).max() < 1e-10, name
+
+
+def test_compat_wrappers_are_heads_first():
+    torch.manual_seed(0)
+    B, H, L, D, K = 2, 3, 21, 16, 5
+    q, k = torch.randn(B, H, L, D, device="cuda"), torch.randn(B, H, L, D, device="cuda")
+    rpb = torch.randn(H, 2 * K - 1, device="cuda")
+    got = v014.natten1dqkrpb(q, k, rpb, K, 1)
+    assert got.shape == (B, H, L, K)
+    ref = F.na1d_qk_rpb(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), rpb, K, 1).permute(0, 2, 1, 3)
+    assert torch.equal(got, ref)
+    attn = torch.softmax(got, -1)
+    v = torch.randn(B, H, L, D, device="cuda")
+    out = v014.natten1dav(attn, v, K, 1)
+    assert out.shape == (B, H, L, D)
+    q2, k2 = torch.randn(1, 2, 9, 8, 16, device="cuda"), torch.randn(1, 2, 9, 8, 16, device="cuda")
+    rpb2 = torch.randn(2, 5, 5, device="cuda")
+    l2 = v014.natten2dqkrpb(q2, k2, rpb2, 3, 1)
+    assert l2.shape == (1, 2, 9, 8, 9)
+    o2 = v014.natten2dav(torch.softmax(l2, -1), torch.randn(1, 2, 9, 8, 16, device="cuda"), 3, 1)
+    assert o2.shape == (1, 2, 9, 8, 16)
+    with pytest.raises(ValueError, match="rpb must have shape"):
+        v014.natten1dqkrpb(q, k, rpb[:, :-1], K, 1)
+
+
+def test_rpb_gradient_is_bit_reproducible_and_3d_runs():
+    torch.manual_seed(1)
+    q = torch.randn(2, 4, 6, 5, 2, 16, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn_like(q).requires_grad_(True)
+    rpb = torch.randn(2, 5, 5, 5, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    grads = []
+    for _ in range(2):
+        out = F.na3d_qk_rpb(q, k, rpb, 3)
+        grads.append(torch.autograd.grad(out.float().square().sum(), [q, k, rpb]))
+    for a, b in zip(*grads):
+        assert torch.equal(a, b)
+    f = lambda t: t.detach().float().cpu().numpy()
+    want = oracle.na_qk_rpb(f(q), f(k), f(rpb), 3, dtype=np.float32)
+    assert np.abs(f(out) - want).max() <= 2e-2 * max(1.0, np.abs(want).max())

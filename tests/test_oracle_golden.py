@@ -79,3 +79,22 @@ def test_float32_oracle_tracks_float64():
     o64, _ = oracle.na_forward(a["q"], a["k"], a["v"], kernel_size=(3, 5))
     o32, _ = oracle.na_forward(a["q"], a["k"], a["v"], kernel_size=(3, 5), dtype=np.float32)
     assert np.abs(o64 - o32).max() < 1e-5
+
+
+def test_pb_start_matches_reference_table():
+    from natten_mps_b200.utils import get_pb_start
+    for i, L, K, dil, want in G.pb_rows():
+        assert oracle.pb_start(i, L, K, dil) == want
+        assert get_pb_start(i, L, K, dil) == want
+
+
+@pytest.mark.parametrize("case", G.rpb_cases(), ids=lambda c: c["name"])
+def test_rpb_against_reference_outputs(case):
+    """Relative position bias: the oracle against the reference's compat.v014 operators."""
+    a = G.arrays(case["name"])
+    kw = G.kw(case)
+    logits = oracle.na_qk_rpb(a["q"], a["k"], a["rpb"], **kw)
+    assert np.abs(logits - a["logits"]).max() < 1e-10
+    dq, dk, drpb = oracle.na_qk_rpb_backward(a["q"], a["k"], a["rpb"], a["glog"], **kw)
+    for name, got in (("dq", dq), ("dk", dk), ("drpb", drpb)):
+        assert np.abs(got - a[name]).max() < 1e-10, name
