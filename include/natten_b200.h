@@ -99,8 +99,12 @@ size_t natten_workspace_bytes(const natten_params_t* params, int op);
 
 /* natten_fused_bwd for callers that cannot allocate device memory (no counterpart in
  * the reference, which always allocates through PyTorch).  Same arguments without the
- * workspace: the scratch is a fixed 4 MiB array inside the library, enough for
- * batch * queries * heads_q <= 1 048 576; larger problems return NATTEN_E_TOO_LARGE.
+ * workspace: the scratch is a fixed array of natten_static_scratch_bytes() (4 MiB) inside the
+ * library.  A problem fits when natten_workspace_bytes(params, NATTEN_OP_FUSED_BWD) is at most
+ * that size; larger problems return NATTEN_E_TOO_LARGE and launch nothing.  The workspace holds
+ * one accumulator per (batch, query, head) -- 4 bytes, 8 for F64 -- plus, with additional
+ * tokens, their partial gradient sums: e.g. batch * queries * heads_q <= 1 048 576 for
+ * F32 / F16 / BF16 without additional tokens, half that for F64.
  * The first call on each device queries the array's device address (no allocation):
  * make it before any stream capture.  All calls on a device share the array, so calls
  * whose kernels can overlap (different streams) race; keep them on one stream.        */

@@ -8,9 +8,11 @@
 // fixed array inside the library image, so the caller passes inputs and outputs only.
 //
 // Limits and rules
-//   * at most kStaticRows rows, i.e. batch * queries * heads_q <= 1 048 576 (4 MiB of
-//     scratch per GPU that loads the library, held until the process exits); larger
-//     problems are rejected with NATTEN_E_TOO_LARGE and nothing is launched;
+//   * the array is 4 MiB per GPU that loads the library, held until the process exits; a problem
+//     fits when natten_workspace_bytes(params, NATTEN_OP_FUSED_BWD) <= 4 MiB: one accumulator per
+//     (batch, query, head) -- 4 bytes, 8 in double precision -- plus the partial sums of the
+//     additional tokens' gradients when there are any (1 048 576 rows in the plain 4-byte case);
+//     larger problems are rejected with NATTEN_E_TOO_LARGE and nothing is launched;
 //   * the first call on each device looks up the array's device address (no
 //     allocation, but a runtime query): make that first call before any stream capture;
 //   * every call on a device uses the same array, so two calls whose kernels may run

@@ -744,21 +744,6 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
 {
     const TcParams& p = plan.p;
     const long long qrows = (long long)g.B * g.ltot * g.Hq;
-    {
-        // rows handled per pass of the grid: a whole number of blocks, a quarter of the rows each
-        auto run_delta = [&](auto per) {
-            constexpr int kPer = decltype(per)::value;
-            const long long rows_per_block = 256 / kPer;
-            const long long blocks = ((qrows + kDeltaRows - 1) / kDeltaRows + rows_per_block - 1) / rows_per_block;
-            tc_delta_kernel<kPer, BF16><<<(unsigned)blocks, 256, 0, s>>>(
-                (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, qrows, blocks * rows_per_block, g.D);
-        };
-        if (g.D <= 32) run_delta(std::integral_constant<int, 4>{});
-        else if (g.D <= 64) run_delta(std::integral_constant<int, 8>{});
-        else run_delta(std::integral_constant<int, 16>{});
-    }
-    tc_count_launch();
-
     const long long dos[3] = {g.ltot * g.Hq * g.Dv, (long long)g.Hq * g.Dv, g.Dv};   // dout is contiguous
     CUtensorMap q_tile, do_tile, k_chunk, v_chunk, k_tile, v_tile, q_chunk, do_chunk, ek_chunk, ev_chunk;
     const bool bf = BF16;
@@ -776,6 +761,22 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
     if (g.n_extra > 0 && (!encode_extra_map(&ek_chunk, ek, bf, g.B, g.n_extra, g.Hkv, g.D, kCols, p.split_heads) ||
                           !encode_extra_map(&ev_chunk, ev, bf, g.B, g.n_extra, g.Hkv, g.D, kCols, p.split_heads)))
         return -2;
+    // delta only once nothing can send this call to the other kernel family any more
+    {
+        // rows handled per pass of the grid: a whole number of blocks, a quarter of the rows each
+        auto run_delta = [&](auto per) {
+            constexpr int kPer = decltype(per)::value;
+            const long long rows_per_block = 256 / kPer;
+            const long long blocks = ((qrows + kDeltaRows - 1) / kDeltaRows + rows_per_block - 1) / rows_per_block;
+            tc_delta_kernel<kPer, BF16><<<(unsigned)blocks, 256, 0, s>>>(
+                (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, qrows, blocks * rows_per_block, g.D);
+        };
+        if (g.D <= 32) run_delta(std::integral_constant<int, 4>{});
+        else if (g.D <= 64) run_delta(std::integral_constant<int, 8>{});
+        else run_delta(std::integral_constant<int, 16>{});
+    }
+    tc_count_launch();
+
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= p.dil[a];
     const dim3 grid_q(persistent_grid(p.work_q, DH == 64 ? 2 : 1));
