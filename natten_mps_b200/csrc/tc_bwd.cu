@@ -737,32 +737,79 @@ tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ d
     }
 }
 
+// Output stride > 1: only every stride-th position is a query.  The backward kernels keep their
+// unit-stride geometry and get full-resolution copies of dout, lse and delta instead: at a query position
+// the caller's row, elsewhere dout = 0, delta = 0 and lse = 1e30, so that the recomputed probability of such
+// a row is exp(s - 1e30) = 0 and it contributes exactly nothing (its dq row comes out as zeros, which is
+// what the operator defines for positions that are not queries).
+struct Expanded {
+    const Geo* original;           // the caller's (strided) geometry
+    void* dout_full;               // [B, *L, Hq, D]
+    float *lse_full, *delta_full;  // [B, *L, Hq]
+};
+
+__global__ void __launch_bounds__(256)
+expand_strided_kernel(const __grid_constant__ Geo g, const uint4* __restrict__ dout, const float* __restrict__ lse,
+                      const float* __restrict__ delta, uint4* __restrict__ dout_full, float* __restrict__ lse_full,
+                      float* __restrict__ delta_full, long long total, int vecs)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int vec = (int)(i % vecs);
+    const long long row = i / vecs;                    // (b * ltot + p) * Hq + h
+    const int h = (int)(row % g.Hq);
+    long long p = (row / g.Hq) % g.ltot;
+    const long long b = row / g.Hq / g.ltot;
+    bool query = true;
+    long long oflat = 0, mul = 1;
+    for (int a = g.rank - 1; a >= 0; --a) {
+        const int pos = (int)(p % g.L[a]);
+        p /= g.L[a];
+        if (pos % g.st[a] != 0) query = false;
+        oflat += (long long)(pos / g.st[a]) * mul;
+        mul *= g.O[a];
+    }
+    const long long orow = (b * g.otot + oflat) * g.Hq + h;
+    dout_full[i] = query ? dout[orow * vecs + vec] : make_uint4(0, 0, 0, 0);
+    if (vec == 0) {
+        lse_full[row] = query ? lse[orow] : 1e30f;
+        delta_full[row] = query ? delta[orow] : 0.f;
+    }
+}
+
 template <int DH, bool BF16>
 int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const void* k, const void* v,
                const void* ek, const void* ev, void* dek, void* dev, const void* out, const void* lse, const void* dout, const void* dlse, void* dq, void* dk,
-               void* dv, float* delta, cudaStream_t s)
+               void* dv, float* delta, cudaStream_t s, const Expanded* ex = nullptr)
 {
     const TcParams& p = plan.p;
-    const long long qrows = (long long)g.B * g.ltot * g.Hq;
+    const long long qrows = (long long)g.B * g.otot * g.Hq;
+    // With an output stride the kernels run on the unit-stride geometry `g` over full-resolution copies of
+    // dout / lse / delta (see expand_strided_kernel); the caller's arrays are only read to build them.
+    const void* dout_k = ex ? ex->dout_full : dout;
+    const float* lse_k = ex ? ex->lse_full : (const float*)lse;
+    const float* delta_k = ex ? ex->delta_full : delta;
     const long long dos[3] = {g.ltot * g.Hq * g.Dv, (long long)g.Hq * g.Dv, g.Dv};   // dout is contiguous
     CUtensorMap q_tile, do_tile, k_chunk, v_chunk, k_tile, v_tile, q_chunk, do_chunk, ek_chunk, ev_chunk;
     const bool bf = BF16;
     using Smem = SmemB<DH>;
     if (!encode_map(&q_tile, q, bf, p, g.Hq, g.D, g.qs, plan.box_q) ||
-        !encode_map(&do_tile, dout, bf, p, g.Hq, g.D, dos, plan.box_q) ||
+        !encode_map(&do_tile, dout_k, bf, p, g.Hq, g.D, dos, plan.box_q) ||
         !encode_map(&k_chunk, k, bf, p, g.Hkv, g.D, g.ks, plan.box_kv) ||
         !encode_map(&v_chunk, v, bf, p, g.Hkv, g.D, g.vs, plan.box_kv) ||
         !encode_map(&k_tile, k, bf, p, g.Hkv, g.D, g.ks, plan.box_q) ||
         !encode_map(&v_tile, v, bf, p, g.Hkv, g.D, g.vs, plan.box_q) ||
         !encode_map(&q_chunk, q, bf, p, g.Hq, g.D, g.qs, plan.box_kv) ||
-        !encode_map(&do_chunk, dout, bf, p, g.Hq, g.D, dos, plan.box_kv))
+        !encode_map(&do_chunk, dout_k, bf, p, g.Hq, g.D, dos, plan.box_kv))
         return -2;
     ek_chunk = k_chunk; ev_chunk = v_chunk;      // placeholders when there are no additional tokens
     if (g.n_extra > 0 && (!encode_extra_map(&ek_chunk, ek, bf, g.B, g.n_extra, g.Hkv, g.D, kCols, p.split_heads) ||
                           !encode_extra_map(&ev_chunk, ev, bf, g.B, g.n_extra, g.Hkv, g.D, kCols, p.split_heads)))
         return -2;
     // delta only once nothing can send this call to the other kernel family any more
+    const Geo& go = ex ? *ex->original : g;      // geometry of out / dout / lse as the caller holds them
     {
+        const long long qrows = (long long)go.B * go.otot * go.Hq;
         // rows handled per pass of the grid: a whole number of blocks, a quarter of the rows each
         auto run_delta = [&](auto per) {
             constexpr int kPer = decltype(per)::value;
@@ -776,6 +823,15 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
         else run_delta(std::integral_constant<int, 16>{});
     }
     tc_count_launch();
+    if (ex) {                                    // scatter dout / lse / delta onto the full-resolution grid
+        const long long rows_full = (long long)g.B * g.ltot * g.Hq;
+        const int vecs = g.D / 8;
+        const long long total = rows_full * vecs;
+        expand_strided_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(
+            *ex->original, (const uint4*)dout, (const float*)lse, delta, (uint4*)ex->dout_full, ex->lse_full,
+            ex->delta_full, total, vecs);
+        tc_count_launch();
+    }
 
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= p.dil[a];
@@ -786,10 +842,10 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
         ensure_dynamic_smem((const void*)tc_bwd_kernel<DH, BF16, false, kInner>, Smem::kTotal);
         ensure_dynamic_smem((const void*)tc_bwd_kernel<DH, BF16, true, kInner>, Smem::kTotal);
         tc_bwd_kernel<DH, BF16, false, kInner><<<grid_q, kThreads, Smem::kTotal, s>>>(
-            q_tile, do_tile, k_chunk, v_chunk, ek_chunk, ev_chunk, p, (const float*)lse, delta, (uint16_t*)dq, nullptr);
+            q_tile, do_tile, k_chunk, v_chunk, ek_chunk, ev_chunk, p, lse_k, delta_k, (uint16_t*)dq, nullptr);
         tc_count_launch();
         tc_bwd_kernel<DH, BF16, true, kInner><<<grid_k, kThreads, Smem::kTotal, s>>>(
-            k_tile, v_tile, q_chunk, do_chunk, ek_chunk, ev_chunk, p, (const float*)lse, delta, (uint16_t*)dk, (uint16_t*)dv);
+            k_tile, v_tile, q_chunk, do_chunk, ek_chunk, ev_chunk, p, lse_k, delta_k, (uint16_t*)dk, (uint16_t*)dv);
         tc_count_launch();
     };
     if (p.cb[2] == 16) launch(std::integral_constant<int, 16>{});
@@ -798,20 +854,44 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
     cudaError_t err = cudaGetLastError();
     // The additional tokens' own gradients sum over every query of the sample: SIMT kernel.
     if (err == cudaSuccess && g.n_extra > 0)
-        err = simt_fused_bwd_extra(dtype, g, q, ek, ev, lse, delta, dout, dek, dev,
-                                   reinterpret_cast<unsigned char*>(delta) + simt_delta_bytes(g, 4), s);
+        err = simt_fused_bwd_extra(dtype, go, q, ek, ev, lse, delta, dout, dek, dev,
+                                   reinterpret_cast<unsigned char*>(delta) + simt_delta_bytes(go, 4), s);
     return err == cudaSuccess ? 0 : (int)err;
 }
 
 } // namespace
 
-int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const void* v, const void* ek,
+namespace {
+size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+bool has_stride(const Geo& g)
+{
+    for (int a = 0; a < g.rank; ++a)
+        if (g.st[a] != 1) return true;
+    return false;
+}
+} // namespace
+
+int tc_fused_bwd(int dtype, const Geo& g_in, const void* q, const void* k, const void* v, const void* ek,
                  const void* ev, const void* out, const void* lse, const void* dout, const void* dlse,
                  void* dq, void* dk, void* dv, void* dek, void* dev, void* workspace, cudaStream_t s)
 {
-    if (!tc_eligible(dtype, g, q, k, v)) return -2;
-    if (g.n_extra > 0 && ((reinterpret_cast<uintptr_t>(ek) | reinterpret_cast<uintptr_t>(ev)) & 15u)) return -2;
+    if (!tc_eligible(dtype, g_in, q, k, v, /*allow_stride=*/true)) return -2;
+    if (g_in.n_extra > 0 && ((reinterpret_cast<uintptr_t>(ek) | reinterpret_cast<uintptr_t>(ev)) & 15u)) return -2;
     if (reinterpret_cast<uintptr_t>(dout) & 15u) return -2;
+    const bool strided = has_stride(g_in);
+    Geo g = g_in;
+    Expanded ex;
+    if (strided) {                               // unit-stride geometry over full-resolution copies
+        for (int a = 0; a < 3; ++a) { g.st[a] = 1; g.O[a] = g.L[a]; }
+        g.otot = g.ltot;
+        unsigned char* base = static_cast<unsigned char*>(workspace) + simt_delta_bytes(g_in, 4) +
+                              simt_extra_partial_bytes(dtype, g_in);
+        const size_t rows_full = (size_t)g.B * (size_t)g.ltot * (size_t)g.Hq;
+        ex.original = &g_in;
+        ex.delta_full = reinterpret_cast<float*>(base);
+        ex.lse_full = reinterpret_cast<float*>(base + align256(rows_full * 4));
+        ex.dout_full = base + 2 * align256(rows_full * 4);
+    }
     Plan plan;
     if (!make_plan(g, plan, kCols)) return -2;
     plan.p.status = status_ptr();
@@ -819,14 +899,22 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
     if (g.B == 0) return 0;
     if (g.Hq > 65535 || g.B > 65535) return -2;
     float* delta = reinterpret_cast<float*>(workspace);
+    const Expanded* exp = strided ? &ex : nullptr;
     if (g.D <= 64)
-        return dtype == 2 ? launch_bwd<64, true>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s)
-                          : launch_bwd<64, false>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s);
-    return dtype == 2 ? launch_bwd<128, true>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s)
-                      : launch_bwd<128, false>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s);
+        return dtype == 2 ? launch_bwd<64, true>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s, exp)
+                          : launch_bwd<64, false>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s, exp);
+    return dtype == 2 ? launch_bwd<128, true>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s, exp)
+                      : launch_bwd<128, false>(dtype, g, plan, q, k, v, ek, ev, dek, dev, out, lse, dout, dlse, dq, dk, dv, delta, s, exp);
 }
 
-size_t tc_bwd_workspace_bytes(int, const Geo&) { return 0; }
+// Scratch of the strided backward (full-resolution delta, lse and dout); sized for every 16-bit strided
+// problem, whichever kernel family ends up serving it.
+size_t tc_bwd_workspace_bytes(int dtype, const Geo& g)
+{
+    if ((dtype != 1 && dtype != 2) || !has_stride(g)) return 0;
+    const size_t rows_full = (size_t)g.B * (size_t)g.ltot * (size_t)g.Hq;
+    return 2 * align256(rows_full * 4) + align256(rows_full * (size_t)g.D * 2);
+}
 
 #ifdef NATTEN_TRACE
 extern "C" int natten_trace_read_bwd(long long* host, int clear)

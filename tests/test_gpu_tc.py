@@ -338,3 +338,49 @@ def test_tc_qk_backward_matches_simt(case, dtype):
     for name, a, r in (("dq", dq, ref_dq), ("dk", dk, ref_dk)):
         err = (a.float() - r.float()).abs().max().item()
         assert err <= 2e-2 * max(1.0, r.float().abs().max().item()), f"{name} differs by {err}"
+
+
+STRIDED_BWD_CASES = [
+    # spatial, B, Hq, Hkv, kernel, dilation, stride, causal, D
+    ((40, 36), 1, 2, 2, (5, 5), (1, 1), (2, 2), (False, False), 64),
+    ((33, 40), 2, 2, 1, (7, 3), (2, 1), (2, 3), (False, True), 64),
+    ((128, 128), 1, 2, 2, (13, 13), (2, 2), (2, 2), (False, False), 64),      # the dilated benchmark shape, stride 2
+    ((301,), 2, 4, 2, (31,), (1,), (4,), (False,), 128),
+    ((6, 10, 12), 1, 2, 2, (3, 3, 5), (1, 1, 1), (1, 2, 2), (True, False, False), 64),
+    ((30, 28), 1, 2, 2, (5, 5), (1, 1), (3, 2), (False, False), 32),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", STRIDED_BWD_CASES, ids=lambda c: "x".join(map(str, c[0])) + f"_s{c[6][-1]}_h{c[8]}")
+def test_tc_strided_backward_matches_simt(case, dtype):
+    """Output stride: the tensor-core backward runs on full-resolution copies of dout / lse / delta in
+    which the rows that are not queries contribute nothing; dq must be exactly zero there."""
+    spatial, B, Hq, Hkv, ks, dil, st, causal, D = case
+    g = torch.Generator(device="cpu").manual_seed(19)
+    osp = [-(-n // s) for n, s in zip(spatial, st)]
+    q = torch.randn((B, *spatial, Hq, D), generator=g).to(dtype).cuda()
+    k = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    v = torch.randn((B, *spatial, Hkv, D), generator=g).to(dtype).cuda()
+    go = torch.randn((B, *osp, Hq, D), generator=g).to(dtype).cuda()
+    glse = torch.randn((B, *osp, Hq), generator=g).cuda()
+    geo = (ks, st, dil, causal, D ** -0.5)
+    try:
+        _cabi.set_force("simt")
+        out, lse = _backend.fused_forward(q, k, v, *geo)
+        ref = _backend.fused_backward(q, k, v, out, lse, go, *geo, dlse=glse)
+        _cabi.set_force("tc")
+        got = _backend.fused_backward(q, k, v, out, lse, go, *geo, dlse=glse)
+        assert _cabi.last_path() == "tcgen05"
+    finally:
+        _cabi.set_force(None)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    for name, a, r in zip(("dq", "dk", "dv"), got[:3], ref[:3]):
+        err = (a.float() - r.float()).abs().max().item()
+        scale = max(1.0, r.float().abs().max().item())
+        assert err <= 2e-2 * scale, f"{name} differs by {err} (scale {scale})"
+    # positions that are not queries get exactly zero dq
+    mask = torch.ones(spatial, dtype=torch.bool)
+    mask[tuple(slice(None, None, s) for s in st)] = False
+    assert float(got[0][:, mask.cuda()].abs().sum()) == 0.0
