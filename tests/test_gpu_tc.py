@@ -149,15 +149,16 @@ def test_tc_additional_tokens_match_simt(case, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
 @pytest.mark.parametrize("D", [64, 128])
-@pytest.mark.parametrize("spatial,ks", [((700,), (255,)), ((40, 48), (13, 13))], ids=["1d", "2d"])
-def test_tc_forward_rescales_when_later_chunks_dominate(spatial, ks, D, dtype):
-    """Scores that grow steeply along the key axis: every later chunk of a tile raises the row
-    maximum by far more than the 2^8 the stored probabilities may exceed their stabiliser by,
-    so the output accumulated in TMEM has to be rescaled chunk after chunk."""
+@pytest.mark.parametrize("spatial,ks,slope", [((700,), (255,), 12.0 / 128.0), ((40, 48), (13, 13), 1.0),
+                                              ((40, 48), (13, 13), 4.0)], ids=["1d", "2d", "2d_steep"])
+def test_tc_forward_rescales_when_later_chunks_dominate(spatial, ks, slope, D, dtype):
+    """Scores that grow steeply along the key axis (`slope` per key along the innermost axis): later
+    chunks of a tile raise the row maximum by far more than the stored probabilities may exceed their
+    stabiliser by (2^8 in the 128-channel kernel; 2^14 for fp16 and 2^60 for bf16 in the 64-channel
+    kernel, which the steep case exceeds), so the output accumulated in TMEM has to be rescaled."""
     rank = len(spatial)
     B, H = 2, 2
     g = torch.Generator(device="cpu").manual_seed(23)
-    slope = 12.0 / 128.0 if rank == 1 else 1.0          # per key along the innermost axis: > 8 / log2(e) per chunk
     ramp = (torch.arange(spatial[-1], dtype=torch.float32) * slope).reshape((1,) * (rank - 1) + (spatial[-1], 1, 1))
     q = torch.randn((B, *spatial, H, D), generator=g) * 0.1 + 1.0
     k = torch.randn((B, *spatial, H, D), generator=g) * 0.1 + ramp.unsqueeze(0) / (D ** 0.5)
