@@ -25,7 +25,7 @@ def _case(seed=0, B=2, H=24, W=40, heads=2, D=64, dtype=torch.bfloat16, device="
 
 
 def _oracle_out(q, k, v, K):
-    f = lambda t: t.float().cpu().numpy()
+    f = lambda t: t.detach().float().cpu().numpy()
     return oracle.na_forward(f(q), f(k), f(v), kernel_size=K, dtype=np.float32)[0]
 
 
