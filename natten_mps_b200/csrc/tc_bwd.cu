@@ -5,8 +5,8 @@
 //     S = Q K^T, dP = dO V^T (tensor cores, TMEM); threads turn them into
 //     dS = P (dP - delta) * scale with P = exp2(S*scale*log2e - lse*log2e); dQ += dS K.
 //   * key side: rows = a box of 128 keys, columns = chunks of the box of queries that
-//     attend to them (the inverse neighbourhood, a contiguous range per axis for odd
-//     kernels), for every query head of the GQA group.  S^T = K Q^T, dP^T = V dO^T;
+//     attend to them (the inverse neighbourhood, a contiguous range per axis), for
+//     every query head of the GQA group.  S^T = K Q^T, dP^T = V dO^T;
 //     dV += P^T dO, dK += dS^T Q.  Per-column lse / delta are staged in shared memory
 //     by a helper warp.
 // The row accumulators live in TMEM for the whole tile, so dK/dV are reduced in a
@@ -79,18 +79,6 @@ struct SmemB {
 
 __device__ __forceinline__ int ws1(int p, int L, int K) { return window_start(p, L, K, 1); }
 
-// Queries attending to key n on one axis (odd kernel, unit dilation inside the sub-grid).
-__device__ __forceinline__ void inverse_range(int n, int L, int K, int causal, int& qlo, int& qhi)
-{
-    if (causal) {
-        qlo = n;
-        qhi = n + K - 1 < L - 1 ? n + K - 1 : L - 1;
-    } else {
-        qlo = (n <= K - 1) ? 0 : n - K / 2;
-        qhi = (n >= L - K) ? L - 1 : n + K / 2;
-    }
-}
-
 // Geometry of one work item: a tile of 128 rows (queries | keys) of one (batch, head).
 struct BwdTile {
     int b, hy;                 // batch; head of the row tensors (query head | kv head)
@@ -130,8 +118,8 @@ __device__ __forceinline__ void bwd_tile_setup(const TcParams& P, unsigned work,
             int hi;
             if (kKeySide) {
                 int t;
-                inverse_range(T.origin[a], T.Lp[a], P.K[a], P.causal[a], T.boxlo[a], t);
-                inverse_range(last, T.Lp[a], P.K[a], P.causal[a], t, hi);
+                inverse_range(T.origin[a], T.Lp[a], P.K[a], P.causal[a], T.boxlo[a], t, /*exact=*/false);
+                inverse_range(last, T.Lp[a], P.K[a], P.causal[a], t, hi, /*exact=*/false);
             } else {
                 T.boxlo[a] = P.causal[a] ? T.origin[a] - (P.K[a] - 1) : ws1(T.origin[a], T.Lp[a], P.K[a]);
                 hi = P.causal[a] ? last : ws1(last, T.Lp[a], P.K[a]) + P.K[a] - 1;

@@ -113,6 +113,25 @@ __device__ __forceinline__ int chunks_along(const TcParams& P, int a, int extent
     return (extent + P.cb[a] - 1) >> lg;
 }
 
+// Queries x of a sub-grid of length L whose window holds key n, as the range [qlo, qhi].  The window
+// start s(x) = window_start(x, L, K, 1) never decreases with x, so the set is a range.  Every window
+// that is clamped at the end starts at `last`: L-K for an odd kernel, L-K-1 for an even one (the
+// reference's window arithmetic never reaches the last key with an even kernel).  `exact` = false
+// gives a range that is never empty (a superset, for bounding boxes); with `exact` a key that no query
+// attends to gets qhi < qlo.
+__device__ __forceinline__ void inverse_range(int n, int L, int K, int causal, int& qlo, int& qhi, bool exact = true)
+{
+    if (causal) {
+        qlo = n;
+        qhi = n + K - 1 < L - 1 ? n + K - 1 : L - 1;
+        return;
+    }
+    const int nh = K / 2, last = L - K - 1 + (K & 1);
+    qlo = (n <= K - 1) ? 0 : n - (K - 1 - nh);
+    qhi = (n >= last) ? L - 1 : n + nh;
+    if (exact && n > last + K - 1) qhi = qlo - 1;
+}
+
 // Row r (0..127) of the tile -> offsets along the three axes.
 __device__ __forceinline__ void row_offsets(const TcParams& P, int r, int (&ri)[3])
 {
@@ -476,6 +495,14 @@ inline unsigned persistent_grid(unsigned work, int per_sm)
     return work < cap ? work : cap;
 }
 
+// Kernel sizes the tensor-core geometry covers along axis a: every odd size; an even size when the axis
+// is not dilated, longer than the kernel and has no per-sample extents (with an even kernel the
+// reference's clamped window start depends on the dilation group and can turn negative at L == K).
+inline bool kernel_axis_ok(const Geo& g, int a)
+{
+    return (g.K[a] & 1) || (g.dil[a] == 1 && g.L[a] > g.K[a] && !g.extents);
+}
+
 inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, const void* v, bool allow_stride = false)
 {
     if (dtype != 1 && dtype != 2) return false;                 // f16 / bf16
@@ -485,8 +512,7 @@ inline bool tc_eligible(int dtype, const Geo& g, const void* q, const void* k, c
     if (!(g.scale > 0.0)) return false;
     for (int a = 0; a < g.rank; ++a) {
         if (g.st[a] != 1 && !allow_stride) return false;
-        if ((g.K[a] & 1) == 0) return false;                    // even kernels: SIMT path
-        if (g.extents && g.dil[a] != 1) return false;
+        if (!kernel_axis_ok(g, a)) return false;
     }
     // heads must be adjacent so that (head, channel) folds into one map dimension
     if (!padded && (g.qs[2] != g.D || g.ks[2] != g.D || g.vs[2] != g.Dv)) return false;

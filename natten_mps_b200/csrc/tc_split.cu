@@ -568,22 +568,11 @@ int launch_apply(const Plan& plan, const CUtensorMap& my, const Geo& g, const vo
 //                 w[query, slot of the key] * x[query]          (QK backward w.r.t. k: w = dlogits, x = q;
 //                                                                 AV backward w.r.t. v: w = attn, x = dout)
 // Rows = a box of 128 keys of one (batch, kv head); columns = chunks of 128 queries of the box of queries
-// that attend to them (the inverse neighbourhood: a contiguous range per axis for odd kernels, unit
+// that attend to them (the inverse neighbourhood: a contiguous range per axis, unit
 // stride), once per query head of the group.  The threads gather w into a dense 16-bit P^T tile in TMEM
 // (lanes of a warp are neighbouring keys, so one load touches one row of w) and acc += P^T X runs on the
 // tensor cores with the X chunk staged by TMA and read MN-major.  The order of accumulation is fixed.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void inv_range(int n, int L, int K, int causal, int& qlo, int& qhi)
-{
-    if (causal) {
-        qlo = n;
-        qhi = n + K - 1 < L - 1 ? n + K - 1 : L - 1;
-    } else {
-        qlo = (n <= K - 1) ? 0 : n - K / 2;
-        qhi = (n >= L - K) ? L - 1 : n + K / 2;
-    }
-}
-
 template <int DH>
 struct SmemG {
     static constexpr int kHalves = DH / 64;
@@ -617,8 +606,8 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     for (int a = 0; a < 3; ++a) {
         const int last = origin[a] + P.tile[a] - 1 < Lp[a] - 1 ? origin[a] + P.tile[a] - 1 : Lp[a] - 1;
         int t, hi;
-        inv_range(origin[a], Lp[a], P.K[a], P.causal[a], boxlo[a], t);
-        inv_range(last, Lp[a], P.K[a], P.causal[a], t, hi);
+        inverse_range(origin[a], Lp[a], P.K[a], P.causal[a], boxlo[a], t, /*exact=*/false);
+        inverse_range(last, Lp[a], P.K[a], P.causal[a], t, hi, /*exact=*/false);
         nc[a] = chunks_along(P, a, hi - boxlo[a] + 1);
         nchunks *= nc[a];
     }
@@ -679,7 +668,7 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             if (kx[a] >= Lp[a]) valid = false;
             pflat = pflat * P.L[a] + (rg[a] + P.dil[a] * kx[a]);
             int qlo, qhi;
-            inv_range(kx[a], Lp[a], P.K[a], P.causal[a], qlo, qhi);
+            inverse_range(kx[a], Lp[a], P.K[a], P.causal[a], qlo, qhi);
             f[a] = qlo - boxlo[a];
             e[a] = qhi + 1 - boxlo[a];
         }
@@ -833,7 +822,7 @@ int tc_scores(int dtype, const Geo& g, const void* x, const long long xs[3], con
     if (g.D != 64 && g.D != 128) return -2;
     if (g.extents || g.n_extra) return -2;
     for (int a = 0; a < g.rank; ++a)
-        if ((g.K[a] & 1) == 0) return -2;
+        if (!kernel_axis_ok(g, a)) return -2;
     if (xs[2] != g.D || ys[2] != g.D) return -2;
     const long long strs[4] = {xs[0], xs[1], ys[0], ys[1]};
     for (long long st : strs)
@@ -870,7 +859,7 @@ int tc_apply(int dtype, const Geo& g, const void* w, const void* y, const long l
     if (g.D != 64 && g.D != 128) return -2;
     if (g.extents || g.n_extra) return -2;
     for (int a = 0; a < g.rank; ++a) {
-        if ((g.K[a] & 1) == 0) return -2;
+        if (!kernel_axis_ok(g, a)) return -2;
         if (out_by_position && g.st[a] != 1) return -2;
     }
     if (ys[2] != g.D || ys[0] % 8 != 0 || ys[1] % 8 != 0) return -2;
@@ -903,7 +892,7 @@ int tc_gather(int dtype, const Geo& g, const void* w, const void* x, const long 
     if (g.D != 64 && g.D != 128) return -2;
     if (g.extents || g.n_extra) return -2;
     for (int a = 0; a < g.rank; ++a)
-        if ((g.K[a] & 1) == 0 || g.st[a] != 1) return -2;
+        if (!kernel_axis_ok(g, a) || g.st[a] != 1) return -2;
     if (xs[2] != g.D || xs[0] % 8 != 0 || xs[1] % 8 != 0) return -2;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dst)) & 15u) return -2;
     if (g.Hkv > 65535 || g.B > 65535) return -2;

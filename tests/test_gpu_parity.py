@@ -107,6 +107,10 @@ RANDOM_CASES = [
     (3, (6, 10, 9), 1, 4, 2, 64, 64, dict(kernel_size=(3, 5, 5), is_causal=(True, False, False)), 0, None),
     (3, (5, 8, 8), 1, 2, 2, 200, 200, dict(kernel_size=3, dilation=(1, 2, 2)), 0, None),
     (2, (12, 12), 1, 2, 2, 64, 64, dict(kernel_size=(4, 6)), 0, None),              # even kernels
+    (1, (150,), 2, 4, 2, 64, 64, dict(kernel_size=12), 0, None),
+    (3, (5, 12, 14), 1, 2, 2, 64, 64, dict(kernel_size=(2, 4, 6), is_causal=(True, False, False)), 0, None),
+    (2, (22, 26), 3, 4, 2, 64, 64, dict(kernel_size=5, dilation=2), 0, [[22, 26], [10, 15], [13, 10]]),   # varlen + dilation
+    (1, (90,), 2, 2, 2, 128, 128, dict(kernel_size=7, dilation=3), 0, [[90], [21]]),
     (2, (28, 28), 2, 4, 2, 32, 32, dict(kernel_size=7), 2, None),                   # head dim 32: padded tensor-core path
     (1, (200,), 2, 4, 4, 96, 96, dict(kernel_size=15, dilation=2), 0, None),        # head dim 96
 ]

@@ -24,6 +24,16 @@ CASES = [
     ((6, 20, 18), 1, 2, 2, (3, 7, 7), (1, 1, 1), (True, False, False), None),
     ((5, 9, 11), 1, 2, 1, (3, 3, 5), (1, 2, 1), (False, False, False), None),
     ((8, 12, 12), 2, 1, 1, (3, 5, 5), (1, 1, 1), (False, False, False), [[8, 12, 12], [4, 7, 9]]),
+    # even kernel sizes: the clamped window stops one short of the last key; the last key has no query
+    ((40, 36), 1, 2, 2, (4, 6), (1, 1), (False, False), None),
+    ((26, 33), 2, 2, 1, (8, 5), (1, 2), (False, False), None),          # even on the undilated axis only
+    ((200,), 2, 2, 2, (32,), (1,), (False,), None),
+    ((9, 9), 1, 1, 1, (8, 8), (1, 1), (False, False), None),            # L = K + 1
+    ((6, 14, 20), 1, 2, 2, (2, 4, 6), (1, 1, 1), (True, False, False), None),
+    # per-sample extents together with dilation
+    ((30, 28), 3, 2, 2, (5, 5), (2, 2), (False, False), [[30, 28], [11, 17], [10, 10]]),
+    ((400,), 3, 2, 1, (15,), (2,), (False,), [[400], [61], [233]]),
+    ((8, 14, 12), 2, 1, 1, (3, 3, 5), (2, 1, 2), (False, False, False), [[8, 14, 12], [6, 7, 10]]),
     # head dim 128 (ninth field)
     ((40, 24), 1, 2, 1, (7, 7), (1, 1), (False, False), None, 128),
     ((600,), 2, 4, 1, (255,), (1,), (False,), [[600], [300]], 128),
@@ -233,6 +243,8 @@ SPLIT_CASES = [
     ((260,), 1, 2, 2, (63,), (1,), (1,), (True,), 128),
     ((6, 20, 18), 1, 2, 2, (3, 7, 7), (1, 1, 1), (1, 1, 1), (True, False, False), 64),     # 147 slots
     ((5, 9, 11), 1, 2, 1, (3, 3, 5), (1, 2, 1), (1, 1, 1), (False, False, False), 128),
+    ((30, 22), 1, 2, 2, (6, 4), (1, 1), (1, 1), (False, False), 64),            # even kernels
+    ((120,), 2, 2, 1, (16,), (1,), (1,), (False,), 64),
 ]
 
 
