@@ -28,6 +28,10 @@
 
 #include <type_traits>
 
+#ifndef NATTEN_ABL
+#define NATTEN_ABL 0
+#endif
+
 namespace natten {
 
 using namespace tc;
@@ -52,9 +56,9 @@ __device__ long long g_trace_bwd[2 * 16 * 512];
 namespace {
 
 constexpr int kCols = 64;                   // columns per chunk
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kComputeWarps = 8;
-constexpr int kThreads = (kComputeWarps + 2) * 32;
+constexpr int kThreads = (kComputeWarps + 3) * 32;    // + MMA issue, helper (tables, statistics), loader
 constexpr uint32_t kColS = 0, kColDP = 64, kColA1 = 128;   // acc2 follows acc1 (64 or 128 columns each)
 constexpr int kRowHalf = kTileRows * 128;   // bytes of one [128 x 64] 16-bit block of a row tile
 constexpr int kColHalf = kCols * 128;       // bytes of one [64 x 64] 16-bit block of a column tile
@@ -72,7 +76,8 @@ struct SmemB {
     static constexpr int kTab = kStats + kStages * 512;         // [2] row tables: 128 x RowEntry, then a TileHead
     static constexpr int kTabBytes = 128 * 32 + 64;
     static constexpr int kBar = kTab + 2 * kTabBytes;
-    static constexpr int kTotal = kBar + 256;
+    static constexpr int kStage = kBar + 256;                    // [kComputeWarps] 32 rows x 64 bytes: output staging
+    static constexpr int kTotal = kStage + kComputeWarps * 2048;
     static constexpr uint32_t kTmemCols = DH == 64 ? 256 : 512;
     static constexpr uint32_t kColA2 = kColA1 + DH;
 };
@@ -99,7 +104,9 @@ struct __align__(16) RowEntry {
 static_assert(sizeof(RowEntry) == 32, "row table entries are 32 bytes");
 struct TileHead {
     int active, total, nbox, nc[3];
+    int nchunks, boxlo[3], Lp[3];      // for the MMA warp: chunks of the column box, its origin, sub-grid extents
 };
+static_assert(sizeof(TileHead) <= 64, "the tile head has 64 bytes behind the row table");
 
 template <bool kKeySide>
 __device__ __forceinline__ void bwd_tile_setup(const TcParams& P, unsigned work, BwdTile& T)
@@ -160,8 +167,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
 
     // ---- shared memory, barriers, TMEM --------------------------------------
     const uint32_t sbase = smem_u32(smem);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kBar + 160);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Smem::kBar + 168);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kBar + 192);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Smem::kBar + 200);
     const uint32_t bar_row = sbase + Smem::kBar + 0;          // row tiles landed
     const uint32_t bar_col = sbase + Smem::kBar + 8;          // [kStages] C1, C2 landed
     const uint32_t bar_stats = sbase + Smem::kBar + 40;       // [kStages] column lse / delta staged
@@ -170,7 +177,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     const uint32_t bar_acc = sbase + Smem::kBar + 88;         // accumulating MMAs of the chunk finished
     const uint32_t bar_free = sbase + Smem::kBar + 96;        // [kStages] the same, per stage (for the statistics warp)
     const uint32_t bar_tab_full = sbase + Smem::kBar + 128;   // [2] row table written
-    const uint32_t bar_tab_empty = sbase + Smem::kBar + 144;  // [2] row table read by every compute thread
+    const uint32_t bar_tab_empty = sbase + Smem::kBar + 144;  // [2] row table read by every compute thread and the MMA warp
+    const uint32_t bar_rowfree = sbase + Smem::kBar + 176;    // every S / dP product of the tile finished: the row tiles are free
     float* stats = reinterpret_cast<float*>(smem + Smem::kStats);
 
     if (warp == kComputeWarps) {
@@ -180,12 +188,13 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             for (int s = 0; s < kStages; ++s) {
                 mbar_init(bar_col + 8 * s, 1);
                 mbar_init(bar_stats + 8 * s, 32);
-                mbar_init(bar_free + 8 * s, 1);
+                mbar_init(bar_free + 8 * s, 2);
             }
-            mbar_init(bar_s, 1);
+            mbar_init(bar_s, 2);                 // one commit per MMA stream
             mbar_init(bar_sp, kComputeWarps * 32);
-            mbar_init(bar_acc, 1);
-            for (int i = 0; i < 2; ++i) { mbar_init(bar_tab_full + 8 * i, 32); mbar_init(bar_tab_empty + 8 * i, kComputeWarps * 32); }
+            mbar_init(bar_acc, 2);
+            for (int i = 0; i < 2; ++i) { mbar_init(bar_tab_full + 8 * i, 32); mbar_init(bar_tab_empty + 8 * i, kComputeWarps * 32 + 2); }
+            mbar_init(bar_rowfree, 2);
             mbar_init_fence();
             fence_async_smem();
         }
@@ -206,163 +215,105 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         return w;
     };
 
-    if (warp == kComputeWarps) {
+    if (warp == kComputeWarps || warp == kComputeWarps + 2) {
         // =====================================================================
-        // TMA + MMA issue (one thread)
+        // MMA issue: one thread in each of two warps.  A single thread gets a tcgen05.mma out every ~65
+        // cycles whatever its N, so the chunk's products are split into two independent streams:
+        //   first  (warp 8):  acc1 += dS x C1   then   dP(next) = R2 x C2^T     (both touch the dP columns)
+        //   second (warp 10): acc2 += P x C2    then   S(next)  = R1 x C1^T     (both touch the S columns; acc2 on
+        //                                                                        the key side only)
+        // Each stream is ordered by its own issue order; the streams share no TMEM columns.  Every barrier that
+        // tracks the products takes one commit from each stream.
         // =====================================================================
-        if (lane == 0 && !*abort_flag) {
+        // The whole warp runs the loop (warp-uniform code); the tensor-core instructions execute on one elected lane.
+        const uint32_t leader = elect_one();
+        if (!*abort_flag) {
+            const bool second = warp != kComputeWarps;
             constexpr uint32_t idesc_kk = instr_desc(BF16 ? 1 : 0, kCols, 0, 0);    // both operands K-major
             constexpr uint32_t idesc_acc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A from TMEM, B MN-major
-            const uint64_t dR1 = smem_desc(sbase + Smem::kR1, 16, 1024), dR2 = smem_desc(sbase + Smem::kR2, 16, 1024);
-            auto issue_s_dp = [&](unsigned g, int cc, const BwdTile& X) {
+            const uint64_t dR = smem_desc(sbase + (second ? Smem::kR1 : Smem::kR2), 16, 1024);
+            const uint32_t col_tiles = second ? Smem::kC1 : Smem::kC2;             // column tiles of this stream's S / dP
+            const uint32_t acc_tiles = second ? Smem::kC2 : Smem::kC1;             // ... and of its accumulating product
+            const uint32_t col_out = second ? kColS : kColDP;                      // TMEM columns of S | dP (and of P | dS)
+            const bool has_acc = !second || kKeySide;
+            auto issue_s_dp = [&](unsigned g, int cc, const TileHead& X) {
                 const int s = g % kStages;
-                if (P.extents && cc < X.nbox) {      // rows of the column tiles past the sample's extent -> zeros
+                if (P.extents && cc < X.nbox) {      // rows of the column tile past the sample's extent -> zeros
                     int r = cc % X.nchunks;
                     const int c2 = r % X.nc[2]; r /= X.nc[2];
                     const int c1 = r % X.nc[1], c0 = r / X.nc[1];
-                    const int box0[3] = {X.boxlo[0] + c0 * P.cb[0], X.boxlo[1] + c1 * P.cb[1], X.boxlo[2] + c2 * P.cb[2]};
-                    zero_rows_past_extent(P, box0, X.Lp, kCols, Smem::kHalves, kColHalf,
-                                          smem + Smem::kC1 + s * kColTile, smem + Smem::kC2 + s * kColTile);
+                    const int box0[3] = {X.boxlo[0] + chunk_coord(P, 0, c0, 0), X.boxlo[1] + chunk_coord(P, 1, c1, 0),
+                                         X.boxlo[2] + chunk_coord(P, 2, c2, 0)};
+                    uint8_t* tile = smem + col_tiles + s * kColTile;     // the other stream zeroes the other tile
+                    if (leader) zero_rows_past_extent(P, box0, X.Lp, kCols, Smem::kHalves, kColHalf, tile, tile);
+                    __syncwarp();
                 }
-                const uint64_t dC1 = smem_desc(sbase + Smem::kC1 + s * kColTile, 16, 1024);
-                const uint64_t dC2 = smem_desc(sbase + Smem::kC2 + s * kColTile, 16, 1024);
+                const uint64_t dC = smem_desc(sbase + col_tiles + s * kColTile, 16, 1024);
                 tc_fence_after();
                 // 32 bytes per k-step inside a 64-channel block; blocks are kRowHalf / kColHalf apart
 #pragma unroll
                 for (int ks = 0; ks < DH / 16; ++ks)
-                    mma_ss(tmem + kColS, dR1 + (((ks / 4) * kRowHalf + (ks % 4) * 32) >> 4),
-                           dC1 + (((ks / 4) * kColHalf + (ks % 4) * 32) >> 4), idesc_kk, ks > 0);
-#pragma unroll
-                for (int ks = 0; ks < DH / 16; ++ks)
-                    mma_ss(tmem + kColDP, dR2 + (((ks / 4) * kRowHalf + (ks % 4) * 32) >> 4),
-                           dC2 + (((ks / 4) * kColHalf + (ks % 4) * 32) >> 4), idesc_kk, ks > 0);
-                mma_commit(bar_s);
+                    mma_ss_e(tmem + col_out, dR + (((ks / 4) * kRowHalf + (ks % 4) * 32) >> 4),
+                             dC + (((ks / 4) * kColHalf + (ks % 4) * 32) >> 4), idesc_kk, ks > 0, leader);
+                mma_commit_e(bar_s, leader);
+                if (cc + 1 == X.total) mma_commit_e(bar_rowfree, leader);      // the tile's last read of this stream's row tile
             };
-            // k-step ks covers columns 16*ks..16*ks+15 of the chunk; their 16-bit pairs sit in the
-            // first 16 TMEM columns of the 32-column piece they came from.  The column tile is read
-            // MN-major: 16 rows (2048 bytes) per k-step, the second 64-channel block kColHalf further.
+            // k-step ks covers columns 16*ks..16*ks+15 of the chunk; their 16-bit pairs sit in the first 8 of
+            // those columns (16-column inner rows) or in the first 16 TMEM columns of the 32-column piece
+            // they came from.  The column tile is read MN-major: 16 rows (2048 bytes) per k-step, the second
+            // 64-channel block kColHalf further.
+            auto pair_col = [](int ks) { return kInner == 16 ? 16 * ks : 32 * (ks / 2) + 8 * (ks % 2); };
             auto issue_acc = [&](unsigned g, bool accumulate) {
                 const int s = g % kStages;
-                const uint64_t dC1 = smem_desc(sbase + Smem::kC1 + s * kColTile, kColHalf, 1024);
-                const uint64_t dC2 = smem_desc(sbase + Smem::kC2 + s * kColTile, kColHalf, 1024);
-                tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < kCols / 16; ++ks)
-                    mma_ts(tmem + kColA1, tmem + kColDP + 32 * (ks / 2) + 8 * (ks % 2), dC1 + 128 * ks, idesc_acc,
-                           (accumulate || ks > 0) ? 1u : 0u);
-                if (kKeySide) {
+                if (has_acc) {
+                    const uint64_t dC = smem_desc(sbase + acc_tiles + s * kColTile, kColHalf, 1024);
+                    tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < kCols / 16; ++ks)
-                        mma_ts(tmem + kColA2, tmem + kColS + 32 * (ks / 2) + 8 * (ks % 2), dC2 + 128 * ks, idesc_acc,
-                               (accumulate || ks > 0) ? 1u : 0u);
+                        mma_ts_e(tmem + (second ? kColA2 : kColA1), tmem + col_out + pair_col(ks), dC + 128 * ks, idesc_acc,
+                                 (accumulate || ks > 0) ? 1u : 0u, leader);
                 }
-                mma_commit(bar_acc);
-                if (kKeySide) mma_commit(bar_free + 8 * s);
-            };
-            auto issue_rows = [&](const BwdTile& X) {
-                const int hx = X.hy * DH;
-                mbar_expect_tx(bar_row, 2 * kTile);
-#pragma unroll
-                for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                    tma_load_heads(sbase + Smem::kR1 + hf * kRowHalf, &tmR1, bar_row, P, DH, hx + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
-                                X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
-                    tma_load_heads(sbase + Smem::kR2 + hf * kRowHalf, &tmR2, bar_row, P, DH, hx + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
-                                X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
-                }
-            };
-            auto prefetch_rows = [&](const BwdTile& X) {
-#pragma unroll
-                for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                    tma_prefetch_heads(&tmR1, P, DH, X.hy * DH + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
-                                       X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
-                    tma_prefetch_heads(&tmR2, P, DH, X.hy * DH + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
-                                       X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
-                }
-            };
-            // Column loads run ahead of the MMAs, across tiles: their own cursor.
-            BwdTile Tl;
-            unsigned wl = next_active(blockIdx.x, Tl), loaded = 0;
-            int ld[3] = {0, 0, 0}, ld_head = 0, ld_in_tile = 0;
-            auto issue_cols = [&]() {
-                if (wl >= nwork) return;
-                const int s = loaded % kStages;
-                const uint32_t bar = bar_col + 8 * s;
-                mbar_expect_tx(bar, 2 * kColTile);
-                const int head_kv = kKeySide ? Tl.hy : Tl.hy / P.group;
-                if (ld_in_tile < Tl.nbox) {
-                    int X[3];
-#pragma unroll
-                    for (int a = 0; a < 3; ++a) X[a] = Tl.rg[a] + P.dil[a] * (Tl.boxlo[a] + ld[a] * P.cb[a]);
-                    // query side: columns are keys (kv head); key side: columns are queries (query head)
-                    const int hx = (kKeySide ? Tl.hy * P.group + ld_head : head_kv) * DH;
-#pragma unroll
-                    for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                        tma_load_heads(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmC1, bar, P, DH, hx + 64 * hf, X[2], X[1], X[0], Tl.b);
-                        tma_load_heads(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmC2, bar, P, DH, hx + 64 * hf, X[2], X[1], X[0], Tl.b);
-                    }
-                    if (++ld[2] == Tl.nc[2]) { ld[2] = 0; if (++ld[1] == Tl.nc[1]) { ld[1] = 0; if (++ld[0] == Tl.nc[0]) { ld[0] = 0; ++ld_head; } } }
-                } else {                                 // additional tokens (rows past n_extra are zero-filled)
-                    const int e0 = (ld_in_tile - Tl.nbox) * kCols;
-#pragma unroll
-                    for (int hf = 0; hf < Smem::kHalves; ++hf) {
-                        tma_load_heads(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmE1, bar, P, DH, head_kv * DH + 64 * hf, e0, 0, 0, Tl.b);
-                        tma_load_heads(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmE2, bar, P, DH, head_kv * DH + 64 * hf, e0, 0, 0, Tl.b);
-                    }
-                }
-                ++loaded;
-                if (++ld_in_tile == Tl.total) {
-                    wl = next_active(wl + gridDim.x, Tl);
-                    ld[0] = ld[1] = ld[2] = 0; ld_head = 0; ld_in_tile = 0;
-                }
+                mma_commit_e(bar_acc, leader);
+                mma_commit_e(bar_free + 8 * s, leader);        // the stage's column tiles (and statistics) may be replaced
             };
 
-            BwdTile T, Tn;
-            unsigned work = next_active(blockIdx.x, T);
-            if (work < nwork) {
-                issue_rows(T);
-                for (int i = 0; i < kStages; ++i) issue_cols();
-            }
-            unsigned g = 0, tileno = 0;
+            unsigned g = 0, tileno = 0, item = 0;
             bool ok = true;
-            while (work < nwork && ok) {
+            for (unsigned work = blockIdx.x; work < nwork && ok; work += gridDim.x, ++item) {
+                const unsigned slot = item & 1;
+                ok = mbar_wait(bar_tab_full + 8 * slot, (item >> 1) & 1, abort_flag, P.wait_budget);
+                if (!ok) break;
+                const TileHead T = *reinterpret_cast<const TileHead*>(smem + Smem::kTab + slot * Smem::kTabBytes + 128 * 32);
+                __syncwarp();                    // every lane has read the head
+                if (leader) mbar_arrive(bar_tab_empty + 8 * slot);
+                if (!T.active) continue;
                 ok = mbar_wait(bar_row, tileno & 1, abort_flag, P.wait_budget) &&
                      mbar_wait(bar_col + 8 * (g % kStages), (g / kStages) & 1, abort_flag, P.wait_budget);
                 if (!ok) break;
                 issue_s_dp(g, 0, T);
-                unsigned wnext = nwork;
                 for (int cc = 0; cc < T.total && ok; ++cc, ++g) {
-                    const bool last = cc + 1 == T.total;
-                    if (cc == 0) {             // while the threads work on the chunk: find the next tile, warm L2 with its rows
-                        wnext = next_active(work + gridDim.x, Tn);
-                        if (wnext < nwork) prefetch_rows(Tn);
-                    }
                     STAMP(200 + cc);
                     ok = mbar_wait(bar_sp, g & 1, abort_flag, P.wait_budget);               // S/dP consumed, P/dS stored
                     if (!ok) break;
                     STAMP(210);
                     issue_acc(g, cc > 0);                                    // reads P/dS ...
-                    if (!last) {
+                    STAMP(215);
+                    if (cc + 1 < T.total) {
                         ok = mbar_wait(bar_col + 8 * ((g + 1) % kStages), ((g + 1) / kStages) & 1, abort_flag, P.wait_budget);
                         if (!ok) break;
+                        STAMP(216);
                         issue_s_dp(g + 1, cc + 1, T);                                // ... before the next S/dP overwrite them
-                    } else if (wnext < nwork) {
-                        issue_rows(Tn);        // every S/dP product of this tile has finished: its rows are free
                     }
                     STAMP(220);
-                    ok = mbar_wait(bar_acc, g & 1, abort_flag, P.wait_budget);              // stage g % kStages is free again
-                    if (!ok) break;
-                    STAMP(230);
-                    issue_cols();
                 }
-                T = Tn;
-                work = wnext;
                 ++tileno;
             }
         }
     } else if (warp == kComputeWarps + 1) {
         // =====================================================================
-        // helper warp: row tables one tile ahead; on the key side also the column statistics
-        // (lse*log2e and delta of the chunk's queries)
+        // helper warp: row tables one tile ahead; the loads (lane 0: row tiles, then the ring of column tiles,
+        // as far ahead of the tensor cores as the stages allow); on the key side also the column statistics
+        // (lse*log2e and delta of the chunk's queries) that go with each column tile
         // =====================================================================
         bool ok = !*abort_flag;
         unsigned g = 0;
@@ -419,12 +370,25 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 hd->active = X.active ? 1 : 0;
                 hd->total = X.total;
                 hd->nbox = X.nbox;
-                hd->nc[0] = X.nc[0]; hd->nc[1] = X.nc[1]; hd->nc[2] = X.nc[2];
+                hd->nchunks = X.nchunks;
+#pragma unroll
+                for (int a = 0; a < 3; ++a) { hd->nc[a] = X.nc[a]; hd->boxlo[a] = X.boxlo[a]; hd->Lp[a] = X.Lp[a]; }
             }
             mbar_arrive(bar_tab_full + 8 * slot);
         };
+        auto issue_rows = [&](const BwdTile& X) {
+            const int hx = X.hy * DH;
+            mbar_expect_tx(bar_row, 2 * kTile);
+#pragma unroll
+            for (int hf = 0; hf < Smem::kHalves; ++hf) {
+                tma_load_heads(sbase + Smem::kR1 + hf * kRowHalf, &tmR1, bar_row, P, DH, hx + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
+                            X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
+                tma_load_heads(sbase + Smem::kR2 + hf * kRowHalf, &tmR2, bar_row, P, DH, hx + 64 * hf, X.rg[2] + P.dil[2] * X.origin[2],
+                            X.rg[1] + P.dil[1] * X.origin[1], X.rg[0] + P.dil[0] * X.origin[0], X.b);
+            }
+        };
         BwdTile T, Tn;
-        unsigned item = 0;
+        unsigned item = 0, tiles = 0;
         if (blockIdx.x < nwork) {
             bwd_tile_setup<kKeySide>(P, blockIdx.x, T);
             write_table(blockIdx.x, 0, T);
@@ -435,11 +399,46 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 bwd_tile_setup<kKeySide>(P, wn, Tn);
                 write_table(wn, item + 1, Tn);
             }
-            if (kKeySide && T.active) {
+            if (T.active) {
+                // the row tiles are free once the previous tile's last S / dP products have finished
+                if (tiles > 0) ok = ok && mbar_wait(bar_rowfree, (tiles - 1) & 1, abort_flag, P.wait_budget);
+                if (lane == 0 && ok) issue_rows(T);
+                ++tiles;
                 int ci[3] = {0, 0, 0}, hc = T.hy * P.group;
+                const int head_kv = kKeySide ? T.hy : T.hy / P.group;
                 for (int cc = 0; cc < T.total; ++cc, ++g) {
                     const int s = g % kStages;
+                    STAMP(400 + cc);
                     if (g >= (unsigned)kStages) ok = ok && mbar_wait(bar_free + 8 * s, ((g / kStages) - 1) & 1, abort_flag, P.wait_budget);
+                    STAMP(410);
+                    if (lane == 0 && ok) {
+                        const uint32_t bar = bar_col + 8 * s;
+                        mbar_expect_tx(bar, 2 * kColTile);
+                        if (cc < T.nbox) {
+                            int X[3];
+#pragma unroll
+                            for (int a = 0; a < 3; ++a) X[a] = T.rg[a] + P.dil[a] * (T.boxlo[a] + chunk_coord(P, a, ci[a], 0));
+                            // query side: columns are keys (kv head); key side: columns are queries (query head)
+                            const int hx = (kKeySide ? hc : head_kv) * DH;
+#pragma unroll
+                            for (int hf = 0; hf < Smem::kHalves; ++hf) {
+                                tma_load_heads(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmC1, bar, P, DH, hx + 64 * hf, X[2], X[1], X[0], T.b);
+                                tma_load_heads(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmC2, bar, P, DH, hx + 64 * hf, X[2], X[1], X[0], T.b);
+                            }
+                        } else {                             // additional tokens (rows past n_extra are zero-filled)
+                            const int e0 = (cc - T.nbox) * kCols;
+#pragma unroll
+                            for (int hf = 0; hf < Smem::kHalves; ++hf) {
+                                tma_load_heads(sbase + Smem::kC1 + s * kColTile + hf * kColHalf, &tmE1, bar, P, DH, head_kv * DH + 64 * hf, e0, 0, 0, T.b);
+                                tma_load_heads(sbase + Smem::kC2 + s * kColTile + hf * kColHalf, &tmE2, bar, P, DH, head_kv * DH + 64 * hf, e0, 0, 0, T.b);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (!kKeySide) {
+                        if (cc < T.nbox && ++ci[2] == T.nc[2]) { ci[2] = 0; if (++ci[1] == T.nc[1]) { ci[1] = 0; ++ci[0]; } }
+                        continue;
+                    }
                     float* st = stats + s * 128;
 #pragma unroll
                     for (int k = 0; k < kCols / 32; ++k) {
@@ -447,9 +446,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                         const int j2 = j & (P.cb[2] - 1);
                         const int j1 = (j >> P.cb2_log) & (P.cb[1] - 1);
                         const int j0 = j >> (P.cb2_log + P.cb1_log);
-                        const int q0 = T.boxlo[0] + ci[0] * P.cb[0] + j0;
-                        const int q1 = T.boxlo[1] + ci[1] * P.cb[1] + j1;
-                        const int q2 = T.boxlo[2] + ci[2] * P.cb[2] + j2;
+                        const int q0 = T.boxlo[0] + chunk_coord(P, 0, ci[0], j0);
+                        const int q1 = T.boxlo[1] + chunk_coord(P, 1, ci[1], j1);
+                        const int q2 = T.boxlo[2] + chunk_coord(P, 2, ci[2], j2);
                         const bool inside = ok && q0 >= 0 && q0 < T.Lp[0] && q1 >= 0 && q1 < T.Lp[1] && q2 >= 0 && q2 < T.Lp[2];
                         float l2 = 0.f, dl = 0.f;
                         if (inside) {
@@ -476,7 +475,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         bool ok = true;
         unsigned g = 0;                          // chunks processed so far (all tiles)
         constexpr int kPairs = kInner > 0 ? kInner / 2 : 1;
-        constexpr int kRows = kInner > 0 ? 32 / kInner : 1;
         unsigned item = 0;
         for (unsigned work = blockIdx.x; work < nwork; work += gridDim.x, ++item) {
             // ---- this thread's row, from the helper warp's table ----
@@ -504,59 +502,84 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 continue;
             }
             const int nbox = T.nbox;
+            // Chunk columns of this warp's half h, and where its 16-bit pairs go.  With 16-column inner rows a
+            // chunk is four rows: the warp takes rows piece and piece + 2, so that the two warps of a lane
+            // quadrant share a row's window evenly when the chunk rows are interleaved; the pairs of a row
+            // overwrite the first 8 of its own 16 columns.  Otherwise the warp takes 32 adjacent columns whose
+            // pairs fill the first 16 of them.
+            auto col0 = [&](int h) { return kInner == 16 ? 16 * (piece + 2 * h) : 32 * piece + 16 * h; };
+            auto dst0 = [&](int h) { return kInner == 16 ? 16 * (piece + 2 * h) : 32 * piece + 8 * h; };
             int ci[3] = {0, 0, 0};               // chunk index per axis, advanced without divisions
             uint32_t colmask[kPairs];            // separable geometry: 16-bit lane masks per column pair
             bool cols_any = false;
             int cached_c2 = -1;
             for (int cc = 0; cc < T.total; ++cc, ++g) {
-                // ---- validity of this warp's 32 columns for this thread's row ----
-                uint32_t word = 0u;                  // generic geometry: one bit per column
-                uint32_t rowmask[kRows];             // separable geometry: all-ones / zero per inner row
-                bool mine = false;
+                // ---- validity of this warp's two 16-column halves for this thread's row ----
+                // half h covers chunk columns col0(h) .. col0(h)+15; bits [16h, 16h+16) of `word` belong to it
+                uint32_t word = 0u;                  // generic geometry / additional tokens: one bit per column
+                uint32_t rowmask[2] = {0u, 0u};      // separable geometry: all-ones / zero per inner row
+                bool mine[2] = {false, false};
                 const bool extra = !kKeySide && cc >= nbox;      // additional tokens: first n_extra columns, every live row
                 if (extra) {
-                    word = valid_row ? low_bits(P.n_extra - ((cc - nbox) * kCols + 32 * piece)) : 0u;
-                    mine = word != 0u;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t w = valid_row ? (low_bits(P.n_extra - ((cc - nbox) * kCols + col0(h))) & 0xFFFFu) : 0u;
+                        word |= w << (16 * h);
+                        mine[h] = w != 0u;
+                    }
                 } else if (kInner > 0) {
+                    // columns of this chunk inside the row's window, per axis (chunks may be interleaved)
                     if (ci[2] != cached_c2) {        // the column masks only change with the innermost chunk index
                         cached_c2 = ci[2];
-                        const int lo2 = f[2] - ci[2] * kInner, hi2 = e[2] - ci[2] * kInner;
+                        int lo2, hi2;
+                        chunk_range(P, 2, ci[2], f[2], e[2], lo2, hi2);
 #pragma unroll
                         for (int i = 0; i < kPairs; ++i)
                             colmask[i] = ((2 * i >= lo2 && 2 * i < hi2) ? 0x0000FFFFu : 0u) |
                                          ((2 * i + 1 >= lo2 && 2 * i + 1 < hi2) ? 0xFFFF0000u : 0u);
-                        cols_any = hi2 > 0 && lo2 < kInner && hi2 > lo2;
+                        cols_any = hi2 > lo2;
                     }
+                    int lo0, hi0, lo1, hi1;
+                    chunk_range(P, 0, ci[0], f[0], e[0], lo0, hi0);
+                    chunk_range(P, 1, ci[1], f[1], e[1], lo1, hi1);
 #pragma unroll
-                    for (int t = 0; t < kRows; ++t) {
-                        const int jj = 32 * piece + t * kInner;
+                    for (int h = 0; h < 2; ++h) {
+                        const int jj = col0(h);
                         const int j1 = (jj >> P.cb2_log) & (P.cb[1] - 1);
                         const int j0 = jj >> (P.cb2_log + P.cb1_log);
-                        const int i0 = ci[0] * P.cb[0] + j0, i1 = ci[1] * P.cb[1] + j1;
-                        const bool rok = i0 >= f[0] && i0 < e[0] && i1 >= f[1] && i1 < e[1];
-                        rowmask[t] = rok ? 0xFFFFFFFFu : 0u;
-                        mine = mine || (rok && cols_any);
+                        const bool rok = j0 >= lo0 && j0 < hi0 && j1 >= lo1 && j1 < hi1;
+                        rowmask[h] = rok ? 0xFFFFFFFFu : 0u;
+                        mine[h] = rok && cols_any;
                     }
                 } else {
-                    word = piece_word(P, ci, piece, f, e);
-                    mine = word != 0u;
+                    int jl[3], jh[3];
+#pragma unroll
+                    for (int a = 0; a < 3; ++a) chunk_range(P, a, ci[a], f[a], e[a], jl[a], jh[a]);
+                    word = piece_word_ranges(P, piece, jl, jh);
+                    mine[0] = (word & 0xFFFFu) != 0u;
+                    mine[1] = (word >> 16) != 0u;
                 }
-                const bool any = __any_sync(0xffffffffu, mine);
+#if NATTEN_ABL == 2
+                const bool any[2] = {false, false};
+#else
+                const bool any[2] = {__any_sync(0xffffffffu, mine[0]), __any_sync(0xffffffffu, mine[1])};
+#endif
                 const bool separable = kInner > 0 && !extra;
                 const bool full = !separable && __all_sync(0xffffffffu, word == 0xffffffffu);
-                STAMP(310 + (any ? 1 : 0));
+                STAMP(310 + ((any[0] || any[1]) ? 1 : 0));
                 ok = ok && mbar_wait(bar_s, g & 1, abort_flag, P.wait_budget);      // also: the previous chunk's P/dS were consumed
                 if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (g % kStages), (g / kStages) & 1, abort_flag, P.wait_budget);
                 tc_fence_after();
                 STAMP(320);
-                if (any) {
-                    const float* stp = stats + (g % kStages) * 128 + 32 * piece;
-                    const float4* st4 = reinterpret_cast<const float4*>(stp);
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {               // 16 columns at a time
-                        uint32_t s[16], dp[16], pk_p[8], pk_ds[8];
-                        tmem_ld16(trow + kColS + 32 * piece + 16 * half, s);
-                        tmem_ld16(trow + kColDP + 32 * piece + 16 * half, dp);
+                for (int half = 0; half < 2; ++half) {               // 16 columns at a time
+                    uint32_t pk_p[8], pk_ds[8];
+                    if (any[half]) {
+                        const float* stp = stats + (g % kStages) * 128 + col0(half);
+                        const float4* st4 = reinterpret_cast<const float4*>(stp);
+                        uint32_t s[16], dp[16];
+                        tmem_ld16(trow + kColS + col0(half), s);
+                        tmem_ld16(trow + kColDP + col0(half), dp);
                         tmem_ld_wait();
                         if (separable || full) {
                             // P = 2^(s*c - lse2), dS = P * (dP*scale - delta*scale); fp32, rounded once each
@@ -564,7 +587,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                             for (int g4 = 0; g4 < 4; ++g4) {             // four columns at a time
                                 float nl[4], nd[4];
                                 if (kKeySide) {
-                                    const float4 a = st4[4 * half + g4], d = st4[kCols / 4 + 4 * half + g4];
+                                    const float4 a = st4[g4], d = st4[kCols / 4 + g4];
                                     nl[0] = a.x; nl[1] = a.y; nl[2] = a.z; nl[3] = a.w;
                                     nd[0] = d.x; nd[1] = d.y; nd[2] = d.z; nd[3] = d.w;
                                 } else {
@@ -574,32 +597,30 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
 #pragma unroll
                                 for (int h2 = 0; h2 < 2; ++h2) {
                                     const int pl = 2 * g4 + h2, j = 2 * pl;      // pair / column inside the half
-                                    const int pi = 8 * half + pl;                // pair inside the piece
                                     const float x0 = fmaf(__uint_as_float(s[j]), P.scale_log2, nl[2 * h2]);
                                     const float x1 = fmaf(__uint_as_float(s[j + 1]), P.scale_log2, nl[2 * h2 + 1]);
                                     const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                                     const float g0 = fmaf(__uint_as_float(dp[j]), P.scale, nd[2 * h2]);
                                     const float g1 = fmaf(__uint_as_float(dp[j + 1]), P.scale, nd[2 * h2 + 1]);
                                     uint32_t dd = cvt_pack<BF16>(p0 * g0, p1 * g1);
-                                    if (separable) dd = dd & colmask[pi % kPairs] & rowmask[pi / kPairs];
+                                    if (separable) dd = dd & colmask[(8 * half + pl) % kPairs] & rowmask[kInner == 16 ? half : 0];
                                     pk_ds[pl] = dd;
                                     if (kKeySide) {
                                         uint32_t pp = cvt_pack<BF16>(p0, p1);
-                                        if (separable) pp = pp & colmask[pi % kPairs] & rowmask[pi / kPairs];
+                                        if (separable) pp = pp & colmask[(8 * half + pl) % kPairs] & rowmask[kInner == 16 ? half : 0];
                                         pk_p[pl] = pp;
                                     }
                                 }
                             }
                         } else {
-                            const float* st = stp + 16 * half;
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
                                 float pv[2], dsv[2];
 #pragma unroll
                                 for (int u = 0; u < 2; ++u) {
                                     const int j = 2 * i + u;
-                                    const float nl = kKeySide ? st[j] : row_lse2;
-                                    const float nd = kKeySide ? st[kCols + j] : row_delta;
+                                    const float nl = kKeySide ? stp[j] : row_lse2;
+                                    const float nd = kKeySide ? stp[kCols + j] : row_delta;
                                     const bool on = (word >> (16 * half + j)) & 1u;
                                     const float p = on ? fast_exp2(fmaf(__uint_as_float(s[j]), P.scale_log2, nl)) : 0.f;
                                     pv[u] = p;
@@ -609,16 +630,13 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                                 pk_ds[i] = pack16(dsv[0], dsv[1], BF16);
                             }
                         }
-                        // the pairs overwrite columns this warp has already read
-                        tmem_st8(trow + kColDP + 32 * piece + 8 * half, pk_ds);
-                        if (kKeySide) tmem_st8(trow + kColS + 32 * piece + 8 * half, pk_p);
-                    }
-                } else {                             // nothing valid here: the MMA must read zeros
-                    uint32_t z[16];
+                    } else {                             // nothing valid in this half: the MMA must read zeros
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) z[i] = 0u;
-                    tmem_st16(trow + kColDP + 32 * piece, z);
-                    if (kKeySide) tmem_st16(trow + kColS + 32 * piece, z);
+                        for (int i = 0; i < 8; ++i) { pk_p[i] = 0u; pk_ds[i] = 0u; }
+                    }
+                    // the pairs overwrite columns this warp has already read (or will not read)
+                    tmem_st8(trow + kColDP + dst0(half), pk_ds);
+                    if (kKeySide) tmem_st8(trow + kColS + dst0(half), pk_p);
                 }
                 tmem_st_wait();
                 tc_fence_before();
@@ -639,8 +657,20 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             ok = ok && mbar_wait(bar_acc, (g - 1) & 1, abort_flag, P.wait_budget);
             tc_fence_after();
             STAMP(350);
-            // The TMEM loads are warp-collective: every lane takes part, only the stores are per row.
+            // The TMEM loads are warp-collective: every lane takes part.  A lane holds 32 channels (64 bytes) of
+            // its own row; the warp passes them through a [32 rows x 64 bytes] block of shared memory so that
+            // four lanes write one row's 64 bytes together: every store instruction fills whole 32-byte sectors
+            // of eight rows instead of touching 32 rows with 16 bytes each.
             const bool live = valid_row && ok;
+            uint8_t* stg = smem + Smem::kStage + warp * 2048;
+            long long row_of[4];                 // output row (or -1) of the rows this lane stores: 8 * i + lane / 4
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int src = 8 * i + (lane >> 2);
+                const long long orow = __shfl_sync(0xffffffffu, out_row, src);
+                const int there = __shfl_sync(0xffffffffu, in_tensor ? 1 : 0, src);
+                row_of[i] = there ? orow : -1;
+            }
 #pragma unroll
             for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
 #pragma unroll
@@ -648,18 +678,26 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                     uint32_t a[32];
                     tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + CH * piece + 32 * part, a);
                     tmem_ld_wait();
-                    if (in_tensor) {
-                        uint4* d4 = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + out_row * P.dreal + piece * CH + 32 * part);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            if (piece * CH + 32 * part + 8 * i >= P.dreal) break;     // padded channels are not part of the output
-                            uint32_t w[4];
+                    for (int c = 0; c < 4; ++c) {        // 16-byte chunks, swizzled against bank conflicts
+                        uint32_t w[4];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                w[j] = live ? pack16(__uint_as_float(a[8 * i + 2 * j]), __uint_as_float(a[8 * i + 2 * j + 1]), BF16) : 0u;
-                            d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
+                        for (int j = 0; j < 4; ++j)
+                            w[j] = live ? pack16(__uint_as_float(a[8 * c + 2 * j]), __uint_as_float(a[8 * c + 2 * j + 1]), BF16) : 0u;
+                        *reinterpret_cast<uint4*>(stg + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
+                    __syncwarp();
+                    const int c = lane & 3;
+                    const int ch0 = piece * CH + 32 * part + 8 * c;          // first channel of this lane's chunk
+                    uint16_t* dst = which == 0 ? out1 : out2;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = 8 * i + (lane >> 2);
+                        const uint4 v = *reinterpret_cast<const uint4*>(stg + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+                        if (row_of[i] >= 0 && ch0 < P.dreal && NATTEN_ABL != 1)          // padded channels are not part of the output
+                            *reinterpret_cast<uint4*>(dst + row_of[i] * P.dreal + ch0) = v;
+                    }
+                    __syncwarp();                        // the block is reused by the next part
                 }
             }
             // the next tile's first accumulating MMA is issued only after every thread has passed here
@@ -783,12 +821,12 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
     using Smem = SmemB<DH>;
     if (!encode_map(&q_tile, q, bf, p, g.Hq, g.D, g.qs, plan.box_q) ||
         !encode_map(&do_tile, dout_k, bf, p, g.Hq, g.D, dos, plan.box_q) ||
-        !encode_map(&k_chunk, k, bf, p, g.Hkv, g.D, g.ks, plan.box_kv) ||
-        !encode_map(&v_chunk, v, bf, p, g.Hkv, g.D, g.vs, plan.box_kv) ||
+        !encode_map(&k_chunk, k, bf, p, g.Hkv, g.D, g.ks, plan.box_kv, false, /*interleaved=*/true) ||
+        !encode_map(&v_chunk, v, bf, p, g.Hkv, g.D, g.vs, plan.box_kv, false, true) ||
         !encode_map(&k_tile, k, bf, p, g.Hkv, g.D, g.ks, plan.box_q) ||
         !encode_map(&v_tile, v, bf, p, g.Hkv, g.D, g.vs, plan.box_q) ||
-        !encode_map(&q_chunk, q, bf, p, g.Hq, g.D, g.qs, plan.box_kv) ||
-        !encode_map(&do_chunk, dout_k, bf, p, g.Hq, g.D, dos, plan.box_kv))
+        !encode_map(&q_chunk, q, bf, p, g.Hq, g.D, g.qs, plan.box_kv, false, true) ||
+        !encode_map(&do_chunk, dout_k, bf, p, g.Hq, g.D, dos, plan.box_kv, false, true))
         return -2;
     ek_chunk = k_chunk; ev_chunk = v_chunk;      // placeholders when there are no additional tokens
     if (g.n_extra > 0 && (!encode_extra_map(&ek_chunk, ek, bf, g.B, g.n_extra, g.Hkv, g.D, kCols, p.split_heads) ||
@@ -881,7 +919,7 @@ int tc_fused_bwd(int dtype, const Geo& g_in, const void* q, const void* k, const
         ex.dout_full = base + 2 * align256(rows_full * 4);
     }
     Plan plan;
-    if (!make_plan(g, plan, kCols)) return -2;
+    if (!make_plan(g, plan, kCols, /*with_stride=*/false, /*interleave=*/true)) return -2;
     plan.p.status = status_ptr();
     if (!plan.p.status) return -2;
     if (g.B == 0) return 0;

@@ -25,6 +25,10 @@
 
 #include <type_traits>
 
+#ifndef NATTEN_ABL
+#define NATTEN_ABL 0
+#endif
+
 namespace natten {
 
 using namespace tc;
@@ -340,6 +344,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!ok) break;
         const FwdTile T = *hdr_slot(t);
         if (T.nch == 0) break;
+        STAMP(290);
         // ---- this thread's query row ----
         int f[3], e[3];
         bool valid_q, in_tensor;
@@ -396,11 +401,20 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int pc = 0; pc < 4; ++pc) {
                 uint32_t pk[8];
                 if (fast) {
+#if NATTEN_ABL == 2
+                    const bool rowok = false;
+#else
                     const bool rowok = ((rowbits >> pc) & 1u) && colbits != 0u;
+#endif
                     if (__any_sync(0xffffffffu, rowok)) {
                         uint32_t s[16];
                         tmem_ld16(trow + kColS + 16 * pc, s);
                         tmem_ld_wait();
+#if NATTEN_ABL == 3
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) pk[i] = s[2 * i] & 1u;
+                        stored |= 1u << pc;
+#else
                         if (m == -INFINITY && rowok) {           // first valid columns of this row: fix the stabiliser
                             float mm = -INFINITY;
 #pragma unroll
@@ -438,6 +452,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         }
                         if (rowok) l += r0 + r1;
                         stored |= 1u << pc;
+#endif
                     } else {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) pk[i] = 0u;
@@ -517,7 +532,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 uint32_t o[32];
                 tmem_ld32(trow + kColO + 32 * part, o);
                 tmem_ld_wait();
-                if (in_tensor) {
+                if (in_tensor && NATTEN_ABL != 1) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         if (32 * part + 8 * i >= P.dreal) break;
