@@ -56,6 +56,7 @@ __device__ long long g_trace_bwd[2 * 16 * 512];
 namespace {
 
 constexpr int kCols = 64;                   // columns per chunk
+constexpr int kAxisEntries = 130;           // entries of a tile's axis table: tile[0] + tile[1] + tile[2] <= 128 + 1 + 1
 constexpr int kStages = 3;
 constexpr int kComputeWarps = 8;
 constexpr int kThreads = (kComputeWarps + 3) * 32;    // + MMA issue, helper (tables, statistics), loader
@@ -73,8 +74,8 @@ struct SmemB {
     static constexpr int kC1 = kR2 + kTile;                     // [kStages]
     static constexpr int kC2 = kC1 + kStages * kColTile;        // [kStages]
     static constexpr int kStats = kC2 + kStages * kColTile;     // [kStages][2][64] float
-    static constexpr int kTab = kStats + kStages * 512;         // [2] row tables: 128 x RowEntry, then a TileHead
-    static constexpr int kTabBytes = 128 * 32 + 64;
+    static constexpr int kTab = kStats + kStages * 512;         // [2] tables: axis entries, then a TileHead
+    static constexpr int kTabBytes = kAxisEntries * 16 + 64;
     static constexpr int kBar = kTab + 2 * kTabBytes;
     static constexpr int kStage = kBar + 256;                    // [kComputeWarps] 32 rows x 64 bytes: output staging
     static constexpr int kTotal = kStage + kComputeWarps * 2048;
@@ -93,20 +94,23 @@ struct BwdTile {
     bool active;
 };
 
-// What a compute thread needs to know about its row of a tile; written one tile ahead by the
-// helper warp (32 bytes per row), so that the compute warps do no geometry of their own.
-struct __align__(16) RowEntry {
-    short f[3], e[3];          // valid column range per axis, relative to the column box
-    int flags;                 // bit 0: row inside the (sub-grid of the) sample, bit 1: row inside the tensor
-    long long out_row;         // row of the output tensors
-    float lse2, delta;         // query side: -lse*log2(e), -delta*scale
+// What a compute thread needs to know about its row of a tile is separable: along every axis the row's
+// coordinate alone decides its position in the tensor, whether it exists, and its valid column range.  The
+// helper warp writes one entry per (axis, coordinate of the tile) one tile ahead, tile[0] + tile[1] + tile[2]
+// entries instead of 128 rows x 3 axes; a compute thread combines the three entries of its row.
+struct __align__(16) AxisEntry {
+    short f, e;                // valid column range along the axis, relative to the column box
+    int pa;                    // position along the axis in the tensor
+    int flags;                 // bit 0: inside the (sub-grid of the) sample, bit 1: inside the tensor
+    int pad;
 };
-static_assert(sizeof(RowEntry) == 32, "row table entries are 32 bytes");
+static_assert(sizeof(AxisEntry) == 16, "axis table entries are 16 bytes");
 struct TileHead {
     int active, total, nbox, nc[3];
-    int nchunks, boxlo[3], Lp[3];      // for the MMA warp: chunks of the column box, its origin, sub-grid extents
+    int nchunks, boxlo[3], Lp[3];      // for the MMA warps: chunks of the column box, its origin, sub-grid extents
+    int b, hy;                         // batch and head of the rows
 };
-static_assert(sizeof(TileHead) <= 64, "the tile head has 64 bytes behind the row table");
+static_assert(sizeof(TileHead) <= 64, "the tile head has 64 bytes behind the axis table");
 
 template <bool kKeySide>
 __device__ __forceinline__ void bwd_tile_setup(const TcParams& P, unsigned work, BwdTile& T)
@@ -174,8 +178,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     const uint32_t bar_stats = sbase + Smem::kBar + 40;       // [kStages] column lse / delta staged
     const uint32_t bar_s = sbase + Smem::kBar + 72;           // S and dP of the chunk are in TMEM
     const uint32_t bar_sp = sbase + Smem::kBar + 80;          // threads consumed S/dP, wrote P/dS
-    const uint32_t bar_acc = sbase + Smem::kBar + 88;         // accumulating MMAs of the chunk finished
-    const uint32_t bar_free = sbase + Smem::kBar + 96;        // [kStages] the same, per stage (for the statistics warp)
+    const uint32_t bar_free = sbase + Smem::kBar + 96;        // [kStages] accumulating MMAs of the stage's chunk finished
     const uint32_t bar_tab_full = sbase + Smem::kBar + 128;   // [2] row table written
     const uint32_t bar_tab_empty = sbase + Smem::kBar + 144;  // [2] row table read by every compute thread and the MMA warp
     const uint32_t bar_rowfree = sbase + Smem::kBar + 176;    // every S / dP product of the tile finished: the row tiles are free
@@ -188,11 +191,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             for (int s = 0; s < kStages; ++s) {
                 mbar_init(bar_col + 8 * s, 1);
                 mbar_init(bar_stats + 8 * s, 32);
-                mbar_init(bar_free + 8 * s, 2);
+                mbar_init(bar_free + 8 * s, kKeySide ? 2 : 1);      // one commit per MMA stream that accumulates
             }
             mbar_init(bar_s, 2);                 // one commit per MMA stream
             mbar_init(bar_sp, kComputeWarps * 32);
-            mbar_init(bar_acc, 2);
             for (int i = 0; i < 2; ++i) { mbar_init(bar_tab_full + 8 * i, 32); mbar_init(bar_tab_empty + 8 * i, kComputeWarps * 32 + 2); }
             mbar_init(bar_rowfree, 2);
             mbar_init_fence();
@@ -273,8 +275,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                         mma_ts_e(tmem + (second ? kColA2 : kColA1), tmem + col_out + pair_col(ks), dC + 128 * ks, idesc_acc,
                                  (accumulate || ks > 0) ? 1u : 0u, leader);
                 }
-                mma_commit_e(bar_acc, leader);
-                mma_commit_e(bar_free + 8 * s, leader);        // the stage's column tiles (and statistics) may be replaced
+                if (has_acc) mma_commit_e(bar_free + 8 * s, leader);     // the stage's column tiles (and statistics) may be replaced
             };
 
             unsigned g = 0, tileno = 0, item = 0;
@@ -283,13 +284,16 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 const unsigned slot = item & 1;
                 ok = mbar_wait(bar_tab_full + 8 * slot, (item >> 1) & 1, abort_flag, P.wait_budget);
                 if (!ok) break;
-                const TileHead T = *reinterpret_cast<const TileHead*>(smem + Smem::kTab + slot * Smem::kTabBytes + 128 * 32);
+                const TileHead T = *reinterpret_cast<const TileHead*>(smem + Smem::kTab + slot * Smem::kTabBytes + kAxisEntries * 16);
                 __syncwarp();                    // every lane has read the head
                 if (leader) mbar_arrive(bar_tab_empty + 8 * slot);
                 if (!T.active) continue;
-                ok = mbar_wait(bar_row, tileno & 1, abort_flag, P.wait_budget) &&
-                     mbar_wait(bar_col + 8 * (g % kStages), (g / kStages) & 1, abort_flag, P.wait_budget);
+                STAMP(190);
+                ok = mbar_wait(bar_row, tileno & 1, abort_flag, P.wait_budget);
+                STAMP(191);
+                ok = ok && mbar_wait(bar_col + 8 * (g % kStages), (g / kStages) & 1, abort_flag, P.wait_budget);
                 if (!ok) break;
+                STAMP(192);
                 issue_s_dp(g, 0, T);
                 for (int cc = 0; cc < T.total && ok; ++cc, ++g) {
                     STAMP(200 + cc);
@@ -322,22 +326,15 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             const unsigned slot = item & 1;
             if (item >= 2) ok = ok && mbar_wait(bar_tab_empty + 8 * slot, ((item >> 1) - 1) & 1, abort_flag, P.wait_budget);
             uint8_t* tab = smem + Smem::kTab + slot * Smem::kTabBytes;
-            RowEntry* rows = reinterpret_cast<RowEntry*>(tab);
-#pragma unroll 1
-            for (int k = 0; k < 4; ++k) {
-                const int r = lane + 32 * k;
-                int ri[3];
-                row_offsets(P, r, ri);
-                RowEntry en;
-                bool valid_row = true, in_tensor = true;
-                long long pflat = 0;
+            AxisEntry* ent = reinterpret_cast<AxisEntry*>(tab);
+            int base = 0;
 #pragma unroll
-                for (int a = 0; a < 3; ++a) {
-                    const int xa = X.origin[a] + ri[a];
-                    const int pa = X.rg[a] + P.dil[a] * xa;
-                    if (xa >= X.Lp[a]) valid_row = false;
-                    if (pa >= P.L[a]) in_tensor = false;
-                    pflat = pflat * P.L[a] + pa;
+            for (int a = 0; a < 3; ++a) {
+                for (int i = lane; i < P.tile[a]; i += 32) {
+                    const int xa = X.origin[a] + i;
+                    AxisEntry en;
+                    en.pa = X.rg[a] + P.dil[a] * xa;
+                    en.flags = (xa < X.Lp[a] ? 1 : 0) | (en.pa < P.L[a] ? 2 : 0);
                     int fa = 0, ea = 0;
                     if (X.active) {
                         if (kKeySide) {
@@ -351,26 +348,21 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                             ea = (first + P.K[a] < X.Lp[a] ? first + P.K[a] : X.Lp[a]) - X.boxlo[a];
                         }
                     }
-                    en.f[a] = (short)fa;
-                    en.e[a] = (short)ea;
+                    en.f = (short)fa;
+                    en.e = (short)ea;
+                    en.pad = 0;
+                    ent[base + i] = en;
                 }
-                if (!valid_row) { en.e[0] = en.f[0]; en.e[1] = en.f[1]; en.e[2] = en.f[2]; }
-                en.flags = (valid_row ? 1 : 0) | (in_tensor ? 2 : 0);
-                en.out_row = ((long long)X.b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + X.hy;
-                en.lse2 = 0.f;
-                en.delta = 0.f;
-                if (!kKeySide && valid_row && in_tensor && X.active && ok) {      // negated, pre-scaled addends
-                    en.lse2 = -lse[en.out_row] * 1.4426950408889634f;
-                    en.delta = -delta[en.out_row] * P.scale;
-                }
-                rows[r] = en;
+                base += P.tile[a];
             }
             if (lane == 0) {
-                TileHead* hd = reinterpret_cast<TileHead*>(tab + 128 * 32);
+                TileHead* hd = reinterpret_cast<TileHead*>(tab + kAxisEntries * 16);
                 hd->active = X.active ? 1 : 0;
                 hd->total = X.total;
                 hd->nbox = X.nbox;
                 hd->nchunks = X.nchunks;
+                hd->b = X.b;
+                hd->hy = X.hy;
 #pragma unroll
                 for (int a = 0; a < 3; ++a) { hd->nc[a] = X.nc[a]; hd->boxlo[a] = X.boxlo[a]; hd->Lp[a] = X.Lp[a]; }
             }
@@ -395,13 +387,16 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         }
         for (unsigned work = blockIdx.x; work < nwork; work += gridDim.x, ++item) {
             const unsigned wn = work + gridDim.x;
+            STAMP(390);
             if (wn < nwork) {                    // the next item's table first: it is needed before this tile ends
                 bwd_tile_setup<kKeySide>(P, wn, Tn);
                 write_table(wn, item + 1, Tn);
             }
+            STAMP(395);
             if (T.active) {
                 // the row tiles are free once the previous tile's last S / dP products have finished
                 if (tiles > 0) ok = ok && mbar_wait(bar_rowfree, (tiles - 1) & 1, abort_flag, P.wait_budget);
+                STAMP(398);
                 if (lane == 0 && ok) issue_rows(T);
                 ++tiles;
                 int ci[3] = {0, 0, 0}, hc = T.hy * P.group;
@@ -409,6 +404,31 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 for (int cc = 0; cc < T.total; ++cc, ++g) {
                     const int s = g % kStages;
                     STAMP(400 + cc);
+                    // key side: the chunk's column statistics are fetched before the wait for the stage, so that
+                    // their latency is not part of what follows it
+                    float raw_lse[kCols / 32], raw_delta[kCols / 32];
+                    if (kKeySide) {
+#pragma unroll
+                        for (int k = 0; k < kCols / 32; ++k) {
+                            const int j = lane + 32 * k;
+                            const int j2 = j & (P.cb[2] - 1);
+                            const int j1 = (j >> P.cb2_log) & (P.cb[1] - 1);
+                            const int j0 = j >> (P.cb2_log + P.cb1_log);
+                            const int q0 = T.boxlo[0] + chunk_coord(P, 0, ci[0], j0);
+                            const int q1 = T.boxlo[1] + chunk_coord(P, 1, ci[1], j1);
+                            const int q2 = T.boxlo[2] + chunk_coord(P, 2, ci[2], j2);
+                            const bool inside = ok && q0 >= 0 && q0 < T.Lp[0] && q1 >= 0 && q1 < T.Lp[1] && q2 >= 0 && q2 < T.Lp[2];
+                            raw_lse[k] = 0.f;
+                            raw_delta[k] = 0.f;
+                            if (inside) {
+                                const long long pflat = ((long long)(T.rg[0] + P.dil[0] * q0) * P.L[1] + (T.rg[1] + P.dil[1] * q1)) * P.L[2]
+                                                        + (T.rg[2] + P.dil[2] * q2);
+                                const long long row = ((long long)T.b * P.ltot + pflat) * P.Hq + hc;
+                                raw_lse[k] = lse[row];
+                                raw_delta[k] = delta[row];
+                            }
+                        }
+                    }
                     if (g >= (unsigned)kStages) ok = ok && mbar_wait(bar_free + 8 * s, ((g / kStages) - 1) & 1, abort_flag, P.wait_budget);
                     STAMP(410);
                     if (lane == 0 && ok) {
@@ -441,25 +461,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                     }
                     float* st = stats + s * 128;
 #pragma unroll
-                    for (int k = 0; k < kCols / 32; ++k) {
-                        const int j = lane + 32 * k;
-                        const int j2 = j & (P.cb[2] - 1);
-                        const int j1 = (j >> P.cb2_log) & (P.cb[1] - 1);
-                        const int j0 = j >> (P.cb2_log + P.cb1_log);
-                        const int q0 = T.boxlo[0] + chunk_coord(P, 0, ci[0], j0);
-                        const int q1 = T.boxlo[1] + chunk_coord(P, 1, ci[1], j1);
-                        const int q2 = T.boxlo[2] + chunk_coord(P, 2, ci[2], j2);
-                        const bool inside = ok && q0 >= 0 && q0 < T.Lp[0] && q1 >= 0 && q1 < T.Lp[1] && q2 >= 0 && q2 < T.Lp[2];
-                        float l2 = 0.f, dl = 0.f;
-                        if (inside) {
-                            const long long pflat = ((long long)(T.rg[0] + P.dil[0] * q0) * P.L[1] + (T.rg[1] + P.dil[1] * q1)) * P.L[2]
-                                                    + (T.rg[2] + P.dil[2] * q2);
-                            const long long row = ((long long)T.b * P.ltot + pflat) * P.Hq + hc;
-                            l2 = -lse[row] * 1.4426950408889634f;        // negated, pre-scaled addends
-                            dl = -delta[row] * P.scale;
-                        }
-                        st[j] = l2;
-                        st[kCols + j] = dl;
+                    for (int k = 0; k < kCols / 32; ++k) {               // negated, pre-scaled addends
+                        st[lane + 32 * k] = -raw_lse[k] * 1.4426950408889634f;
+                        st[kCols + lane + 32 * k] = -raw_delta[k] * P.scale;
                     }
                     mbar_arrive(bar_stats + 8 * s);
                     if (++ci[2] == T.nc[2]) { ci[2] = 0; if (++ci[1] == T.nc[1]) { ci[1] = 0; if (++ci[0] == T.nc[0]) { ci[0] = 0; ++hc; } } }
@@ -482,13 +486,36 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             ok = mbar_wait(bar_tab_full + 8 * slot, (item >> 1) & 1, abort_flag, P.wait_budget) && ok;
             const uint8_t* tab = smem + Smem::kTab + slot * Smem::kTabBytes;
             STAMP(300);
-            const RowEntry en = reinterpret_cast<const RowEntry*>(tab)[quad * 32 + lane];
-            const TileHead T = *reinterpret_cast<const TileHead*>(tab + 128 * 32);
+            const TileHead T = *reinterpret_cast<const TileHead*>(tab + kAxisEntries * 16);
+            int f[3], e[3];
+            bool valid_row = true, in_tensor = true;
+            long long pflat = 0;
+            {
+                int ri[3];
+                row_offsets(P, quad * 32 + lane, ri);
+                const AxisEntry* ent = reinterpret_cast<const AxisEntry*>(tab);
+                int base = 0;
+#pragma unroll
+                for (int a = 0; a < 3; ++a) {
+                    const AxisEntry en = ent[base + ri[a]];
+                    base += P.tile[a];
+                    f[a] = en.f;
+                    e[a] = en.e;
+                    valid_row = valid_row && (en.flags & 1);
+                    in_tensor = in_tensor && (en.flags & 2);
+                    pflat = pflat * P.L[a] + en.pa;
+                }
+            }
             mbar_arrive(bar_tab_empty + 8 * slot);
-            const int f[3] = {en.f[0], en.f[1], en.f[2]}, e[3] = {en.e[0], en.e[1], en.e[2]};
-            const bool valid_row = en.flags & 1, in_tensor = (en.flags & 2) != 0;
-            const long long out_row = en.out_row;
-            const float row_lse2 = en.lse2, row_delta = en.delta;
+            if (!valid_row) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
+            const long long out_row = ((long long)T.b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + T.hy;
+            // query side: the row's lse and delta; scaled where they are first used, so that the loads' latency
+            // runs under the set-up of the first chunk and the wait for its scores
+            float raw_lse = 0.f, raw_delta = 0.f;
+            if (!kKeySide && valid_row && in_tensor && T.active && ok) {
+                raw_lse = lse[out_row];
+                raw_delta = delta[out_row];
+            }
             if (!T.active) {                     // padding rows get zero gradients
                 if (in_tensor) {
 #pragma unroll
@@ -571,6 +598,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (g % kStages), (g / kStages) & 1, abort_flag, P.wait_budget);
                 tc_fence_after();
                 STAMP(320);
+                const float row_lse2 = -raw_lse * 1.4426950408889634f, row_delta = -raw_delta * P.scale;   // negated, pre-scaled addends
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {               // 16 columns at a time
                     uint32_t pk_p[8], pk_ds[8];
@@ -654,7 +682,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
 
             // ---- accumulators -> global: this warp owns 32 of the 64 channels ----
             STAMP(340);
-            ok = ok && mbar_wait(bar_acc, (g - 1) & 1, abort_flag, P.wait_budget);
+            ok = ok && mbar_wait(bar_free + 8 * ((g - 1) % kStages), ((g - 1) / kStages) & 1, abort_flag, P.wait_budget);   // the last chunk's accumulating products
             tc_fence_after();
             STAMP(350);
             // The TMEM loads are warp-collective: every lane takes part.  A lane holds 32 channels (64 bytes) of
