@@ -128,6 +128,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             constexpr uint32_t idesc_qk = instr_desc(BF16 ? 1 : 0, kKeys, 0, 0);
             constexpr uint32_t idesc_pv = instr_desc(BF16 ? 1 : 0, DH, 0, 1);
             const uint64_t dq0 = smem_desc(sbase + kOffQ, 16, 1024);
+            const uint32_t leader = elect_one();
             bool ok = true;
             Cursor cur;
             cur.init(P, blockIdx.x, gridDim.x);
@@ -217,19 +218,21 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 const int s = n_qk % kStages;
                 ok = ok && mbar_wait(bar_kv + 8 * s, (n_qk / kStages) & 1, abort_flag, P.wait_budget);
                 if (!ok) return;
-                if (lane == 0) {
-                    if (P.extents && c < H->nnb) {
-                        const int box0[3] = {H->lo[0] + chunk_coord(P, 0, qc[0], 0), H->lo[1] + chunk_coord(P, 1, qc[1], 0),
-                                             H->lo[2] + chunk_coord(P, 2, qc[2], 0)};
+                if (P.extents && c < H->nnb) {
+                    const int box0[3] = {H->lo[0] + chunk_coord(P, 0, qc[0], 0), H->lo[1] + chunk_coord(P, 1, qc[1], 0),
+                                         H->lo[2] + chunk_coord(P, 2, qc[2], 0)};
+                    if (lane == 0)
                         zero_rows_past_extent(P, box0, H->Lp, kKeys, 1, kKVBytes, smem + kOffK + s * kKVBytes, smem + kOffV + s * kKVBytes);
-                    }
+                    __syncwarp();
+                }
+                {   // warp-uniform code; the tensor-core instructions execute on the elected lane
                     const uint64_t dk0 = smem_desc(sbase + kOffK + s * kKVBytes, 16, 1024);
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < DH / 16; ++ks)            // 32 bytes per k-step
-                        mma_ss(tmem + kColS, dq0 + 2 * ks, dk0 + 2 * ks, idesc_qk, ks > 0);
-                    mma_commit(bar_s);
-                    if (c + 1 == H->nch) mma_commit(bar_qfree);     // last scores of the tile: Q may go once they are done
+                        mma_ss_e(tmem + kColS, dq0 + 2 * ks, dk0 + 2 * ks, idesc_qk, ks > 0, leader);
+                    mma_commit_e(bar_s, leader);
+                    if (c + 1 == H->nch) mma_commit_e(bar_qfree, leader);     // last scores of the tile: Q may go once they are done
                 }
                 if (c < H->nnb) { if (++qc[2] == H->nc[2]) { qc[2] = 0; if (++qc[1] == H->nc[1]) { qc[1] = 0; ++qc[0]; } } }
                 ++n_qk;
@@ -238,14 +241,14 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             auto issue_pv = [&](int c, bool last) {
                 // V read MN-major: 16 key rows per k-step; P sits as 16-bit pairs in the first 32 S columns
                 const int s = n_pv % kStages;
-                if (lane == 0) {
+                {
                     const uint64_t dv0 = smem_desc(sbase + kOffV + s * kKVBytes, kKVBytes, 1024);
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < kKeys / 16; ++ks)
-                        mma_ts(tmem + kColO, tmem + kColS + 8 * ks, dv0 + 128 * ks, idesc_pv, (c > 0 || ks > 0) ? 1u : 0u);
-                    mma_commit(bar_kvfree + 8 * s);
-                    if (last) mma_commit(bar_o);
+                        mma_ts_e(tmem + kColO, tmem + kColS + 8 * ks, dv0 + 128 * ks, idesc_pv, (c > 0 || ks > 0) ? 1u : 0u, leader);
+                    mma_commit_e(bar_kvfree + 8 * s, leader);
+                    if (last) mma_commit_e(bar_o, leader);
                 }
                 ++n_pv;
             };
