@@ -234,9 +234,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
     if (warp == 8) {
         // =====================================================================
-        // TMA + MMA issue (one thread)
+        // TMA + MMA issue: the warp runs the loop converged, the tensor-core instructions execute on an
+        // elected lane (a thread issuing alone from a divergent branch pays for every operand it moves into
+        // the uniform registers those instructions take)
         // =====================================================================
-        if (lane == 0 && !*abort_flag) {
+        const uint32_t leader = elect_one();
+        if (!*abort_flag) {
             constexpr uint32_t idesc_qk = instr_desc(BF16 ? 1 : 0, kChunk, 0, 0);
             constexpr uint32_t idesc_pv = instr_desc(BF16 ? 1 : 0, DH, 0, 1);
             const uint64_t dq0 = smem_desc(sbase + SM::kQ, 16, 1024);
@@ -244,8 +247,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             auto issue_qk = [&](int c) {
                 if (P.extents && c < nnb) {
                     const int box0[3] = {lo[0] + qc[0] * P.cb[0], lo[1] + qc[1] * P.cb[1], lo[2] + qc[2] * P.cb[2]};
-                    zero_rows_past_extent(P, box0, Lp, kChunk, SM::kHalves, SM::kHalf,
-                                          smem + SM::kK + (c % kStages) * SM::kTile, smem + SM::kV + (c % kStages) * SM::kTile);
+                    if (leader)
+                        zero_rows_past_extent(P, box0, Lp, kChunk, SM::kHalves, SM::kHalf,
+                                              smem + SM::kK + (c % kStages) * SM::kTile, smem + SM::kV + (c % kStages) * SM::kTile);
+                    __syncwarp();
                     if (++qc[2] == nc[2]) { qc[2] = 0; if (++qc[1] == nc[1]) { qc[1] = 0; ++qc[0]; } }
                 }
                 const uint64_t dk0 = smem_desc(sbase + SM::kK + (c % kStages) * SM::kTile, 16, 1024);
@@ -253,9 +258,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
                 for (int ks = 0; ks < DH / 16; ++ks) {       // 32 bytes per k-step inside a 64-channel block
                     const uint32_t off = ((ks / 4) * SM::kHalf + (ks % 4) * 32) >> 4;
-                    mma_ss(tmem + kColS, dq0 + off, dk0 + off, idesc_qk, ks > 0);
+                    mma_ss_e(tmem + kColS, dq0 + off, dk0 + off, idesc_qk, ks > 0, leader);
                 }
-                mma_commit(bar_s);
+                mma_commit_e(bar_s, leader);
             };
             auto issue_pv = [&](int c) {
                 // V read MN-major: 16 key rows per k-step, the second 64-channel block sits kHalf bytes further.
@@ -264,8 +269,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kChunk / 16; ++ks)
-                    mma_ts(tmem + kColO, tmem + kColP + 8 * ks, dv0 + 128 * ks, idesc_pv, c > 0 || ks > 0);
-                mma_commit(bar_o);
+                    mma_ts_e(tmem + kColO, tmem + kColP + 8 * ks, dv0 + 128 * ks, idesc_pv, c > 0 || ks > 0, leader);
+                mma_commit_e(bar_o, leader);
             };
             bool ok = mbar_wait(bar_q, 0, abort_flag, P.wait_budget);
             ok = ok && mbar_wait(bar_kv, 0, abort_flag, P.wait_budget);
@@ -291,7 +296,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 if (c + kStages < nch) {
                     ok = mbar_wait(bar_o, c & 1, abort_flag, P.wait_budget);        // stage c % kStages is free again
                     if (!ok) break;
-                    issue_kv();
+                    if (leader) issue_kv();
+                    __syncwarp();
                 }
             }
         }

@@ -225,7 +225,9 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 8) {
-        if (lane == 0 && !*abort_flag) {
+        // the warp runs the loop converged; the tensor-core instructions execute on an elected lane
+        const uint32_t leader = elect_one();
+        if (!*abort_flag) {
             constexpr uint32_t idesc = instr_desc(BF16 ? 1 : 0, kChunk, 0, 0);
             const uint64_t dx0 = smem_desc(sbase + SM::kX, 16, 1024);
             auto issue_s = [&](int c) {
@@ -234,16 +236,17 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 #pragma unroll
                 for (int ks = 0; ks < DH / 16; ++ks) {
                     const uint32_t off = ((ks / 4) * SM::kHalf + (ks % 4) * 32) >> 4;
-                    mma_ss(tmem, dx0 + off, dy0 + off, idesc, ks > 0);
+                    mma_ss_e(tmem, dx0 + off, dy0 + off, idesc, ks > 0, leader);
                 }
-                mma_commit(bar_s);
+                mma_commit_e(bar_s, leader);
             };
             bool ok = mbar_wait(bar_x, 0, abort_flag, P.wait_budget) && mbar_wait(bar_y, 0, abort_flag, P.wait_budget);
             if (ok) issue_s(0);
             for (int c = 0; c < nch && ok; ++c) {
                 ok = mbar_wait(bar_s, c & 1, abort_flag, P.wait_budget);            // the product is done: its Y stage is free
                 if (!ok) break;
-                if (c + kStages < nch) issue_y();
+                if (c + kStages < nch && leader) issue_y();
+                __syncwarp();
                 ok = mbar_wait(bar_sp, c & 1, abort_flag, P.wait_budget);           // S(c) read by every thread
                 if (!ok) break;
                 if (c + 1 < nch) {
@@ -437,7 +440,9 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 8) {
-        if (lane == 0 && !*abort_flag) {
+        // the warp runs the loop converged; the tensor-core instructions execute on an elected lane
+        const uint32_t leader = elect_one();
+        if (!*abort_flag) {
             constexpr uint32_t idesc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A = P from TMEM, B = Y MN-major
             bool ok = true;
             for (int c = 0; c < nch && ok; ++c) {
@@ -448,12 +453,13 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kChunk / 16; ++ks)
-                    mma_ts(tmem + SM::kColO, tmem + SM::kColP + 64 * (c & 1) + 8 * ks, dy0 + 128 * ks, idesc, c > 0 || ks > 0);
-                mma_commit(bar_o + 8 * (c & 1));
+                    mma_ts_e(tmem + SM::kColO, tmem + SM::kColP + 64 * (c & 1) + 8 * ks, dy0 + 128 * ks, idesc, c > 0 || ks > 0, leader);
+                mma_commit_e(bar_o + 8 * (c & 1), leader);
                 if (c >= 1 && c + 2 < nch) {             // the product before this one is done: its Y stage is free
                     ok = mbar_wait(bar_o + 8 * ((c - 1) & 1), ((c - 1) >> 1) & 1, abort_flag, P.wait_budget);
                     if (!ok) break;
-                    issue_y();
+                    if (leader) issue_y();
+                    __syncwarp();
                 }
             }
         }
@@ -682,7 +688,9 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 8) {
-        if (lane == 0 && !*abort_flag) {
+        // the warp runs the loop converged; the tensor-core instructions execute on an elected lane
+        const uint32_t leader = elect_one();
+        if (!*abort_flag) {
             constexpr uint32_t idesc = instr_desc(BF16 ? 1 : 0, DH, 0, 1);      // A = P^T from TMEM, B = X MN-major
             bool ok = true;
             for (int c = 0; c < total && ok; ++c) {
@@ -693,12 +701,13 @@ tc_gather_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kChunk / 16; ++ks)
-                    mma_ts(tmem + SM::kColO, tmem + SM::kColP + 64 * (c & 1) + 8 * ks, dx0 + 128 * ks, idesc, c > 0 || ks > 0);
-                mma_commit(bar_o + 8 * (c & 1));
+                    mma_ts_e(tmem + SM::kColO, tmem + SM::kColP + 64 * (c & 1) + 8 * ks, dx0 + 128 * ks, idesc, c > 0 || ks > 0, leader);
+                mma_commit_e(bar_o + 8 * (c & 1), leader);
                 if (c >= 1 && c + 2 < total) {           // the product before this one is done: its X stage is free
                     ok = mbar_wait(bar_o + 8 * ((c - 1) & 1), ((c - 1) >> 1) & 1, abort_flag, P.wait_budget);
                     if (!ok) break;
-                    issue_x();
+                    if (leader) issue_x();
+                    __syncwarp();
                 }
             }
         }
