@@ -358,6 +358,30 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         int ci[3] = {0, 0, 0};
         int jl[3] = {0, 0, 0}, jh[3] = {0, 0, 0};
         uint32_t rowbits = 0u, colbits = 0u, dirty = 7u;     // 16-column rows: one bit per piece, one per column
+        // 16-column rows with a single chunk along the innermost axis and at most 16 chunks: which pieces of
+        // which chunk lie inside the row's window is worked out once per tile from the row's side (a loop over
+        // the window's rows, each of which lands in one piece of one chunk), four bits per chunk.
+        bool mapped = false;
+        unsigned long long rowmap = 0ull;
+        if constexpr (kRows16) {
+            if (T.nc[2] == 1 && T.nnb <= 16) {
+                mapped = true;
+                for (int x0 = f[0]; x0 < e[0]; ++x0) {
+                    int c0, j0;
+                    if (P.il[0] == 1) { c0 = x0 >> P.cb0_log; j0 = x0 & (P.cb[0] - 1); }
+                    else { j0 = (int)fast_div((unsigned)x0, P.il_mul[0]); c0 = x0 - j0 * P.il[0]; }
+                    for (int x1 = f[1]; x1 < e[1]; ++x1) {
+                        int c1, j1;
+                        if (P.il[1] == 1) { c1 = x1 >> P.cb1_log; j1 = x1 & (P.cb[1] - 1); }
+                        else { j1 = (int)fast_div((unsigned)x1, P.il_mul[1]); c1 = x1 - j1 * P.il[1]; }
+                        rowmap |= 1ull << (4 * (c0 * T.nc[1] + c1) + (j0 << P.cb1_log) + j1);
+                    }
+                }
+                int l2, h2;
+                chunk_range(P, 2, 0, f[2], e[2], l2, h2);
+                colbits = h2 > l2 ? (low_bits(h2) & ~low_bits(l2)) : 0u;
+            }
+        }
         for (int c = 0; c < T.nch; ++c, ++n) {
             // ---- validity of this row's columns in this chunk ----
             // jl/jh (columns of the chunk inside the row's window, per axis) only change along the axes whose
@@ -368,6 +392,8 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
                 for (int pc = 0; pc < 2; ++pc)
                     words[pc] = valid_q ? low_bits(P.n_extra - ((c - T.nnb) * kKeys + 32 * pc)) : 0u;
+            } else if (mapped) {
+                rowbits = (uint32_t)(rowmap >> (4 * c)) & 15u;
             } else {
 #pragma unroll
                 for (int a = 0; a < 3; ++a)
@@ -513,11 +539,13 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tc_fence_before();
             mbar_arrive(bar_p);
             STAMP(330);
-            ++ci[2];
-            dirty = 4u;
-            if (ci[2] == T.nc[2]) {
-                ci[2] = 0; ++ci[1]; dirty = T.nc[2] > 1 ? 6u : 2u;
-                if (ci[1] == T.nc[1]) { ci[1] = 0; ++ci[0]; dirty = 1u | (T.nc[1] > 1 ? 2u : 0u) | (T.nc[2] > 1 ? 4u : 0u); }
+            if (!mapped) {
+                ++ci[2];
+                dirty = 4u;
+                if (ci[2] == T.nc[2]) {
+                    ci[2] = 0; ++ci[1]; dirty = T.nc[2] > 1 ? 6u : 2u;
+                    if (ci[1] == T.nc[1]) { ci[1] = 0; ++ci[0]; dirty = 1u | (T.nc[1] > 1 ? 2u : 0u) | (T.nc[2] > 1 ? 4u : 0u); }
+                }
             }
         }
 
