@@ -75,10 +75,10 @@ struct SmemB {
     static constexpr int kC2 = kC1 + kStages * kColTile;        // [kStages]
     static constexpr int kStats = kC2 + kStages * kColTile;     // [kStages][2][64] float
     static constexpr int kTab = kStats + kStages * 512;         // [2] tables: axis entries, then a TileHead
-    static constexpr int kTabBytes = kAxisEntries * 16 + 64;
+    static constexpr int kTabBytes = kAxisEntries * 16 + 96;
     static constexpr int kBar = kTab + 2 * kTabBytes;
-    static constexpr int kStage = kBar + 256;                    // [kComputeWarps] 32 rows x 64 bytes: output staging
-    static constexpr int kTotal = kStage + kComputeWarps * 2048;
+    static constexpr int kStage = (kBar + 256 + 1023) & ~1023;   // output staging: a row tile [128 x DH] 16-bit, swizzled like the loads
+    static constexpr int kTotal = kStage + kTile;
     static constexpr uint32_t kTmemCols = DH == 64 ? 256 : 512;
     static constexpr uint32_t kColA2 = kColA1 + DH;
 };
@@ -109,8 +109,9 @@ struct TileHead {
     int active, total, nbox, nc[3];
     int nchunks, boxlo[3], Lp[3];      // for the MMA warps: chunks of the column box, its origin, sub-grid extents
     int b, hy;                         // batch and head of the rows
+    short rg0, rg1, rg2, origin0, origin1, origin2;   // dilation residues and origin of the row tile (for its store)
 };
-static_assert(sizeof(TileHead) <= 64, "the tile head has 64 bytes behind the axis table");
+static_assert(sizeof(TileHead) <= 96, "the tile head has 96 bytes behind the axis table");
 
 template <bool kKeySide>
 __device__ __forceinline__ void bwd_tile_setup(const TcParams& P, unsigned work, BwdTile& T)
@@ -154,6 +155,7 @@ __global__ void __launch_bounds__(kThreads, (DH == 64 ? 2 : 1))
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
               const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2,
               const __grid_constant__ CUtensorMap tmE1, const __grid_constant__ CUtensorMap tmE2,
+              const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
               const __grid_constant__ TcParams P, const float* __restrict__ lse,
               const float* __restrict__ delta, uint16_t* __restrict__ out1, uint16_t* __restrict__ out2)
 {
@@ -363,6 +365,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 hd->nchunks = X.nchunks;
                 hd->b = X.b;
                 hd->hy = X.hy;
+                hd->rg0 = (short)X.rg[0]; hd->rg1 = (short)X.rg[1]; hd->rg2 = (short)X.rg[2];
+                hd->origin0 = (short)X.origin[0]; hd->origin1 = (short)X.origin[1]; hd->origin2 = (short)X.origin[2];
 #pragma unroll
                 for (int a = 0; a < 3; ++a) { hd->nc[a] = X.nc[a]; hd->boxlo[a] = X.boxlo[a]; hd->Lp[a] = X.Lp[a]; }
             }
@@ -507,6 +511,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 }
             }
             mbar_arrive(bar_tab_empty + 8 * slot);
+            STAMP(301);
             if (!valid_row) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
             const long long out_row = ((long long)T.b * P.ltot + pflat) * (kKeySide ? P.Hkv : P.Hq) + T.hy;
             // query side: the row's lse and delta; scaled where they are first used, so that the loads' latency
@@ -516,6 +521,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 raw_lse = lse[out_row];
                 raw_delta = delta[out_row];
             }
+            STAMP(302);
             if (!T.active) {                     // padding rows get zero gradients
                 if (in_tensor) {
 #pragma unroll
@@ -685,47 +691,43 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             ok = ok && mbar_wait(bar_free + 8 * ((g - 1) % kStages), ((g - 1) / kStages) & 1, abort_flag, P.wait_budget);   // the last chunk's accumulating products
             tc_fence_after();
             STAMP(350);
-            // The TMEM loads are warp-collective: every lane takes part.  A lane holds 32 channels (64 bytes) of
-            // its own row; the warp passes them through a [32 rows x 64 bytes] block of shared memory so that
-            // four lanes write one row's 64 bytes together: every store instruction fills whole 32-byte sectors
-            // of eight rows instead of touching 32 rows with 16 bytes each.
+            // The accumulators leave through shared memory and a bulk tensor store: every thread converts its
+            // 32 channels of its row and writes them into a [128 x DH] tile laid out like the row tiles the loads
+            // bring in (128-byte rows, 16-byte chunks swizzled by the row); one thread then hands the tile to the
+            // TMA unit, which writes it out in the background (rows outside the tensor are clipped) while the
+            // threads go on.  The tile is reused only after that thread has seen the store finish reading it.
             const bool live = valid_row && ok;
-            uint8_t* stg = smem + Smem::kStage + warp * 2048;
-            long long row_of[4];                 // output row (or -1) of the rows this lane stores: 8 * i + lane / 4
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int src = 8 * i + (lane >> 2);
-                const long long orow = __shfl_sync(0xffffffffu, out_row, src);
-                const int there = __shfl_sync(0xffffffffu, in_tensor ? 1 : 0, src);
-                row_of[i] = there ? orow : -1;
-            }
+            const int row = quad * 32 + lane;
 #pragma unroll
             for (int which = 0; which < (kKeySide ? 2 : 1); ++which) {
+                if (warp == 0 && lane == 0) tma_store_wait_read();               // the previous store has let go of the tile
+                asm volatile("bar.sync 1, 256;" ::: "memory");
 #pragma unroll
                 for (int part = 0; part < CH / 32; ++part) {
                     uint32_t a[32];
                     tmem_ld32(trow + (which == 0 ? kColA1 : kColA2) + CH * piece + 32 * part, a);
                     tmem_ld_wait();
+                    const int ch = CH * piece + 32 * part;                   // first of this thread's 32 channels
+                    uint8_t* blk = smem + Smem::kStage + (ch >> 6) * kRowHalf + row * 128;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {        // 16-byte chunks, swizzled against bank conflicts
+                    for (int c = 0; c < 4; ++c) {
                         uint32_t w[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
                             w[j] = live ? pack16(__uint_as_float(a[8 * c + 2 * j]), __uint_as_float(a[8 * c + 2 * j + 1]), BF16) : 0u;
-                        *reinterpret_cast<uint4*>(stg + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                        const int chunk = ((ch & 63) >> 3) + c;
+                        *reinterpret_cast<uint4*>(blk + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    __syncwarp();
-                    const int c = lane & 3;
-                    const int ch0 = piece * CH + 32 * part + 8 * c;          // first channel of this lane's chunk
-                    uint16_t* dst = which == 0 ? out1 : out2;
+                }
+                fence_async_smem();                                          // the TMA unit reads through the async proxy
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (warp == 0 && lane == 0 && ok && NATTEN_ABL != 1) {
+                    const CUtensorMap* map = which == 0 ? &tmO1 : &tmO2;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int r = 8 * i + (lane >> 2);
-                        const uint4 v = *reinterpret_cast<const uint4*>(stg + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
-                        if (row_of[i] >= 0 && ch0 < P.dreal && NATTEN_ABL != 1)          // padded channels are not part of the output
-                            *reinterpret_cast<uint4*>(dst + row_of[i] * P.dreal + ch0) = v;
-                    }
-                    __syncwarp();                        // the block is reused by the next part
+                    for (int hf = 0; hf < Smem::kHalves; ++hf)
+                        tma_store_heads(map, sbase + Smem::kStage + hf * kRowHalf, P, DH, T.hy * DH + 64 * hf,
+                                        T.rg2 + P.dil[2] * T.origin2, T.rg1 + P.dil[1] * T.origin1, T.rg0 + P.dil[0] * T.origin0, T.b);
+                    tma_store_commit();
                 }
             }
             // the next tile's first accumulating MMA is issued only after every thread has passed here
@@ -734,6 +736,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
         }
     }
 
+    if (warp == 0 && lane == 0) tma_store_wait_all();     // bulk stores of the last tiles
     if (*abort_flag) abort_grace_sleep();       // loads of a wait that gave up may still be landing
     tc_fence_before();
     __syncthreads();
@@ -856,6 +859,14 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
         !encode_map(&q_chunk, q, bf, p, g.Hq, g.D, g.qs, plan.box_kv, false, true) ||
         !encode_map(&do_chunk, dout_k, bf, p, g.Hq, g.D, dos, plan.box_kv, false, true))
         return -2;
+    // outputs: contiguous [B, *L, H, D]; stored as row tiles
+    CUtensorMap dq_tile, dk_tile, dv_tile;
+    const long long dqs[3] = {g.ltot * g.Hq * g.D, (long long)g.Hq * g.D, g.D};
+    const long long dks[3] = {g.ltot * g.Hkv * g.D, (long long)g.Hkv * g.D, g.D};
+    if (!encode_map(&dq_tile, dq, bf, p, g.Hq, g.D, dqs, plan.box_q) ||
+        !encode_map(&dk_tile, dk, bf, p, g.Hkv, g.D, dks, plan.box_q) ||
+        !encode_map(&dv_tile, dv, bf, p, g.Hkv, g.D, dks, plan.box_q))
+        return -2;
     ek_chunk = k_chunk; ev_chunk = v_chunk;      // placeholders when there are no additional tokens
     if (g.n_extra > 0 && (!encode_extra_map(&ek_chunk, ek, bf, g.B, g.n_extra, g.Hkv, g.D, kCols, p.split_heads) ||
                           !encode_extra_map(&ev_chunk, ev, bf, g.B, g.n_extra, g.Hkv, g.D, kCols, p.split_heads)))
@@ -896,10 +907,10 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
         ensure_dynamic_smem((const void*)tc_bwd_kernel<DH, BF16, false, kInner>, Smem::kTotal);
         ensure_dynamic_smem((const void*)tc_bwd_kernel<DH, BF16, true, kInner>, Smem::kTotal);
         tc_bwd_kernel<DH, BF16, false, kInner><<<grid_q, kThreads, Smem::kTotal, s>>>(
-            q_tile, do_tile, k_chunk, v_chunk, ek_chunk, ev_chunk, p, lse_k, delta_k, (uint16_t*)dq, nullptr);
+            q_tile, do_tile, k_chunk, v_chunk, ek_chunk, ev_chunk, dq_tile, dq_tile, p, lse_k, delta_k, (uint16_t*)dq, nullptr);
         tc_count_launch();
         tc_bwd_kernel<DH, BF16, true, kInner><<<grid_k, kThreads, Smem::kTotal, s>>>(
-            k_tile, v_tile, q_chunk, do_chunk, ek_chunk, ev_chunk, p, lse_k, delta_k, (uint16_t*)dk, (uint16_t*)dv);
+            k_tile, v_tile, q_chunk, do_chunk, ek_chunk, ev_chunk, dk_tile, dv_tile, p, lse_k, delta_k, (uint16_t*)dk, (uint16_t*)dv);
         tc_count_launch();
     };
     if (p.cb[2] == 16) launch(std::integral_constant<int, 16>{});
@@ -931,7 +942,9 @@ int tc_fused_bwd(int dtype, const Geo& g_in, const void* q, const void* k, const
 {
     if (!tc_eligible(dtype, g_in, q, k, v, /*allow_stride=*/true)) return -2;
     if (g_in.n_extra > 0 && ((reinterpret_cast<uintptr_t>(ek) | reinterpret_cast<uintptr_t>(ev)) & 15u)) return -2;
-    if (reinterpret_cast<uintptr_t>(dout) & 15u) return -2;
+    if ((reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
+         reinterpret_cast<uintptr_t>(dv)) & 15u)
+        return -2;
     const bool strided = has_stride(g_in);
     Geo g = g_in;
     Expanded ex;

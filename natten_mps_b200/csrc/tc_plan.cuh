@@ -98,6 +98,12 @@ __device__ __forceinline__ void tma_load_heads(uint32_t dst, const CUtensorMap* 
     if (P.split_heads) tma_load_5d(dst, map, bar, c0 & (dh - 1), c0 / dh, c1, c2, c4);
     else tma_load_5d(dst, map, bar, c0, c1, c2, c3, c4);
 }
+__device__ __forceinline__ void tma_store_heads(const CUtensorMap* map, uint32_t src, const TcParams& P, int dh, int c0,
+                                                int c1, int c2, int c3, int c4)
+{
+    if (P.split_heads) tma_store_5d(map, src, c0 & (dh - 1), c0 / dh, c1, c2, c4);
+    else tma_store_5d(map, src, c0, c1, c2, c3, c4);
+}
 __device__ __forceinline__ void tma_prefetch_heads(const CUtensorMap* map, const TcParams& P, int dh, int c0, int c1,
                                                    int c2, int c3, int c4)
 {
