@@ -546,6 +546,26 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             uint32_t colmask[kPairs];            // separable geometry: 16-bit lane masks per column pair
             bool cols_any = false;
             int cached_c2 = -1;
+            // 16-column inner rows, one chunk along the innermost axis, at most 16 chunks in the box: which of a
+            // chunk's four rows lie inside this thread's range is worked out once per tile from the row's side
+            // (every row of the range lands in one row of one chunk), four bits per chunk.
+            bool mapped = false;
+            unsigned long long rowmap = 0ull;
+            int cl = 0;                          // chunk of the box (wraps with every query head on the key side)
+            if (kInner == 16 && T.nc[2] == 1 && T.nchunks <= 16) {
+                mapped = true;
+                for (int x0 = f[0]; x0 < e[0]; ++x0) {
+                    int c0, j0;
+                    if (P.il[0] == 1) { c0 = x0 >> P.cb0_log; j0 = x0 & (P.cb[0] - 1); }
+                    else { j0 = (int)fast_div((unsigned)x0, P.il_mul[0]); c0 = x0 - j0 * P.il[0]; }
+                    for (int x1 = f[1]; x1 < e[1]; ++x1) {
+                        int c1, j1;
+                        if (P.il[1] == 1) { c1 = x1 >> P.cb1_log; j1 = x1 & (P.cb[1] - 1); }
+                        else { j1 = (int)fast_div((unsigned)x1, P.il_mul[1]); c1 = x1 - j1 * P.il[1]; }
+                        rowmap |= 1ull << (4 * (c0 * T.nc[1] + c1) + (j0 << P.cb1_log) + j1);
+                    }
+                }
+            }
             for (int cc = 0; cc < T.total; ++cc, ++g) {
                 // ---- validity of this warp's two 16-column halves for this thread's row ----
                 // half h covers chunk columns col0(h) .. col0(h)+15; bits [16h, 16h+16) of `word` belong to it
@@ -572,17 +592,27 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                                          ((2 * i + 1 >= lo2 && 2 * i + 1 < hi2) ? 0xFFFF0000u : 0u);
                         cols_any = hi2 > lo2;
                     }
-                    int lo0, hi0, lo1, hi1;
-                    chunk_range(P, 0, ci[0], f[0], e[0], lo0, hi0);
-                    chunk_range(P, 1, ci[1], f[1], e[1], lo1, hi1);
+                    if (mapped) {
+                        const uint32_t bits = (uint32_t)(rowmap >> (4 * cl)) & 15u;
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int jj = col0(h);
-                        const int j1 = (jj >> P.cb2_log) & (P.cb[1] - 1);
-                        const int j0 = jj >> (P.cb2_log + P.cb1_log);
-                        const bool rok = j0 >= lo0 && j0 < hi0 && j1 >= lo1 && j1 < hi1;
-                        rowmask[h] = rok ? 0xFFFFFFFFu : 0u;
-                        mine[h] = rok && cols_any;
+                        for (int h = 0; h < 2; ++h) {
+                            const bool rok = (bits >> (piece + 2 * h)) & 1u;
+                            rowmask[h] = rok ? 0xFFFFFFFFu : 0u;
+                            mine[h] = rok && cols_any;
+                        }
+                    } else {
+                        int lo0, hi0, lo1, hi1;
+                        chunk_range(P, 0, ci[0], f[0], e[0], lo0, hi0);
+                        chunk_range(P, 1, ci[1], f[1], e[1], lo1, hi1);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int jj = col0(h);
+                            const int j1 = (jj >> P.cb2_log) & (P.cb[1] - 1);
+                            const int j0 = jj >> (P.cb2_log + P.cb1_log);
+                            const bool rok = j0 >= lo0 && j0 < hi0 && j1 >= lo1 && j1 < hi1;
+                            rowmask[h] = rok ? 0xFFFFFFFFu : 0u;
+                            mine[h] = rok && cols_any;
+                        }
                     }
                 } else {
                     int jl[3], jh[3];
@@ -605,6 +635,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 tc_fence_after();
                 STAMP(320);
                 const float row_lse2 = -raw_lse * 1.4426950408889634f, row_delta = -raw_delta * P.scale;   // negated, pre-scaled addends
+                const uint64_t scale_log2_2 = pack2(P.scale_log2, P.scale_log2), scale_2 = pack2(P.scale, P.scale);
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {               // 16 columns at a time
                     uint32_t pk_p[8], pk_ds[8];
@@ -631,12 +662,14 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
 #pragma unroll
                                 for (int h2 = 0; h2 < 2; ++h2) {
                                     const int pl = 2 * g4 + h2, j = 2 * pl;      // pair / column inside the half
-                                    const float x0 = fmaf(__uint_as_float(s[j]), P.scale_log2, nl[2 * h2]);
-                                    const float x1 = fmaf(__uint_as_float(s[j + 1]), P.scale_log2, nl[2 * h2 + 1]);
-                                    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-                                    const float g0 = fmaf(__uint_as_float(dp[j]), P.scale, nd[2 * h2]);
-                                    const float g1 = fmaf(__uint_as_float(dp[j + 1]), P.scale, nd[2 * h2 + 1]);
-                                    uint32_t dd = cvt_pack<BF16>(p0 * g0, p1 * g1);
+                                    // two columns per instruction: packed fp32 fma / mul
+                                    const uint64_t x = fma2(pack2(__uint_as_float(s[j]), __uint_as_float(s[j + 1])), scale_log2_2,
+                                                            pack2(nl[2 * h2], nl[2 * h2 + 1]));
+                                    const float p0 = fast_exp2(lo_of(x)), p1 = fast_exp2(hi_of(x));
+                                    const uint64_t gg = fma2(pack2(__uint_as_float(dp[j]), __uint_as_float(dp[j + 1])), scale_2,
+                                                             pack2(nd[2 * h2], nd[2 * h2 + 1]));
+                                    const uint64_t ds2 = mul2(pack2(p0, p1), gg);
+                                    uint32_t dd = cvt_pack<BF16>(lo_of(ds2), hi_of(ds2));
                                     if (separable) dd = dd & colmask[(8 * half + pl) % kPairs] & rowmask[kInner == 16 ? half : 0];
                                     pk_ds[pl] = dd;
                                     if (kKeySide) {
@@ -677,7 +710,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 mbar_arrive(bar_sp);
                 STAMP(330);
                 // next chunk (innermost axis fastest; wraps to the next query head on the key side)
-                if (++ci[2] == T.nc[2]) {
+                if (mapped) {
+                    if (++cl == T.nchunks) cl = 0;
+                } else if (++ci[2] == T.nc[2]) {
                     ci[2] = 0;
                     if (++ci[1] == T.nc[1]) {
                         ci[1] = 0;

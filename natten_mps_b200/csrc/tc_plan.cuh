@@ -277,6 +277,27 @@ template <bool BF16> __device__ __forceinline__ uint32_t mul_x2(uint32_t a, uint
     return d;
 }
 
+// Two fp32 values in one 64-bit register pair, and the packed fp32 arithmetic of sm_100 on them (one
+// instruction for two lanes of an fma / mul).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi)
+{
+    return (static_cast<uint64_t>(__float_as_uint(hi)) << 32) | __float_as_uint(lo);
+}
+__device__ __forceinline__ float lo_of(uint64_t v) { return __uint_as_float(static_cast<uint32_t>(v)); }
+__device__ __forceinline__ float hi_of(uint64_t v) { return __uint_as_float(static_cast<uint32_t>(v >> 32)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t pack16(float a, float b, bool bf16)
 {
     if (bf16) {
