@@ -453,10 +453,12 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                             refresh_add(colbits);
                         }
                         float x[16], xa = -INFINITY, xb = -INFINITY;
+                        const uint64_t sc2 = pack2(P.scale_log2, P.scale_log2);
 #pragma unroll
-                        for (int i = 0; i < 16; i += 2) {
-                            x[i] = fmaf(__uint_as_float(s[i]), P.scale_log2, add[i]);
-                            x[i + 1] = fmaf(__uint_as_float(s[i + 1]), P.scale_log2, add[i + 1]);
+                        for (int i = 0; i < 16; i += 2) {              // two columns per packed fp32 fma
+                            const uint64_t xx = fma2(pack2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, pack2(add[i], add[i + 1]));
+                            x[i] = lo_of(xx);
+                            x[i + 1] = hi_of(xx);
                             xa = fmaxf(xa, x[i]);
                             xb = fmaxf(xb, x[i + 1]);
                         }
@@ -470,16 +472,15 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                                 for (int i = 0; i < 16; ++i) x[i] -= xmax;
                             }
                         }
-                        float r0 = 0.f, r1 = 0.f;
+                        uint64_t rr = 0ull;                                 // two partial row sums
                         const uint32_t keep = rowok ? 0xffffffffu : 0u;     // rows outside their window store zeros
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const float p0 = fast_exp2(x[2 * i]), p1 = fast_exp2(x[2 * i + 1]);
-                            r0 += p0;
-                            r1 += p1;
+                            rr = add2(rr, pack2(p0, p1));
                             pk[i] = cvt_pack<BF16>(p0, p1) & keep;
                         }
-                        if (rowok) l += r0 + r1;
+                        if (rowok) l += lo_of(rr) + hi_of(rr);
                         stored |= 1u << pc;
 #endif
                     } else {
