@@ -17,6 +17,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>
+#include <mma.h>
 #include <initializer_list>
 #include <type_traits>
 
@@ -1223,6 +1224,152 @@ inline unsigned grid_for(long long rows) { return (unsigned)((rows + kWarps - 1)
     } while (0)
 
 
+// The same partial sums with the four small matrix products of a tile on the warp-level tensor-core path
+// (16 x 16 x 16 fragments; the additional tokens are the 16-wide side of every product):
+//   phase 1  S = Qt Ek^T, dP = Gt Ev^T          [64 rows x 16 tokens], K = head dim    (warps 0-3 | 4-7, one row block each)
+//   threads  p = exp(S*scale - lse), ds = p (dP - delta) scale, rounded to the tensors' 16-bit type like the
+//            probabilities of the fused kernels
+//   phase 2  dEk += ds^T Qt, dEv += p^T Gt      [16 tokens x head dim], K = 64 rows     (warp w: channels 16w .. 16w+15)
+// The accumulators of phase 2 stay in registers across the block's tiles.  Head dims: multiples of 16 up to 128.
+template <typename T>
+__global__ void __launch_bounds__(256)
+extra_grad_mma_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T* __restrict__ ek,
+                      const T* __restrict__ ev, const float* __restrict__ lse,
+                      const float* __restrict__ delta, const T* __restrict__ dout,
+                      const float* __restrict__ dlse, float* __restrict__ partial, int e0, int ne)
+{
+    using namespace nvcuda;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int D = g.D, Dv = g.Dv, W = D + Dv;
+    const int qstr = D + 8, vstr = Dv + 8;                     // padded row strides (elements)
+    constexpr int kPStr = kExtraGroup + 8;                      // row stride of the 16-bit p / ds tiles
+    T* qt = reinterpret_cast<T*>(smem_raw);                     // [64][qstr]
+    T* gt = qt + kExtraTileRows * qstr;                         // [64][vstr]
+    T* ekt = gt + kExtraTileRows * vstr;                        // [16][qstr]   (tokens past ne are zero)
+    T* evt = ekt + kExtraGroup * qstr;                          // [16][vstr]
+    T* pt = evt + kExtraGroup * vstr;                           // [64][kPStr]  p
+    T* dst = pt + kExtraTileRows * kPStr;                       // [64][kPStr]  ds
+    float* sbuf = reinterpret_cast<float*>(dst + kExtraTileRows * kPStr);    // [64][16]  S
+    float* dbuf = sbuf + kExtraTileRows * kExtraGroup;          // [64][16]  dP
+    float* rl = dbuf + kExtraTileRows * kExtraGroup;            // [64] lse
+    float* rd = rl + kExtraTileRows;                            // [64] delta
+    long long* qoff = reinterpret_cast<long long*>(rd + kExtraTileRows);   // [64] element offset of the q row, -1 = no row
+    long long* orow = qoff + kExtraTileRows;                    // [64] row of dout / lse / delta
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int seg = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    for (int i = tid; i < kExtraGroup * D; i += 256) {
+        const int e = i / D, d = i % D;
+        ekt[e * qstr + d] = e < ne ? ek[(((long long)b * g.n_extra + e0 + e) * g.Hkv + hk) * D + d] : T(0.f);
+    }
+    for (int i = tid; i < kExtraGroup * Dv; i += 256) {
+        const int e = i / Dv, d = i % Dv;
+        evt[e * vstr + d] = e < ne ? ev[(((long long)b * g.n_extra + e0 + e) * g.Hkv + hk) * Dv + d] : T(0.f);
+    }
+
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc_k, acc_v;
+    wmma::fill_fragment(acc_k, 0.f);
+    wmma::fill_fragment(acc_v, 0.f);
+    const float scale = (float)g.scale;
+    const long long total = g.otot * g.group;
+    long long end = (long long)(seg + 1) * kExtraSegRows;
+    if (end > total) end = total;
+
+    for (long long base = (long long)seg * kExtraSegRows; base < end; base += kExtraTileRows) {
+        __syncthreads();                                        // the previous tile has been consumed
+        bool mine_inside = false;
+        if (tid < kExtraTileRows) {
+            const long long cnd = base + tid;
+            long long qo = -1, ro = 0;
+            if (cnd < end) {
+                const int gi = (int)(cnd / g.otot);
+                QueryCtx c;
+                decode_query(g, ((long long)b * g.otot + cnd % g.otot) * g.Hq + hk * g.group + gi, c);
+                if (c.inside) {
+                    qo = c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
+                    ro = c.row;
+                    mine_inside = true;
+                }
+            }
+            qoff[tid] = qo;
+            orow[tid] = ro;
+            rl[tid] = mine_inside ? lse[ro] : 0.f;
+            rd[tid] = mine_inside ? delta[ro] - (dlse ? dlse[ro] : 0.f) : 0.f;
+        }
+        if (!__syncthreads_or(mine_inside ? 1 : 0)) continue;   // nothing of this tile is inside its sample
+        // ---- stage the rows (16 bytes at a time; rows outside are zero) ----
+        for (int i = tid; i < kExtraTileRows * (D / 8); i += 256) {
+            const int r = i / (D / 8), c8 = i % (D / 8);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (qoff[r] >= 0) v = *reinterpret_cast<const uint4*>(q + qoff[r] + 8 * c8);
+            *reinterpret_cast<uint4*>(qt + r * qstr + 8 * c8) = v;
+        }
+        for (int i = tid; i < kExtraTileRows * (Dv / 8); i += 256) {
+            const int r = i / (Dv / 8), c8 = i % (Dv / 8);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (qoff[r] >= 0) v = *reinterpret_cast<const uint4*>(dout + orow[r] * Dv + 8 * c8);
+            *reinterpret_cast<uint4*>(gt + r * vstr + 8 * c8) = v;
+        }
+        __syncthreads();
+        // ---- phase 1: S (warps 0-3) and dP (warps 4-7), one block of 16 rows each ----
+        {
+            const int mt = warp & 3;
+            const bool second = warp >= 4;
+            const T* rows = (second ? gt : qt) + 16 * mt * (second ? vstr : qstr);
+            const T* toks = second ? evt : ekt;
+            const int str = second ? vstr : qstr, depth = second ? Dv : D;
+            wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
+            wmma::fill_fragment(c, 0.f);
+            for (int k = 0; k < depth; k += 16) {
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> a;
+                wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::col_major> bm;
+                wmma::load_matrix_sync(a, rows + k, str);
+                wmma::load_matrix_sync(bm, toks + k, str);      // B(k, token) = toks[token][k]
+                wmma::mma_sync(c, a, bm, c);
+            }
+            wmma::store_matrix_sync((second ? dbuf : sbuf) + 16 * mt * kExtraGroup, c, kExtraGroup, wmma::mem_row_major);
+        }
+        __syncthreads();
+        // ---- probabilities and dS: thread = (row, 4 tokens) ----
+        {
+            const int r = tid >> 2, t0 = 4 * (tid & 3);
+            const bool live = qoff[r] >= 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool on = live && t0 + j < ne;
+                const float pj = on ? expf(sbuf[r * kExtraGroup + t0 + j] * scale - rl[r]) : 0.f;
+                const float dj = on ? pj * (dbuf[r * kExtraGroup + t0 + j] - rd[r]) * scale : 0.f;
+                pt[r * kPStr + t0 + j] = T(pj);
+                dst[r * kPStr + t0 + j] = T(dj);
+            }
+        }
+        __syncthreads();
+        // ---- phase 2: warp w owns channels 16w .. 16w+15 of dEk and of dEv ----
+        for (int k = 0; k < kExtraTileRows; k += 16) {
+            wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::col_major> a;      // A(token, row) = w[row][token]
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> bm;
+            if (16 * warp < D) {
+                wmma::load_matrix_sync(a, dst + k * kPStr, kPStr);
+                wmma::load_matrix_sync(bm, qt + k * qstr + 16 * warp, qstr);
+                wmma::mma_sync(acc_k, a, bm, acc_k);
+            }
+            if (16 * warp < Dv) {
+                wmma::load_matrix_sync(a, pt + k * kPStr, kPStr);
+                wmma::load_matrix_sync(bm, gt + k * vstr + 16 * warp, vstr);
+                wmma::mma_sync(acc_v, a, bm, acc_v);
+            }
+        }
+    }
+    // ---- this block's partial sums: [token][D | Dv], through shared memory ----
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(smem_raw);            // [16][W], over the row tiles
+    if (16 * warp < D) wmma::store_matrix_sync(red + 16 * warp, acc_k, W, wmma::mem_row_major);
+    if (16 * warp < Dv) wmma::store_matrix_sync(red + D + 16 * warp, acc_v, W, wmma::mem_row_major);
+    __syncthreads();
+    float* out = partial + ((((long long)b * g.Hkv + hk) * gridDim.x + seg) * kExtraGroup) * W;
+    for (int i = tid; i < ne * W; i += 256) out[i] = red[i];
+}
+
 inline int extra_segments(const Geo& g) { return (int)((g.otot * g.group + kExtraSegRows - 1) / kExtraSegRows); }
 
 // Fast path for the additional tokens' gradients; returns false when it does not apply.
@@ -1247,7 +1394,15 @@ bool launch_extra_fast(const Geo& g, const void* q, const void* ek, const void* 
             // rows must be readable 16 bytes at a time
             const bool aligned = g.D % 8 == 0 && g.Dv % 8 == 0 && g.qs[0] % 8 == 0 && g.qs[1] % 8 == 0 && g.qs[2] % 8 == 0 &&
                                  ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(dout)) & 15u) == 0;
-            if (aligned) {
+            if (aligned && g.D % 16 == 0 && g.Dv % 16 == 0) {        // warp-level tensor-core products
+                const size_t msmem = (size_t)(kExtraTileRows + kExtraGroup) * (g.D + 8 + g.Dv + 8) * sizeof(T) +
+                                     (size_t)2 * kExtraTileRows * (kExtraGroup + 8) * sizeof(T) +
+                                     (size_t)kExtraTileRows * (2 * kExtraGroup + 2) * sizeof(float) + (size_t)kExtraTileRows * 2 * sizeof(long long);
+                ensure_dynamic_smem((const void*)extra_grad_mma_kernel<T>, 96 * 1024);
+                extra_grad_mma_kernel<T><<<grid, 256, msmem, s>>>(g, (const T*)q, (const T*)ek, (const T*)ev, (const float*)lse,
+                    (const float*)delta, (const T*)dout, (const float*)dlse, (float*)partial, e0, ne);
+                tiled = true;
+            } else if (aligned) {
                 const size_t tsmem = (size_t)kExtraTileRows * (g.D + 8 + g.Dv + 8) * sizeof(T) + (size_t)kExtraGroup * W * sizeof(float) +
                                      (size_t)kExtraTileRows * (2 * kExtraGroup + 2) * sizeof(float) + (size_t)kExtraTileRows * 2 * sizeof(long long);
                 ensure_dynamic_smem((const void*)extra_grad_tile_kernel<T>, 96 * 1024);
