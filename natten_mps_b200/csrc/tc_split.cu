@@ -97,7 +97,9 @@ __device__ __forceinline__ bool split_row(const TcParams& P, const SplitGeo& G, 
     return valid;
 }
 
-template <int DH, bool BF16>
+// kInner = 16: the chunk's innermost extent is 16 columns (every 16 columns of a chunk are one inner row whose
+// slots are consecutive: static offsets from one pointer per row); 0: any geometry (slot table per column).
+template <int DH, bool BF16, int kInner>
 __global__ void __launch_bounds__(kThreads, (DH == 64 ? 2 : 1))
 tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ TcParams P, uint16_t* __restrict__ out, float scale, uint32_t fill16,
@@ -276,7 +278,23 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 uint32_t s[32];
                 tmem_ld32(trow + 64 * team + 32 * pc, s);
                 tmem_ld_wait();
-                if (ok) {
+                if (ok && kInner == 16) {
+                    // two inner rows of 16 columns: column j2 of a row goes to slot (row's first slot) + j2
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const uint32_t bits = (words[pc] >> (16 * rr)) & 0xFFFFu;
+                        if (bits == 0u) continue;
+                        const int r = 4 * team + 2 * pc + rr;                    // inner row of the chunk
+                        const int i0 = ci[0] * P.cb[0] + (r >> P.cb1_log), i1 = ci[1] * P.cb[1] + (r & (P.cb[1] - 1));
+                        uint16_t* rowp = myrow + ((i0 - fs[0]) * P.K[1] + (i1 - fs[1])) * P.K[2] + (ci[2] * 16 - fs[2]);
+#pragma unroll
+                        for (int i = 0; i < 16; i += 2) {
+                            const uint32_t both = cvt_pack<BF16>(__uint_as_float(s[16 * rr + i]) * scale, __uint_as_float(s[16 * rr + i + 1]) * scale);
+                            if ((bits >> i) & 1u) rowp[i] = static_cast<uint16_t>(both & 0xFFFFu);
+                            if ((bits >> (i + 1)) & 1u) rowp[i + 1] = static_cast<uint16_t>(both >> 16);
+                        }
+                    }
+                } else if (ok) {
                     const int* cs = colslot + 64 * team + 32 * pc;
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {     // pairs: one conversion for two columns
@@ -317,14 +335,26 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     }
 }
 
+template <int DH, bool BF16, int kInner>
+int launch_scores_inner(const Plan& plan, const CUtensorMap& mx, const CUtensorMap& my, const Geo& g, void* out,
+                        float scale, bool neg_inf, cudaStream_t s);
+
 template <int DH, bool BF16>
 int launch_scores(const Plan& plan, const CUtensorMap& mx, const CUtensorMap& my, const Geo& g, void* out,
                   float scale, bool neg_inf, cudaStream_t s)
 {
+    return plan.p.cb[2] == 16 ? launch_scores_inner<DH, BF16, 16>(plan, mx, my, g, out, scale, neg_inf, s)
+                              : launch_scores_inner<DH, BF16, 0>(plan, mx, my, g, out, scale, neg_inf, s);
+}
+
+template <int DH, bool BF16, int kInner>
+int launch_scores_inner(const Plan& plan, const CUtensorMap& mx, const CUtensorMap& my, const Geo& g, void* out,
+                        float scale, bool neg_inf, cudaStream_t s)
+{
     using SM = SmemS<DH>;
     const size_t smem = (size_t)SM::kOut + (size_t)kTileRows * g.ktot * 2;
     if (smem > kMaxDynamicSmem) return -2;
-    if (ensure_dynamic_smem((const void*)tc_scores_kernel<DH, BF16>, kMaxDynamicSmem) != cudaSuccess) {
+    if (ensure_dynamic_smem((const void*)tc_scores_kernel<DH, BF16, kInner>, kMaxDynamicSmem) != cudaSuccess) {
         cudaGetLastError();
         return -2;
     }
@@ -332,7 +362,7 @@ int launch_scores(const Plan& plan, const CUtensorMap& mx, const CUtensorMap& my
     for (int a = 0; a < 3; ++a) ngroups *= plan.p.grp_n[a];
     const dim3 grid((unsigned)(plan.p.ntiles * ngroups), (unsigned)g.Hq, (unsigned)g.B);
     const uint32_t fill = neg_inf ? (BF16 ? 0xFF80u : 0xFC00u) : 0u;
-    tc_scores_kernel<DH, BF16><<<grid, kThreads, smem, s>>>(mx, my, plan.p, (uint16_t*)out, scale, fill, g.ktot);
+    tc_scores_kernel<DH, BF16, kInner><<<grid, kThreads, smem, s>>>(mx, my, plan.p, (uint16_t*)out, scale, fill, g.ktot);
     tc_count_launch();
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? 0 : (int)err;
@@ -360,7 +390,7 @@ struct SmemA {
     static constexpr uint32_t kTmemCols = 256;
 };
 
-template <int DH, bool BF16>
+template <int DH, bool BF16, int kInner>
 __global__ void __launch_bounds__(kThreads, (DH == 64 ? 2 : 1))
 tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__ TcParams P,
                 const uint16_t* __restrict__ w, uint16_t* __restrict__ out, float scale, int ktot,
@@ -496,7 +526,23 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
 #pragma unroll
             for (int pc = 0; pc < 2; ++pc) {
                 uint32_t packed[16];
-                if (__any_sync(0xffffffffu, words[pc] != 0u)) {
+                if (kInner == 16 && __any_sync(0xffffffffu, words[pc] != 0u)) {
+                    // two inner rows of 16 columns: column j2 of a row reads slot (row's first slot) + j2
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const uint32_t bits = (words[pc] >> (16 * rr)) & 0xFFFFu;
+                        const int r = 4 * team + 2 * pc + rr;                    // inner row of the chunk
+                        const int i0 = ci[0] * P.cb[0] + (r >> P.cb1_log), i1 = ci[1] * P.cb[1] + (r & (P.cb[1] - 1));
+                        const uint16_t* rowp = myrow + ((i0 - fs[0]) * P.K[1] + (i1 - fs[1])) * P.K[2] + (ci[2] * 16 - fs[2]);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            uint32_t lo16 = 0u, hi16 = 0u;
+                            if ((bits >> (2 * i)) & 1u) lo16 = rowp[2 * i];
+                            if ((bits >> (2 * i + 1)) & 1u) hi16 = rowp[2 * i + 1];
+                            packed[8 * rr + i] = lo16 | (hi16 << 16);
+                        }
+                    }
+                } else if (__any_sync(0xffffffffu, words[pc] != 0u)) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int c0 = 64 * team + 32 * pc + 2 * i;
@@ -548,21 +594,33 @@ tc_apply_kernel(const __grid_constant__ CUtensorMap tmY, const __grid_constant__
     }
 }
 
+template <int DH, bool BF16, int kInner>
+int launch_apply_inner(const Plan& plan, const CUtensorMap& my, const Geo& g, const void* w, void* out, float scale,
+                       bool out_by_position, cudaStream_t s);
+
 template <int DH, bool BF16>
 int launch_apply(const Plan& plan, const CUtensorMap& my, const Geo& g, const void* w, void* out, float scale,
                  bool out_by_position, cudaStream_t s)
 {
+    return plan.p.cb[2] == 16 ? launch_apply_inner<DH, BF16, 16>(plan, my, g, w, out, scale, out_by_position, s)
+                              : launch_apply_inner<DH, BF16, 0>(plan, my, g, w, out, scale, out_by_position, s);
+}
+
+template <int DH, bool BF16, int kInner>
+int launch_apply_inner(const Plan& plan, const CUtensorMap& my, const Geo& g, const void* w, void* out, float scale,
+                       bool out_by_position, cudaStream_t s)
+{
     using SM = SmemA<DH>;
     const size_t smem = (size_t)SM::kW + (size_t)kTileRows * g.ktot * 2;
     if (smem > kMaxDynamicSmem) return -2;
-    if (ensure_dynamic_smem((const void*)tc_apply_kernel<DH, BF16>, kMaxDynamicSmem) != cudaSuccess) {
+    if (ensure_dynamic_smem((const void*)tc_apply_kernel<DH, BF16, kInner>, kMaxDynamicSmem) != cudaSuccess) {
         cudaGetLastError();
         return -2;
     }
     int ngroups = 1;
     for (int a = 0; a < 3; ++a) ngroups *= plan.p.grp_n[a];
     const dim3 grid((unsigned)(plan.p.ntiles * ngroups), (unsigned)g.Hq, (unsigned)g.B);
-    tc_apply_kernel<DH, BF16><<<grid, kThreads, smem, s>>>(my, plan.p, (const uint16_t*)w, (uint16_t*)out, scale, g.ktot,
+    tc_apply_kernel<DH, BF16, kInner><<<grid, kThreads, smem, s>>>(my, plan.p, (const uint16_t*)w, (uint16_t*)out, scale, g.ktot,
                                                          out_by_position ? 1 : 0);
     tc_count_launch();
     const cudaError_t err = cudaGetLastError();
