@@ -199,12 +199,20 @@ int natten_qk_rpb_fwd(const natten_params_t* p, const void* q, const void* k, co
                       void* stream)
 {
     if (!rpb) return NATTEN_E_INVALID;
-    int rc = natten_qk_fwd(p, q, k, logits, stream);
-    if (rc) return rc;
     Geo g;
-    rc = make_geo(p, g);
+    int rc = make_geo(p, g);
     if (rc) return rc;
     if (g.B == 0) return NATTEN_OK;
+    // tensor-core kernel: the bias is added while the logits tile is written out (one pass over the logits)
+    if (q && k && logits && !g.extents && !g.n_extra && !(p->flags & NATTEN_FLAG_FORCE_SIMT)) {
+        rc = tc_scores(p->dtype, g, q, g.qs, k, g.ks, g.has_scale ? (float)g.scale : 1.f, true, logits,
+                       (cudaStream_t)stream, rpb);
+        if (rc == 0) { t_last_path = NATTEN_PATH_TCGEN05; return NATTEN_OK; }
+        if (rc > 0) return rc;
+    }
+    // otherwise the logits first, then the bias in a second pass
+    rc = natten_qk_fwd(p, q, k, logits, stream);
+    if (rc) return rc;
     simt_count_launch(1);
     return rpb_add(p->dtype, g, rpb, logits, (cudaStream_t)stream);
 }

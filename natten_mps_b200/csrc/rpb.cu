@@ -121,7 +121,7 @@ long long table_size(const Geo& g)
 bool supported(const Geo& g)
 {
     for (int a = 0; a < g.rank; ++a)
-        if (g.st[a] != 1 || g.causal[a]) return false;
+        if (g.st[a] != 1 || g.causal[a] || (g.K[a] & 1) == 0) return false;     // even kernels index past the table
     return g.extents == nullptr && g.n_extra == 0 && g.Hq == g.Hkv;
 }
 

@@ -18,8 +18,10 @@ int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const vo
 size_t tc_bwd_workspace_bytes(int dtype, const Geo& g);
 // out[row, slot] = scale * <x[row], y[key of slot]> (QK forward; AV backward w.r.t. attn).  x is indexed by
 // input position with strides xs (batch, token, head); masked slots get -inf (neg_inf) or 0.
+// With `rpb` (a relative position bias table [Hq, 2K-1, ...], unit stride, no causal axis) the bias of every slot is
+// added while the finished tile is written out.
 int tc_scores(int dtype, const Geo& g, const void* x, const long long xs[3], const void* y, const long long ys[3],
-              float scale, bool neg_inf, void* out, cudaStream_t s);
+              float scale, bool neg_inf, void* out, cudaStream_t s, const void* rpb = nullptr);
 // out[row] = scale * sum_slot w[row, slot] * y[key of slot] (AV forward; QK backward w.r.t. q).
 int tc_apply(int dtype, const Geo& g, const void* w, const void* y, const long long ys[3], float scale,
              bool out_by_position, void* out, cudaStream_t s);

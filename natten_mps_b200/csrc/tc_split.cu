@@ -103,7 +103,7 @@ template <int DH, bool BF16, int kInner>
 __global__ void __launch_bounds__(kThreads, (DH == 64 ? 2 : 1))
 tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ TcParams P, uint16_t* __restrict__ out, float scale, uint32_t fill16,
-                 int ktot)
+                 int ktot, const uint16_t* __restrict__ rpb, int rpb_table)
 {
     using SM = SmemS<DH>;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -149,6 +149,9 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     int* colslot = reinterpret_cast<int*>(smem + SM::kColSlot);
     long long* rowout = reinterpret_cast<long long*>(smem + SM::kRowOut);
     uint16_t* tile = reinterpret_cast<uint16_t*>(smem + SM::kOut);
+    // relative position bias (optional): per row the first bias entry of its window, per slot its offset from there
+    int* rowpb = reinterpret_cast<int*>(smem + SM::kOut + ((kTileRows * ktot * 2 + 15) & ~15));
+    int* slotpb = rowpb + kTileRows;
     const uint32_t bar_x = sbase + SM::kBar + 0;
     const uint32_t bar_y = sbase + SM::kBar + 8;        // [3]
     const uint32_t bar_s = sbase + SM::kBar + 32;
@@ -212,6 +215,31 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
         if (!valid_q) { e[0] = f[0]; e[1] = f[1]; e[2] = f[2]; }
         if (team == 0) rowout[row] = valid_q ? (((long long)b * P.otot + oflat) * P.Hq + h) * ktot : -1;   // element offset
+        if (rpb) {                               // unit stride, no causal axis: the bias window start of the reference
+            if (team == 0) {
+                int pbi = 0;
+#pragma unroll
+                for (int a = 0; a < 3; ++a) {
+                    const int pa = rg[a] + P.dil[a] * (x0[a] + sx[a] * (origin[a] + qi[a]));
+                    const int K = P.K[a], nh = K / 2, L = P.L[a], d = P.dil[a];
+                    int pb;
+                    if (d <= 1) pb = nh + (pa < nh ? nh - pa : (pa + nh >= L ? L - pa - 1 - nh : 0));
+                    else pb = pa - nh * d < 0 ? K - 1 - pa / d : (pa + nh * d >= L ? (L - pa - 1) / d : nh);
+                    pbi = pbi * (2 * K - 1) + pb;
+                }
+                rowpb[row] = pbi;
+            }
+            for (int j = tid; j < ktot; j += 256) {
+                int rem = j, off = 0, mul = 1;
+#pragma unroll
+                for (int a = 2; a >= 0; --a) {
+                    off += (rem % P.K[a]) * mul;
+                    rem /= P.K[a];
+                    mul *= 2 * P.K[a] - 1;
+                }
+                slotpb[j] = off;
+            }
+        }
         // column jj of a chunk sits at box offset (j0, j1, j2): its slot relative to the chunk's first column
         if (tid < 128) {
             const int j2 = tid & (P.cb[2] - 1);
@@ -317,7 +345,16 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             const int total = kTileRows * ktot;
             for (int idx = tid; idx < total; idx += 256) {
                 const long long off = rowout[r];
-                if (off >= 0) out[off + j] = tile[idx];
+                if (off >= 0) {
+                    uint16_t v = tile[idx];
+                    if (rpb) {                   // masked slots hold -inf and stay -inf
+                        const uint32_t bv = rpb[(long long)h * rpb_table + rowpb[r] + slotpb[j]];
+                        const float x = BF16 ? __uint_as_float(static_cast<uint32_t>(v) << 16) : __half2float(__ushort_as_half(v));
+                        const float y = BF16 ? __uint_as_float(bv << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(bv)));
+                        v = static_cast<uint16_t>(cvt_pack<BF16>(x + y, 0.f) & 0xFFFFu);
+                    }
+                    out[off + j] = v;
+                }
                 r += dr;
                 j += dj;
                 if (j >= ktot) { j -= ktot; ++r; }
@@ -337,22 +374,22 @@ tc_scores_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 
 template <int DH, bool BF16, int kInner>
 int launch_scores_inner(const Plan& plan, const CUtensorMap& mx, const CUtensorMap& my, const Geo& g, void* out,
-                        float scale, bool neg_inf, cudaStream_t s);
+                        float scale, bool neg_inf, cudaStream_t s, const void* rpb, int rpb_table);
 
 template <int DH, bool BF16>
 int launch_scores(const Plan& plan, const CUtensorMap& mx, const CUtensorMap& my, const Geo& g, void* out,
-                  float scale, bool neg_inf, cudaStream_t s)
+                  float scale, bool neg_inf, cudaStream_t s, const void* rpb, int rpb_table)
 {
-    return plan.p.cb[2] == 16 ? launch_scores_inner<DH, BF16, 16>(plan, mx, my, g, out, scale, neg_inf, s)
-                              : launch_scores_inner<DH, BF16, 0>(plan, mx, my, g, out, scale, neg_inf, s);
+    return plan.p.cb[2] == 16 ? launch_scores_inner<DH, BF16, 16>(plan, mx, my, g, out, scale, neg_inf, s, rpb, rpb_table)
+                              : launch_scores_inner<DH, BF16, 0>(plan, mx, my, g, out, scale, neg_inf, s, rpb, rpb_table);
 }
 
 template <int DH, bool BF16, int kInner>
 int launch_scores_inner(const Plan& plan, const CUtensorMap& mx, const CUtensorMap& my, const Geo& g, void* out,
-                        float scale, bool neg_inf, cudaStream_t s)
+                        float scale, bool neg_inf, cudaStream_t s, const void* rpb, int rpb_table)
 {
     using SM = SmemS<DH>;
-    const size_t smem = (size_t)SM::kOut + (size_t)kTileRows * g.ktot * 2;
+    const size_t smem = (size_t)SM::kOut + (((size_t)kTileRows * g.ktot * 2 + 15) & ~(size_t)15) + (rpb ? 4 * (kTileRows + (size_t)g.ktot) : 0);
     if (smem > kMaxDynamicSmem) return -2;
     if (ensure_dynamic_smem((const void*)tc_scores_kernel<DH, BF16, kInner>, kMaxDynamicSmem) != cudaSuccess) {
         cudaGetLastError();
@@ -362,7 +399,8 @@ int launch_scores_inner(const Plan& plan, const CUtensorMap& mx, const CUtensorM
     for (int a = 0; a < 3; ++a) ngroups *= plan.p.grp_n[a];
     const dim3 grid((unsigned)(plan.p.ntiles * ngroups), (unsigned)g.Hq, (unsigned)g.B);
     const uint32_t fill = neg_inf ? (BF16 ? 0xFF80u : 0xFC00u) : 0u;
-    tc_scores_kernel<DH, BF16, kInner><<<grid, kThreads, smem, s>>>(mx, my, plan.p, (uint16_t*)out, scale, fill, g.ktot);
+    tc_scores_kernel<DH, BF16, kInner><<<grid, kThreads, smem, s>>>(mx, my, plan.p, (uint16_t*)out, scale, fill, g.ktot,
+                                                                   (const uint16_t*)rpb, rpb_table);
     tc_count_launch();
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? 0 : (int)err;
@@ -883,8 +921,16 @@ int launch_gather(const Plan& plan, const CUtensorMap& mx, const Geo& g, const v
 // x: the row tensor [B, *L, Hq, D] with strides xs (batch, token, head), indexed by input position;
 // y: the key-side tensor [B, *L, Hkv, D] with strides ys.  out: [B, *O, Hq, ktot].
 int tc_scores(int dtype, const Geo& g, const void* x, const long long xs[3], const void* y, const long long ys[3],
-              float scale, bool neg_inf, void* out, cudaStream_t s)
+              float scale, bool neg_inf, void* out, cudaStream_t s, const void* rpb)
 {
+    int rpb_table = 1;
+    if (rpb) {                                   // bias added while the tile is written out: unit stride, no causal axis
+        for (int a = 0; a < g.rank; ++a) {
+            if (g.st[a] != 1 || g.causal[a] || (g.K[a] & 1) == 0) return -2;
+            rpb_table *= 2 * g.K[a] - 1;
+        }
+        if (g.Hq != g.Hkv) return -2;
+    }
     if (dtype != 1 && dtype != 2) return -2;
     if (g.D != 64 && g.D != 128) return -2;
     if (g.extents || g.n_extra) return -2;
@@ -899,7 +945,7 @@ int tc_scores(int dtype, const Geo& g, const void* x, const long long xs[3], con
     // the [128 x slots] tile must fit beside the operand stages (two CTAs per SM at D = 64)
     const size_t budget = g.D == 64 ? 113 * 1024 : 227 * 1024;
     const size_t base = g.D == 64 ? (size_t)SmemS<64>::kOut : (size_t)SmemS<128>::kOut;
-    if (base + (size_t)kTileRows * g.ktot * 2 > budget) return -2;
+    if (base + (size_t)kTileRows * g.ktot * 2 + 16 + (rpb ? 4 * (kTileRows + (size_t)g.ktot) : 0) > budget) return -2;
     Plan plan;
     if (!make_plan(g, plan, kChunk, /*with_stride=*/true)) return -2;
     const bool bf16 = dtype == 2;
@@ -911,10 +957,10 @@ int tc_scores(int dtype, const Geo& g, const void* x, const long long xs[3], con
     if (!plan.p.status) return -2;
     if (plan.p.work_q == 0) return 0;
     if (g.D == 64)
-        return bf16 ? launch_scores<64, true>(plan, mx, my, g, out, scale, neg_inf, s)
-                    : launch_scores<64, false>(plan, mx, my, g, out, scale, neg_inf, s);
-    return bf16 ? launch_scores<128, true>(plan, mx, my, g, out, scale, neg_inf, s)
-                : launch_scores<128, false>(plan, mx, my, g, out, scale, neg_inf, s);
+        return bf16 ? launch_scores<64, true>(plan, mx, my, g, out, scale, neg_inf, s, rpb, rpb_table)
+                    : launch_scores<64, false>(plan, mx, my, g, out, scale, neg_inf, s, rpb, rpb_table);
+    return bf16 ? launch_scores<128, true>(plan, mx, my, g, out, scale, neg_inf, s, rpb, rpb_table)
+                : launch_scores<128, false>(plan, mx, my, g, out, scale, neg_inf, s, rpb, rpb_table);
 }
 
 // w: [B, *O, Hq, ktot]; y: [B, *L, Hkv, D] with strides ys; out: [B, *O, Hq, D] (by output row) or, for a

@@ -259,6 +259,10 @@ def _na_qk_rpb(rank, query, key, rpb, kernel_size, dilation, scale):
     spatial = tuple(query.shape[1:1 + rank])
     check_kernel_size_vs_input(ks, spatial)
     check_dilation_kernel_vs_input(dil, ks, spatial)
+    if any(x % 2 == 0 for x in ks):
+        # with an even kernel the bias window start reaches K, so start + slot runs one past the 2K-1 entries
+        # (the reference's table lookup fails there as well)
+        raise ValueError("relative position bias needs odd kernel sizes.")
     want = (query.shape[-2], *[2 * x - 1 for x in ks])
     if tuple(rpb.shape) != want:
         raise ValueError(f"rpb must have shape {list(want)} for {rank}D.")

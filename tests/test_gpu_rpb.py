@@ -6,13 +6,13 @@ import pytest
 import torch
 
 import oracle
-from natten_mps_b200 import functional as F
+from natten_mps_b200 import _cabi, functional as F
 from natten_mps_b200.compat import v014
 from tests import _golden as G
 from tests._gpu_util import TOL, dev, rounded
 
 pytestmark = pytest.mark.gpu
-FN = {1: F.na1d_qk_rpb, 2: F.na2d_qk_rpb}
+FN = {1: F.na1d_qk_rpb, 2: F.na2d_qk_rpb, 3: F.na3d_qk_rpb}
 
 
 @pytest.mark.parametrize("dtype", [torch.float64, torch.float32, torch.bfloat16, torch.float16],
@@ -36,6 +36,54 @@ def test_rpb_against_golden_and_oracle(case, dtype):
     if dtype == torch.float64:                                  # the reference's own numbers
         for name, got in (("logits", logits), ("dq", dq), ("dk", dk), ("drpb", drpb)):
             assert np.abs(got.detach().cpu().numpy() - a[name]).max() < 1e-10, name
+
+
+TC_CASES = [
+    # rank, spatial, kernel, dilation
+    (1, (120,), (9,), (2,)),
+    (2, (24, 20), (7, 5), (1, 1)),
+    (2, (30, 28), (5, 5), (2, 2)),
+    (3, (4, 10, 12), (3, 5, 5), (1, 1, 1)),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", TC_CASES, ids=lambda c: "x".join(map(str, c[1])) + f"_k{c[2][-1]}_d{c[3][-1]}")
+def test_rpb_inside_the_tensor_core_kernel(case, dtype):
+    """Head dim 64 in 16-bit: the bias is added while the tensor-core kernel writes its logits tile out
+    (no second pass); compared with the oracle on the rounded inputs and with the two-pass SIMT path."""
+    rank, spatial, K, dil = case
+    g = torch.Generator().manual_seed(41)
+    B, H, D = 2, 2, 64
+    q = torch.randn((B, *spatial, H, D), generator=g).to(dtype).cuda()
+    k = torch.randn((B, *spatial, H, D), generator=g).to(dtype).cuda()
+    rpb = torch.randn((H, *[2 * kk - 1 for kk in K]), generator=g).to(dtype).cuda()
+    got = FN[rank](q, k, rpb, K, dil)
+    assert _cabi.last_path() == "tcgen05"
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0
+    f = lambda t: t.double().cpu().numpy()
+    want = oracle.na_qk_rpb(f(q), f(k), f(rpb), kernel_size=K, dilation=dil)
+    g64 = f(got)
+    assert np.array_equal(np.isinf(g64), np.isinf(want))
+    fin = np.isfinite(want)
+    err = np.abs(g64[fin] - want[fin]).max()
+    bound = TOL[dtype] * max(1.0, np.abs(want[fin]).max())
+    assert err <= bound, (err, bound)
+    try:
+        _cabi.set_force("simt")
+        two_pass = FN[rank](q, k, rpb, K, dil)
+        assert _cabi.last_path() == "simt"
+    finally:
+        _cabi.set_force(None)
+    d = (got.float() - two_pass.float())[torch.isfinite(two_pass)].abs().max().item()
+    assert d <= bound, d
+
+
+def test_rpb_rejects_even_kernels():
+    q = torch.randn(1, 12, 2, 16, device="cuda")
+    with pytest.raises(ValueError, match="odd kernel sizes"):
+        F.na1d_qk_rpb(q, q, torch.randn(2, 7, device="cuda"), 4)
 
 
 def test_compat_wrappers_are_heads_first():
