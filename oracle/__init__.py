@@ -239,6 +239,8 @@ def na_qk_rpb(q, k, rpb, kernel_size, dilation=1, scale=None, dtype=np.float64):
     """Split QK plus relative position bias (``compat/v014.py:66-183``, heads-last layout)."""
     logits = na_qk(q, k, kernel_size, dilation=dilation, scale=scale, dtype=dtype)
     rank = q.ndim - 3
+    if any(int(x) % 2 == 0 for x in np.broadcast_to(np.asarray(kernel_size), (rank,))):
+        raise ValueError("relative position bias needs odd kernel sizes (the lookup runs past the table otherwise)")
     (rpb,) = _prep(dtype, rpb)
     c = _Call(rank, q.shape, k.shape[-2], q.shape[-1], kernel_size, 1, dilation, False, 1.0, 0, None, 0)
     fn = getattr(_load(), "ora_rpb_add" + _suffix(dtype))
