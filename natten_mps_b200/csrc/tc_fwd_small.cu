@@ -51,29 +51,43 @@ __device__ long long g_trace_small[8 * 512];
 
 namespace {
 
-constexpr int DH = 64;
 constexpr int kKeys = 64;                   // keys per chunk
 constexpr int kKeysLog = 6;
 constexpr int kStages = 2;
 constexpr int kThreads = 160;               // 4 softmax warps + 1 warp that loads and issues
-constexpr int kQBytes = kTileRows * 128;    // [128 x 64] 16-bit
-constexpr int kKVBytes = kKeys * 128;       // [64 x 64] 16-bit
-constexpr int kOffQ = 0, kOffK = kQBytes, kOffV = kQBytes + kStages * kKVBytes;
-constexpr int kBar = kQBytes + 2 * kStages * kKVBytes;
 constexpr int kHdrSlots = 3;                // tile headers published by the issuing warp
 constexpr int kHdrBytes = 144;
-constexpr int kHdr = kBar + 128;
-constexpr int kSmemTotal = kHdr + kHdrSlots * kHdrBytes;
 static_assert(sizeof(FwdTile) <= kHdrBytes, "header slot too small");
-constexpr uint32_t kColS = 0, kColO = 64, kTmemCols = 128;
+constexpr uint32_t kColS = 0, kColO = 64;
 
-template <bool BF16, int kInner>
-__global__ void __launch_bounds__(kThreads, 4)
+// Shared memory and TMEM of one CTA for head dim DH (64: four CTAs per SM, 128 TMEM columns; 128: two CTAs per
+// SM, 256 TMEM columns).  Tiles are stored as blocks of 64 channels (128-byte rows, 128-byte swizzle).
+template <int DH>
+struct FwdSmall {
+    static constexpr int kHalves = DH / 64;
+    static constexpr int kQHalf = kTileRows * 128;          // [128 x 64] 16-bit
+    static constexpr int kKVHalf = kKeys * 128;             // [64 x 64] 16-bit
+    static constexpr int kQBytes = kQHalf * kHalves;
+    static constexpr int kKVBytes = kKVHalf * kHalves;
+    static constexpr int kOffQ = 0, kOffK = kQBytes, kOffV = kQBytes + kStages * kKVBytes;
+    static constexpr int kBar = kQBytes + 2 * kStages * kKVBytes;
+    static constexpr int kHdr = kBar + 128;
+    static constexpr int kSmemTotal = kHdr + kHdrSlots * kHdrBytes;
+    static constexpr uint32_t kTmemCols = DH == 64 ? 128 : 256;     // S 64 + O DH, rounded up to a power of two
+    static constexpr int kPerSm = DH == 64 ? 4 : 2;
+};
+
+template <int DH, bool BF16, int kInner>
+__global__ void __launch_bounds__(kThreads, FwdSmall<DH>::kPerSm)
 tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmEK,
                     const __grid_constant__ CUtensorMap tmEV, const __grid_constant__ TcParams P,
                     uint16_t* __restrict__ out, float* __restrict__ lse)
 {
+    using FS = FwdSmall<DH>;
+    constexpr int kHalves = FS::kHalves, kQHalf = FS::kQHalf, kKVHalf = FS::kKVHalf, kQBytes = FS::kQBytes, kKVBytes = FS::kKVBytes;
+    constexpr int kOffQ = FS::kOffQ, kOffK = FS::kOffK, kOffV = FS::kOffV, kBar = FS::kBar, kHdr = FS::kHdr;
+    constexpr uint32_t kTmemCols = FS::kTmemCols;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef NATTEN_TRACE
@@ -179,10 +193,12 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     if (!ok) return false;
                     if (lane == 0) {
                         mbar_expect_tx(bar_q, kQBytes + ((P.inject == 1 && tl == 0) ? 16u : 0u));
-                        tma_load_heads(sbase + kOffQ, &tmQ, bar_q, P, DH, H->h * DH,
-                                    H->rg[2] + P.dil[2] * (H->x0[2] + H->sx[2] * H->origin[2]),
-                                    H->rg[1] + P.dil[1] * (H->x0[1] + H->sx[1] * H->origin[1]),
-                                    H->rg[0] + P.dil[0] * (H->x0[0] + H->sx[0] * H->origin[0]), H->b);
+#pragma unroll
+                        for (int hf = 0; hf < kHalves; ++hf)
+                            tma_load_heads(sbase + kOffQ + hf * kQHalf, &tmQ, bar_q, P, DH, H->h * DH + 64 * hf,
+                                        H->rg[2] + P.dil[2] * (H->x0[2] + H->sx[2] * H->origin[2]),
+                                        H->rg[1] + P.dil[1] * (H->x0[1] + H->sx[1] * H->origin[1]),
+                                        H->rg[0] + P.dil[0] * (H->x0[0] + H->sx[0] * H->origin[0]), H->b);
                     }
                     q_loaded = true;
                     return true;
@@ -199,12 +215,18 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         const int X0 = H->rg[0] + P.dil[0] * (H->lo[0] + chunk_coord(P, 0, ldc[0], 0));
                         const int X1 = H->rg[1] + P.dil[1] * (H->lo[1] + chunk_coord(P, 1, ldc[1], 0));
                         const int X2 = H->rg[2] + P.dil[2] * (H->lo[2] + chunk_coord(P, 2, ldc[2], 0));
-                        tma_load_heads(sbase + kOffK + s * kKVBytes, &tmK, bar, P, DH, H->hk * DH, X2, X1, X0, H->b);
-                        tma_load_heads(sbase + kOffV + s * kKVBytes, &tmV, bar, P, DH, H->hk * DH, X2, X1, X0, H->b);
+#pragma unroll
+                        for (int hf = 0; hf < kHalves; ++hf) {
+                            tma_load_heads(sbase + kOffK + s * kKVBytes + hf * kKVHalf, &tmK, bar, P, DH, H->hk * DH + 64 * hf, X2, X1, X0, H->b);
+                            tma_load_heads(sbase + kOffV + s * kKVBytes + hf * kKVHalf, &tmV, bar, P, DH, H->hk * DH + 64 * hf, X2, X1, X0, H->b);
+                        }
                     } else {                     // additional tokens (rows past n_extra are zero-filled)
                         const int e0 = (cl - H->nnb) * kKeys;
-                        tma_load_heads(sbase + kOffK + s * kKVBytes, &tmEK, bar, P, DH, H->hk * DH, e0, 0, 0, H->b);
-                        tma_load_heads(sbase + kOffV + s * kKVBytes, &tmEV, bar, P, DH, H->hk * DH, e0, 0, 0, H->b);
+#pragma unroll
+                        for (int hf = 0; hf < kHalves; ++hf) {
+                            tma_load_heads(sbase + kOffK + s * kKVBytes + hf * kKVHalf, &tmEK, bar, P, DH, H->hk * DH + 64 * hf, e0, 0, 0, H->b);
+                            tma_load_heads(sbase + kOffV + s * kKVBytes + hf * kKVHalf, &tmEV, bar, P, DH, H->hk * DH + 64 * hf, e0, 0, 0, H->b);
+                        }
                     }
                 }
                 if (cl < H->nnb) { if (++ldc[2] == H->nc[2]) { ldc[2] = 0; if (++ldc[1] == H->nc[1]) { ldc[1] = 0; ++ldc[0]; } } }
@@ -222,15 +244,16 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const int box0[3] = {H->lo[0] + chunk_coord(P, 0, qc[0], 0), H->lo[1] + chunk_coord(P, 1, qc[1], 0),
                                          H->lo[2] + chunk_coord(P, 2, qc[2], 0)};
                     if (lane == 0)
-                        zero_rows_past_extent(P, box0, H->Lp, kKeys, 1, kKVBytes, smem + kOffK + s * kKVBytes, smem + kOffV + s * kKVBytes);
+                        zero_rows_past_extent(P, box0, H->Lp, kKeys, kHalves, kKVHalf, smem + kOffK + s * kKVBytes, smem + kOffV + s * kKVBytes);
                     __syncwarp();
                 }
                 {   // warp-uniform code; the tensor-core instructions execute on the elected lane
                     const uint64_t dk0 = smem_desc(sbase + kOffK + s * kKVBytes, 16, 1024);
                     tc_fence_after();
 #pragma unroll
-                    for (int ks = 0; ks < DH / 16; ++ks)            // 32 bytes per k-step
-                        mma_ss_e(tmem + kColS, dq0 + 2 * ks, dk0 + 2 * ks, idesc_qk, ks > 0, leader);
+                    for (int ks = 0; ks < DH / 16; ++ks)            // 32 bytes per k-step inside a 64-channel block
+                        mma_ss_e(tmem + kColS, dq0 + ((((ks / 4) * kQHalf) + (ks % 4) * 32) >> 4),
+                                 dk0 + ((((ks / 4) * kKVHalf) + (ks % 4) * 32) >> 4), idesc_qk, ks > 0, leader);
                     mma_commit_e(bar_s, leader);
                     if (c + 1 == H->nch) mma_commit_e(bar_qfree, leader);     // last scores of the tile: Q may go once they are done
                 }
@@ -242,7 +265,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 // V read MN-major: 16 key rows per k-step; P sits as 16-bit pairs in the first 32 S columns
                 const int s = n_pv % kStages;
                 {
-                    const uint64_t dv0 = smem_desc(sbase + kOffV + s * kKVBytes, kKVBytes, 1024);
+                    const uint64_t dv0 = smem_desc(sbase + kOffV + s * kKVBytes, kKVHalf, 1024);
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < kKeys / 16; ++ks)
@@ -601,7 +624,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 int tc_fused_fwd_small(int dtype, const Geo& g, const void* q, const void* k, const void* v, const void* ek,
                        const void* ev, void* out, void* lse, cudaStream_t s)
 {
-    if (g.D > 64) return -2;
+    if (g.D > 128) return -2;
     if (!tc_eligible(dtype, g, q, k, v, /*allow_stride=*/true)) return -2;
     if (g.n_extra > 0 && ((reinterpret_cast<uintptr_t>(ek) | reinterpret_cast<uintptr_t>(ev)) & 15u)) return -2;
     Plan plan;
@@ -619,22 +642,28 @@ int tc_fused_fwd_small(int dtype, const Geo& g, const void* q, const void* k, co
     plan.p.status = status_ptr();
     if (!plan.p.status) return -2;
     if (plan.p.work_q == 0 || g.B == 0) return 0;
-    const unsigned grid = persistent_grid(plan.p.work_q, 4);
     cudaError_t err = cudaSuccess;
-    auto launch = [&](auto bf, auto inner) {
+    auto launch = [&](auto dh, auto bf, auto inner) {
+        constexpr int kDh = decltype(dh)::value;
         constexpr bool kBf = decltype(bf)::value;
         constexpr int kInner = decltype(inner)::value;
-        err = ensure_dynamic_smem((const void*)tc_fwd_small_kernel<kBf, kInner>, kSmemTotal);
+        using FS = FwdSmall<kDh>;
+        const unsigned grid = persistent_grid(plan.p.work_q, FS::kPerSm);
+        err = ensure_dynamic_smem((const void*)tc_fwd_small_kernel<kDh, kBf, kInner>, FS::kSmemTotal);
         if (err != cudaSuccess) return;
-        tc_fwd_small_kernel<kBf, kInner><<<grid, kThreads, kSmemTotal, s>>>(mq, mk, mv, mek, mev, plan.p, (uint16_t*)out, (float*)lse);
+        tc_fwd_small_kernel<kDh, kBf, kInner><<<grid, kThreads, FS::kSmemTotal, s>>>(mq, mk, mv, mek, mev, plan.p, (uint16_t*)out, (float*)lse);
     };
-    auto by_inner = [&](auto bf) {
-        if (plan.p.cb[2] == 16) launch(bf, std::integral_constant<int, 16>{});
-        else if (plan.p.cb[2] == 32) launch(bf, std::integral_constant<int, 32>{});
-        else launch(bf, std::integral_constant<int, 0>{});
+    auto by_inner = [&](auto dh, auto bf) {
+        if (plan.p.cb[2] == 16) launch(dh, bf, std::integral_constant<int, 16>{});
+        else if (plan.p.cb[2] == 32) launch(dh, bf, std::integral_constant<int, 32>{});
+        else launch(dh, bf, std::integral_constant<int, 0>{});
     };
-    if (bf16) by_inner(std::true_type{});
-    else by_inner(std::false_type{});
+    auto by_type = [&](auto dh) {
+        if (bf16) by_inner(dh, std::true_type{});
+        else by_inner(dh, std::false_type{});
+    };
+    if (g.D <= 64) by_type(std::integral_constant<int, 64>{});
+    else by_type(std::integral_constant<int, 128>{});
     if (err == cudaSuccess) err = cudaGetLastError();
     tc_count_launch();
     return err == cudaSuccess ? 0 : (int)err;
