@@ -97,9 +97,8 @@ int natten_fused_fwd(const natten_params_t* p, const void* q, const void* k, con
     set_vec_ok(g, p->dtype, true, true, true, {q, k, v, extra_k, extra_v});
     cudaStream_t s = (cudaStream_t)stream;
     if (!(p->flags & NATTEN_FLAG_FORCE_SIMT)) {
-        // small persistent CTAs (four per SM up to head dim 64, two above); one tile per CTA as the fallback
+        // small persistent CTAs (four per SM up to head dim 64, two above)
         rc = tc_fused_fwd_small(p->dtype, g, q, k, v, extra_k, extra_v, out, lse, s);
-        if (rc == NATTEN_E_UNSUPPORTED) rc = tc_fused_fwd(p->dtype, g, q, k, v, extra_k, extra_v, out, lse, s);
         if (rc != NATTEN_E_UNSUPPORTED) { t_last_path = NATTEN_PATH_TCGEN05; return rc; }
     }
     if (p->flags & NATTEN_FLAG_FORCE_TC) return NATTEN_E_UNSUPPORTED;

@@ -96,19 +96,29 @@ struct QueryCtx {
     bool inside;
 };
 
-__device__ __forceinline__ void decode_query(const Geo& g, long long row, QueryCtx& c)
+// Geometry of the query at output position o (row-major over the output extents) of sample b, head h.
+__device__ __forceinline__ void decode_at(const Geo& g, int b, long long o, int h, QueryCtx& c)
 {
-    c.row = row;
-    c.h = (int)(row % g.Hq);
-    long long bo = row / g.Hq;
-    long long o = bo % g.otot;
-    c.b = (int)(bo / g.otot);
-    c.hk = c.h / g.group;
+    c.row = ((long long)b * g.otot + o) * g.Hq + h;
+    c.h = h;
+    c.b = b;
+    c.hk = h / g.group;
     c.inside = true;
     int pos[3] = {0, 0, 0};
+    if (g.otot <= 0x7fffffffll) {                                // 32-bit divisions: the common case
+        unsigned o32 = (unsigned)o;
+        for (int a = g.rank - 1; a >= 0; --a) {
+            const unsigned nx = o32 / (unsigned)g.O[a];
+            pos[a] = (int)(o32 - nx * (unsigned)g.O[a]) * g.st[a];
+            o32 = nx;
+        }
+    } else {
+        for (int a = g.rank - 1; a >= 0; --a) {
+            pos[a] = (int)(o % g.O[a]) * g.st[a];
+            o /= g.O[a];
+        }
+    }
     for (int a = g.rank - 1; a >= 0; --a) {
-        pos[a] = (int)(o % g.O[a]) * g.st[a];
-        o /= g.O[a];
         c.Ls[a] = g.extents ? g.extents[c.b * g.rank + a] : g.L[a];
         if (pos[a] >= c.Ls[a]) c.inside = false;
     }
@@ -117,6 +127,13 @@ __device__ __forceinline__ void decode_query(const Geo& g, long long row, QueryC
         c.pflat = c.pflat * g.L[a] + pos[a];
         c.first[a] = c.inside ? axis_first_key(pos[a], c.Ls[a], g.K[a], g.dil[a], g.causal[a]) : 0;
     }
+}
+
+__device__ __forceinline__ void decode_query(const Geo& g, long long row, QueryCtx& c)
+{
+    const int h = (int)(row % g.Hq);
+    const long long bo = row / g.Hq;
+    decode_at(g, (int)(bo / g.otot), bo % g.otot, h, c);
 }
 
 // Flat key position of neighbour slot j (row-major over the per-axis slots).
@@ -196,7 +213,7 @@ fused_fwd_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T
                  T* __restrict__ out, typename AccOf<T>::type* __restrict__ lse, long long rows)
 {
     using A = typename AccOf<T>::type;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     A* qsh = reinterpret_cast<A*>(smem_raw) + (size_t)warp * g.D;
     const long long row = (long long)blockIdx.x * kWarps + warp;
@@ -299,7 +316,7 @@ fused_bwd_dq_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, cons
                     T* __restrict__ dq, long long rows)
 {
     using A = typename AccOf<T>::type;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     A* qsh = reinterpret_cast<A*>(smem_raw) + (size_t)warp * (g.D + g.Dv);
     A* dosh = qsh + g.D;
@@ -377,7 +394,7 @@ fused_bwd_dkdv_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, co
                       T* __restrict__ dk, T* __restrict__ dv, long long rows)
 {
     using A = typename AccOf<T>::type;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     A* ksh = reinterpret_cast<A*>(smem_raw) + (size_t)warp * (g.D + g.Dv);
     A* vsh = ksh + g.D;
@@ -470,7 +487,7 @@ fused_bwd_extra_kernel(const __grid_constant__ Geo g, const T* __restrict__ q,
                        T* __restrict__ dek, T* __restrict__ dev)
 {
     using A = typename AccOf<T>::type;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     A* ksh = reinterpret_cast<A*>(smem_raw);               // D + Dv staged once per block
     A* vsh = ksh + g.D;
@@ -549,7 +566,7 @@ fused_bwd_extra_kernel(const __grid_constant__ Geo g, const T* __restrict__ q,
 // tokens' rows sit in shared memory.  Blocks write partial sums that a second kernel adds in
 // a fixed order (deterministic, no atomics).
 constexpr int kExtraGroup = 16;
-constexpr int kExtraSegRows = 2048;
+constexpr int kExtraSegRows = 1024;
 
 template <typename T, int ND>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -558,7 +575,7 @@ extra_grad_partial_kernel(const __grid_constant__ Geo g, const T* __restrict__ q
                           const float* __restrict__ delta, const T* __restrict__ dout,
                           const float* __restrict__ dlse, float* __restrict__ partial, int e0, int ne)
 {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     float* eks = reinterpret_cast<float*>(smem_raw);           // [ne][D]
     float* evs = eks + kExtraGroup * g.D;                      // [ne][Dv]
     float* red = evs + kExtraGroup * g.Dv;                     // [ne][D + Dv]
@@ -646,6 +663,39 @@ extra_grad_partial_kernel(const __grid_constant__ Geo g, const T* __restrict__ q
 // row-per-warp kernel above keeps 128 accumulators per thread and runs one.
 constexpr int kExtraTileRows = 64;
 
+// Stage one tile of query rows and of their output-gradient rows in shared memory, 16 bytes at a time (rows
+// outside their sample are zero; head dims up to 128, 256 threads).  All of a thread's loads are issued
+// before its first store: with stores to shared memory in between, the loads go out one latency apart.
+template <typename T>
+__device__ __forceinline__ void stage_extra_rows(const T* __restrict__ q, const T* __restrict__ dout, const long long* qoff,
+                                                 const long long* orow, T* qt, T* gt, int D, int Dv, int qstr, int vstr, int tid)
+{
+    constexpr int kPer = kExtraTileRows * (128 / 8) / 256;      // 16-byte pieces per thread and tensor at head dim 128
+    const int nq8 = D / 8, nv8 = Dv / 8;
+    uint4 vq[kPer], vg[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        const int i = tid + 256 * j;
+        vq[j] = make_uint4(0, 0, 0, 0);
+        vg[j] = make_uint4(0, 0, 0, 0);
+        if (i < kExtraTileRows * nq8) {
+            const int r = i / nq8, c8 = i - r * nq8;
+            const long long o = qoff[r];
+            if (o >= 0) vq[j] = __ldg(reinterpret_cast<const uint4*>(q + o + 8 * c8));
+        }
+        if (i < kExtraTileRows * nv8) {
+            const int r = i / nv8, c8 = i - r * nv8;
+            if (qoff[r] >= 0) vg[j] = __ldg(reinterpret_cast<const uint4*>(dout + orow[r] * Dv + 8 * c8));
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        const int i = tid + 256 * j;
+        if (i < kExtraTileRows * nq8) { const int r = i / nq8, c8 = i - r * nq8; *reinterpret_cast<uint4*>(qt + r * qstr + 8 * c8) = vq[j]; }
+        if (i < kExtraTileRows * nv8) { const int r = i / nv8, c8 = i - r * nv8; *reinterpret_cast<uint4*>(gt + r * vstr + 8 * c8) = vg[j]; }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 extra_grad_tile_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T* __restrict__ ek,
@@ -653,7 +703,7 @@ extra_grad_tile_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, c
                        const float* __restrict__ delta, const T* __restrict__ dout,
                        const float* __restrict__ dlse, float* __restrict__ partial, int e0, int ne)
 {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int D = g.D, Dv = g.Dv, W = D + Dv;
     const int qstr = D + 8, vstr = Dv + 8;                     // padded row strides (elements): no bank conflicts
     T* qt = reinterpret_cast<T*>(smem_raw);                     // [64][qstr]
@@ -690,9 +740,12 @@ extra_grad_tile_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, c
             const long long cnd = base + tid;
             long long qo = -1, ro = 0;
             if (cnd < end) {
-                const int gi = (int)(cnd / g.otot);
+                int gi;
+                long long o;
+                if (total <= 0x7fffffffll) { gi = (int)((unsigned)cnd / (unsigned)g.otot); o = (long long)((unsigned)cnd - (unsigned)gi * (unsigned)g.otot); }
+                else { gi = (int)(cnd / g.otot); o = cnd % g.otot; }
                 QueryCtx c;
-                decode_query(g, ((long long)b * g.otot + cnd % g.otot) * g.Hq + hk * g.group + gi, c);
+                decode_at(g, b, o, hk * g.group + gi, c);
                 if (c.inside) {
                     qo = c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
                     ro = c.row;
@@ -705,19 +758,7 @@ extra_grad_tile_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, c
             rd[tid] = mine_inside ? delta[ro] - (dlse ? dlse[ro] : 0.f) : 0.f;
         }
         if (!__syncthreads_or(mine_inside ? 1 : 0)) continue;   // nothing of this tile is inside its sample
-        // ---- stage the rows (16 bytes at a time; rows outside are zero) ----
-        for (int i = tid; i < kExtraTileRows * (D / 8); i += 256) {
-            const int r = i / (D / 8), c8 = i % (D / 8);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (qoff[r] >= 0) v = *reinterpret_cast<const uint4*>(q + qoff[r] + 8 * c8);
-            *reinterpret_cast<uint4*>(qt + r * qstr + 8 * c8) = v;
-        }
-        for (int i = tid; i < kExtraTileRows * (Dv / 8); i += 256) {
-            const int r = i / (Dv / 8), c8 = i % (Dv / 8);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (qoff[r] >= 0) v = *reinterpret_cast<const uint4*>(dout + orow[r] * Dv + 8 * c8);
-            *reinterpret_cast<uint4*>(gt + r * vstr + 8 * c8) = v;
-        }
+        stage_extra_rows(q, dout, qoff, orow, qt, gt, D, Dv, qstr, vstr, tid);
         __syncthreads();
         // ---- phase 1: probabilities and dS of 4 tokens for one row ----
         {
@@ -828,7 +869,7 @@ qk_fwd_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T* _
               T* __restrict__ logits, long long rows)
 {
     using A = typename AccOf<T>::type;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     A* qsh = reinterpret_cast<A*>(smem_raw) + (size_t)warp * g.D;
     const long long row = (long long)blockIdx.x * kWarps + warp;
@@ -980,7 +1021,7 @@ av_bwd_dattn_kernel(const __grid_constant__ Geo g, const T* __restrict__ v, cons
                     T* __restrict__ dattn, long long rows)
 {
     using A = typename AccOf<T>::type;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     A* dosh = reinterpret_cast<A*>(smem_raw) + (size_t)warp * g.Dv;
     const long long row = (long long)blockIdx.x * kWarps + warp;
@@ -1042,7 +1083,7 @@ dot_neighbours_vec_kernel(const __grid_constant__ Geo g, const T* __restrict__ x
                           long long yts, long long yhs, float scale, int masked_is_neg_inf,
                           T* __restrict__ out, long long rows)
 {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int* koff = reinterpret_cast<int*>(smem_raw) + (size_t)warp * g.ktot;
     const long long row = (long long)blockIdx.x * kWarps + warp;
@@ -1080,7 +1121,7 @@ sum_neighbours_vec_kernel(const __grid_constant__ Geo g, const T* __restrict__ w
                           long long ybs, long long yts, long long yhs, int D, float scale,
                           int out_by_position, T* __restrict__ out, long long rows)
 {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int* koff = reinterpret_cast<int*>(smem_raw) + (size_t)warp * g.ktot;
     const long long row = (long long)blockIdx.x * kWarps + warp;
@@ -1282,9 +1323,12 @@ extra_grad_mma_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, co
             const long long cnd = base + tid;
             long long qo = -1, ro = 0;
             if (cnd < end) {
-                const int gi = (int)(cnd / g.otot);
+                int gi;
+                long long o;
+                if (total <= 0x7fffffffll) { gi = (int)((unsigned)cnd / (unsigned)g.otot); o = (long long)((unsigned)cnd - (unsigned)gi * (unsigned)g.otot); }
+                else { gi = (int)(cnd / g.otot); o = cnd % g.otot; }
                 QueryCtx c;
-                decode_query(g, ((long long)b * g.otot + cnd % g.otot) * g.Hq + hk * g.group + gi, c);
+                decode_at(g, b, o, hk * g.group + gi, c);
                 if (c.inside) {
                     qo = c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
                     ro = c.row;
@@ -1297,19 +1341,7 @@ extra_grad_mma_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, co
             rd[tid] = mine_inside ? delta[ro] - (dlse ? dlse[ro] : 0.f) : 0.f;
         }
         if (!__syncthreads_or(mine_inside ? 1 : 0)) continue;   // nothing of this tile is inside its sample
-        // ---- stage the rows (16 bytes at a time; rows outside are zero) ----
-        for (int i = tid; i < kExtraTileRows * (D / 8); i += 256) {
-            const int r = i / (D / 8), c8 = i % (D / 8);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (qoff[r] >= 0) v = *reinterpret_cast<const uint4*>(q + qoff[r] + 8 * c8);
-            *reinterpret_cast<uint4*>(qt + r * qstr + 8 * c8) = v;
-        }
-        for (int i = tid; i < kExtraTileRows * (Dv / 8); i += 256) {
-            const int r = i / (Dv / 8), c8 = i % (Dv / 8);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (qoff[r] >= 0) v = *reinterpret_cast<const uint4*>(dout + orow[r] * Dv + 8 * c8);
-            *reinterpret_cast<uint4*>(gt + r * vstr + 8 * c8) = v;
-        }
+        stage_extra_rows(q, dout, qoff, orow, qt, gt, D, Dv, qstr, vstr, tid);
         __syncthreads();
         // ---- phase 1: S (warps 0-3) and dP (warps 4-7), one block of 16 rows each ----
         {

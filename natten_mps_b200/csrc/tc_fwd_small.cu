@@ -669,6 +669,11 @@ int tc_fused_fwd_small(int dtype, const Geo& g, const void* q, const void* k, co
     return err == cudaSuccess ? 0 : (int)err;
 }
 
+// launches of the tensor-core kernels, counted on the host by every launcher
+static unsigned long long g_tc_launches = 0;
+void tc_count_launch() { ++g_tc_launches; }
+unsigned long long tc_launch_count() { return g_tc_launches; }
+
 #ifdef NATTEN_TRACE
 extern "C" int natten_trace_read_small(long long* host, int clear)
 {

@@ -6,9 +6,8 @@
 
 namespace natten {
 
-int tc_fused_fwd(int dtype, const Geo& g, const void* q, const void* k, const void* v,
-                 const void* ek, const void* ev, void* out, void* lse, cudaStream_t s);
-// The same for head dim 64 from small persistent CTAs (four per SM, 64-key chunks, interleaved chunk rows).
+// Fused forward for head dims up to 128 from small persistent CTAs (four per SM up to head dim 64, two above;
+// 64-key chunks, interleaved chunk rows).
 int tc_fused_fwd_small(int dtype, const Geo& g, const void* q, const void* k, const void* v,
                        const void* ek, const void* ev, void* out, void* lse, cudaStream_t s);
 int tc_fused_bwd(int dtype, const Geo& g, const void* q, const void* k, const void* v,

@@ -378,8 +378,10 @@ inline bool make_plan(const Geo& g, Plan& plan, int chunk = kChunk, bool with_st
             const int t0 = 128 / (t1 * t2);
             const int t[3] = {t0, t1, t2};
             bool fits = true;
-            for (int a = 0; a < 3; ++a)
+            for (int a = 0; a < 3; ++a) {
                 if (p.L[a] == 1 && t[a] != 1) fits = false;      // unused axis
+                if (t[a] * p.dil[a] * p.qstep[a] > 256) fits = false;     // TMA box limit of the query tile
+            }
             if (!fits) continue;
             const int E2 = (t2 - 1) * p.qstep[2] + p.K[2];
             int cb2 = pow2ceil(E2);
