@@ -17,7 +17,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>
-#include <mma.h>
 #include <initializer_list>
 #include <type_traits>
 
@@ -96,7 +95,9 @@ struct QueryCtx {
     bool inside;
 };
 
-// Geometry of the query at output position o (row-major over the output extents) of sample b, head h.
+// Geometry of the query at output position o (row-major over the output extents) of sample b, head h;
+// without kWindows the window starts (c.first) are left out.
+template <bool kWindows = true>
 __device__ __forceinline__ void decode_at(const Geo& g, int b, long long o, int h, QueryCtx& c)
 {
     c.row = ((long long)b * g.otot + o) * g.Hq + h;
@@ -105,27 +106,38 @@ __device__ __forceinline__ void decode_at(const Geo& g, int b, long long o, int 
     c.hk = h / g.group;
     c.inside = true;
     int pos[3] = {0, 0, 0};
+    // loops over the three axes with the rank as a guard: the small arrays stay in registers
     if (g.otot <= 0x7fffffffll) {                                // 32-bit divisions: the common case
         unsigned o32 = (unsigned)o;
-        for (int a = g.rank - 1; a >= 0; --a) {
+#pragma unroll
+        for (int a = 2; a >= 0; --a) {
+            if (a >= g.rank) continue;
             const unsigned nx = o32 / (unsigned)g.O[a];
             pos[a] = (int)(o32 - nx * (unsigned)g.O[a]) * g.st[a];
             o32 = nx;
         }
     } else {
-        for (int a = g.rank - 1; a >= 0; --a) {
+#pragma unroll
+        for (int a = 2; a >= 0; --a) {
+            if (a >= g.rank) continue;
             pos[a] = (int)(o % g.O[a]) * g.st[a];
             o /= g.O[a];
         }
     }
-    for (int a = g.rank - 1; a >= 0; --a) {
+    c.pflat = 0;
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+        if (a >= g.rank) continue;
         c.Ls[a] = g.extents ? g.extents[c.b * g.rank + a] : g.L[a];
         if (pos[a] >= c.Ls[a]) c.inside = false;
-    }
-    c.pflat = 0;
-    for (int a = 0; a < g.rank; ++a) {
         c.pflat = c.pflat * g.L[a] + pos[a];
-        c.first[a] = c.inside ? axis_first_key(pos[a], c.Ls[a], g.K[a], g.dil[a], g.causal[a]) : 0;
+    }
+    if constexpr (kWindows) {
+#pragma unroll
+        for (int a = 0; a < 3; ++a) {
+            if (a >= g.rank) continue;
+            c.first[a] = c.inside ? axis_first_key(pos[a], c.Ls[a], g.K[a], g.dil[a], g.causal[a]) : 0;
+        }
     }
 }
 
@@ -672,27 +684,33 @@ __device__ __forceinline__ void stage_extra_rows(const T* __restrict__ q, const 
 {
     constexpr int kPer = kExtraTileRows * (128 / 8) / 256;      // 16-byte pieces per thread and tensor at head dim 128
     const int nq8 = D / 8, nv8 = Dv / 8;
+    // piece index / pieces per row by a multiplication: exact for indices below 4096 and divisors up to 16
+    const unsigned mq = (65536u + nq8 - 1) / nq8, mv = (65536u + nv8 - 1) / nv8;
     uint4 vq[kPer], vg[kPer];
+    int sq[kPer], sg[kPer];                                     // shared-memory element offsets, -1 = nothing to store
 #pragma unroll
     for (int j = 0; j < kPer; ++j) {
         const int i = tid + 256 * j;
         vq[j] = make_uint4(0, 0, 0, 0);
         vg[j] = make_uint4(0, 0, 0, 0);
+        sq[j] = -1;
+        sg[j] = -1;
         if (i < kExtraTileRows * nq8) {
-            const int r = i / nq8, c8 = i - r * nq8;
+            const int r = (int)(((unsigned)i * mq) >> 16), c8 = i - r * nq8;
             const long long o = qoff[r];
+            sq[j] = r * qstr + 8 * c8;
             if (o >= 0) vq[j] = __ldg(reinterpret_cast<const uint4*>(q + o + 8 * c8));
         }
         if (i < kExtraTileRows * nv8) {
-            const int r = i / nv8, c8 = i - r * nv8;
+            const int r = (int)(((unsigned)i * mv) >> 16), c8 = i - r * nv8;
+            sg[j] = r * vstr + 8 * c8;
             if (qoff[r] >= 0) vg[j] = __ldg(reinterpret_cast<const uint4*>(dout + orow[r] * Dv + 8 * c8));
         }
     }
 #pragma unroll
     for (int j = 0; j < kPer; ++j) {
-        const int i = tid + 256 * j;
-        if (i < kExtraTileRows * nq8) { const int r = i / nq8, c8 = i - r * nq8; *reinterpret_cast<uint4*>(qt + r * qstr + 8 * c8) = vq[j]; }
-        if (i < kExtraTileRows * nv8) { const int r = i / nv8, c8 = i - r * nv8; *reinterpret_cast<uint4*>(gt + r * vstr + 8 * c8) = vg[j]; }
+        if (sq[j] >= 0) *reinterpret_cast<uint4*>(qt + sq[j]) = vq[j];
+        if (sg[j] >= 0) *reinterpret_cast<uint4*>(gt + sg[j]) = vg[j];
     }
 }
 
@@ -745,7 +763,7 @@ extra_grad_tile_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, c
                 if (total <= 0x7fffffffll) { gi = (int)((unsigned)cnd / (unsigned)g.otot); o = (long long)((unsigned)cnd - (unsigned)gi * (unsigned)g.otot); }
                 else { gi = (int)(cnd / g.otot); o = cnd % g.otot; }
                 QueryCtx c;
-                decode_at(g, b, o, hk * g.group + gi, c);
+                decode_at<false>(g, b, o, hk * g.group + gi, c);
                 if (c.inside) {
                     qo = c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
                     ro = c.row;
@@ -1265,24 +1283,59 @@ inline unsigned grid_for(long long rows) { return (unsigned)((rows + kWarps - 1)
     } while (0)
 
 
+// Warp-level tensor-core helpers for the kernel below: 8 x 8 16-bit matrices from shared memory (every row
+// address 16-byte aligned) and the m16n8k16 product with fp32 accumulation.
+__device__ __forceinline__ uint32_t shared_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t& r0, uint32_t& r1, uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    if constexpr (std::is_same<T, __half>::value)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi)
+{
+    const T a = from_acc<T, float>(lo), b = from_acc<T, float>(hi);
+    return (uint32_t)(*reinterpret_cast<const unsigned short*>(&a)) | ((uint32_t)(*reinterpret_cast<const unsigned short*>(&b)) << 16);
+}
+
 // The same partial sums with the four small matrix products of a tile on the warp-level tensor-core path
-// (16 x 16 x 16 fragments; the additional tokens are the 16-wide side of every product):
-//   phase 1  S = Qt Ek^T, dP = Gt Ev^T          [64 rows x 16 tokens], K = head dim    (warps 0-3 | 4-7, one row block each)
-//   threads  p = exp(S*scale - lse), ds = p (dP - delta) scale, rounded to the tensors' 16-bit type like the
-//            probabilities of the fused kernels
+// (m16n8k16 fragments fed by ldmatrix; the additional tokens are the 16-wide side of every product):
+//   phase 1  warp w takes the 16 rows of block w & 3 and the 8 tokens of half w >> 2:  S = Qt Ek^T and
+//            dP = Gt Ev^T over the head dim, then, still in registers, p = exp(S*scale - lse) and
+//            ds = p (dP - delta) scale, rounded to the tensors' 16-bit type like the probabilities of the
+//            fused kernels and written as [row][token] tiles
 //   phase 2  dEk += ds^T Qt, dEv += p^T Gt      [16 tokens x head dim], K = 64 rows     (warp w: channels 16w .. 16w+15)
 // The accumulators of phase 2 stay in registers across the block's tiles.  Head dims: multiples of 16 up to 128.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 extra_grad_mma_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, const T* __restrict__ ek,
                       const T* __restrict__ ev, const float* __restrict__ lse,
                       const float* __restrict__ delta, const T* __restrict__ dout,
                       const float* __restrict__ dlse, float* __restrict__ partial, int e0, int ne)
 {
-    using namespace nvcuda;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int D = g.D, Dv = g.Dv, W = D + Dv;
-    const int qstr = D + 8, vstr = Dv + 8;                     // padded row strides (elements)
+    const int qstr = D + 8, vstr = Dv + 8;                     // padded row strides (elements; 16-byte multiples)
     constexpr int kPStr = kExtraGroup + 8;                      // row stride of the 16-bit p / ds tiles
     T* qt = reinterpret_cast<T*>(smem_raw);                     // [64][qstr]
     T* gt = qt + kExtraTileRows * qstr;                         // [64][vstr]
@@ -1290,45 +1343,50 @@ extra_grad_mma_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, co
     T* evt = ekt + kExtraGroup * qstr;                          // [16][vstr]
     T* pt = evt + kExtraGroup * vstr;                           // [64][kPStr]  p
     T* dst = pt + kExtraTileRows * kPStr;                       // [64][kPStr]  ds
-    float* sbuf = reinterpret_cast<float*>(dst + kExtraTileRows * kPStr);    // [64][16]  S
-    float* dbuf = sbuf + kExtraTileRows * kExtraGroup;          // [64][16]  dP
-    float* rl = dbuf + kExtraTileRows * kExtraGroup;            // [64] lse
+    float* rl = reinterpret_cast<float*>(dst + kExtraTileRows * kPStr);      // [64] lse
     float* rd = rl + kExtraTileRows;                            // [64] delta
     long long* qoff = reinterpret_cast<long long*>(rd + kExtraTileRows);   // [64] element offset of the q row, -1 = no row
     long long* orow = qoff + kExtraTileRows;                    // [64] row of dout / lse / delta
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seg = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-    for (int i = tid; i < kExtraGroup * D; i += 256) {
-        const int e = i / D, d = i % D;
-        ekt[e * qstr + d] = e < ne ? ek[(((long long)b * g.n_extra + e0 + e) * g.Hkv + hk) * D + d] : T(0.f);
+    // the tokens' rows, 16 bytes at a time
+    for (int i = tid; i < kExtraGroup * (D / 8); i += 256) {
+        const int e = i / (D / 8), c8 = i - e * (D / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (e < ne) v = __ldg(reinterpret_cast<const uint4*>(ek + (((long long)b * g.n_extra + e0 + e) * g.Hkv + hk) * D + 8 * c8));
+        *reinterpret_cast<uint4*>(ekt + e * qstr + 8 * c8) = v;
     }
-    for (int i = tid; i < kExtraGroup * Dv; i += 256) {
-        const int e = i / Dv, d = i % Dv;
-        evt[e * vstr + d] = e < ne ? ev[(((long long)b * g.n_extra + e0 + e) * g.Hkv + hk) * Dv + d] : T(0.f);
+    for (int i = tid; i < kExtraGroup * (Dv / 8); i += 256) {
+        const int e = i / (Dv / 8), c8 = i - e * (Dv / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (e < ne) v = __ldg(reinterpret_cast<const uint4*>(ev + (((long long)b * g.n_extra + e0 + e) * g.Hkv + hk) * Dv + 8 * c8));
+        *reinterpret_cast<uint4*>(evt + e * vstr + 8 * c8) = v;
     }
 
-    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc_k, acc_v;
-    wmma::fill_fragment(acc_k, 0.f);
-    wmma::fill_fragment(acc_v, 0.f);
+    float acc_k[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, acc_v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     const float scale = (float)g.scale;
     const long long total = g.otot * g.group;
     long long end = (long long)(seg + 1) * kExtraSegRows;
     if (end > total) end = total;
+    const int lr = lane & 7, lm = lane >> 3;                   // row inside an 8 x 8 matrix, matrix of the ldmatrix group
+    const int fg = lane >> 2, ft = lane & 3;                   // fragment row and column pair of this lane
 
     for (long long base = (long long)seg * kExtraSegRows; base < end; base += kExtraTileRows) {
         __syncthreads();                                        // the previous tile has been consumed
         bool mine_inside = false;
+        long long my_row = 0;
         if (tid < kExtraTileRows) {
             const long long cnd = base + tid;
             long long qo = -1, ro = 0;
             if (cnd < end) {
                 int gi;
                 long long o;
-                if (total <= 0x7fffffffll) { gi = (int)((unsigned)cnd / (unsigned)g.otot); o = (long long)((unsigned)cnd - (unsigned)gi * (unsigned)g.otot); }
-                else { gi = (int)(cnd / g.otot); o = cnd % g.otot; }
+                // the heads of the group are the fast index: a tile reads group x D contiguous channels per position
+                if (total <= 0x7fffffffll) { const unsigned o32 = (unsigned)cnd / (unsigned)g.group; gi = (int)((unsigned)cnd - o32 * (unsigned)g.group); o = (long long)o32; }
+                else { o = cnd / g.group; gi = (int)(cnd - o * g.group); }
                 QueryCtx c;
-                decode_at(g, b, o, hk * g.group + gi, c);
+                decode_at<false>(g, b, o, hk * g.group + gi, c);
                 if (c.inside) {
                     qo = c.b * g.qs[0] + c.pflat * g.qs[1] + c.h * g.qs[2];
                     ro = c.row;
@@ -1337,66 +1395,93 @@ extra_grad_mma_kernel(const __grid_constant__ Geo g, const T* __restrict__ q, co
             }
             qoff[tid] = qo;
             orow[tid] = ro;
-            rl[tid] = mine_inside ? lse[ro] : 0.f;
-            rd[tid] = mine_inside ? delta[ro] - (dlse ? dlse[ro] : 0.f) : 0.f;
+            my_row = ro;
         }
         if (!__syncthreads_or(mine_inside ? 1 : 0)) continue;   // nothing of this tile is inside its sample
-        stage_extra_rows(q, dout, qoff, orow, qt, gt, D, Dv, qstr, vstr, tid);
-        __syncthreads();
-        // ---- phase 1: S (warps 0-3) and dP (warps 4-7), one block of 16 rows each ----
-        {
-            const int mt = warp & 3;
-            const bool second = warp >= 4;
-            const T* rows = (second ? gt : qt) + 16 * mt * (second ? vstr : qstr);
-            const T* toks = second ? evt : ekt;
-            const int str = second ? vstr : qstr, depth = second ? Dv : D;
-            wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
-            wmma::fill_fragment(c, 0.f);
-            for (int k = 0; k < depth; k += 16) {
-                wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> a;
-                wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::col_major> bm;
-                wmma::load_matrix_sync(a, rows + k, str);
-                wmma::load_matrix_sync(bm, toks + k, str);      // B(k, token) = toks[token][k]
-                wmma::mma_sync(c, a, bm, c);
-            }
-            wmma::store_matrix_sync((second ? dbuf : sbuf) + 16 * mt * kExtraGroup, c, kExtraGroup, wmma::mem_row_major);
+        // the rows' statistics travel together with the rows: one global latency per tile, not two
+        float my_lse = 0.f, my_delta = 0.f;
+        if (mine_inside) {
+            my_lse = lse[my_row];
+            my_delta = delta[my_row] - (dlse ? dlse[my_row] : 0.f);
         }
+        stage_extra_rows(q, dout, qoff, orow, qt, gt, D, Dv, qstr, vstr, tid);
+        if (tid < kExtraTileRows) { rl[tid] = my_lse; rd[tid] = my_delta; }
         __syncthreads();
-        // ---- probabilities and dS: thread = (row, 4 tokens) ----
+        // ---- phase 1: S and dP of 16 rows x 8 tokens, then p and ds from the fragments ----
         {
-            const int r = tid >> 2, t0 = 4 * (tid & 3);
-            const bool live = qoff[r] >= 0;
+            const int mt = warp & 3, nh = warp >> 2;
+            float cs[4] = {0.f, 0.f, 0.f, 0.f}, cd[4] = {0.f, 0.f, 0.f, 0.f};
+            const int arow = 16 * mt + lr + 8 * (lm & 1), acol = 8 * (lm >> 1);      // A: rows x depth, row-major
+            const int brow = 8 * nh + lr, bcol = 8 * (lm & 1);                       // B(k, token) = toks[token][k]
+            const uint32_t aq = shared_addr(qt + arow * qstr + acol), ag = shared_addr(gt + arow * vstr + acol);
+            const uint32_t bk = shared_addr(ekt + brow * qstr + bcol), bv = shared_addr(evt + brow * vstr + bcol);
+            for (int k = 0; k < D; k += 16) {
+                uint32_t a[4], b0, b1;
+                ldsm_x4(a, aq + 2 * k);
+                ldsm_x2(b0, b1, bk + 2 * k);
+                mma_16816<T>(cs, a, b0, b1);
+            }
+            for (int k = 0; k < Dv; k += 16) {
+                uint32_t a[4], b0, b1;
+                ldsm_x4(a, ag + 2 * k);
+                ldsm_x2(b0, b1, bv + 2 * k);
+                mma_16816<T>(cd, a, b0, b1);
+            }
+            const int tk = 8 * nh + 2 * ft;                    // this lane's two tokens
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const bool on = live && t0 + j < ne;
-                const float pj = on ? expf(sbuf[r * kExtraGroup + t0 + j] * scale - rl[r]) : 0.f;
-                const float dj = on ? pj * (dbuf[r * kExtraGroup + t0 + j] - rd[r]) * scale : 0.f;
-                pt[r * kPStr + t0 + j] = T(pj);
-                dst[r * kPStr + t0 + j] = T(dj);
+            for (int hh = 0; hh < 2; ++hh) {                   // fragment rows fg and fg + 8
+                const int r = 16 * mt + fg + 8 * hh;
+                const bool live = qoff[r] >= 0;
+                const float lr_ = rl[r], dl = rd[r];
+                float pj[2], dj[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const bool on = live && tk + j < ne;
+                    pj[j] = on ? expf(cs[2 * hh + j] * scale - lr_) : 0.f;
+                    dj[j] = on ? pj[j] * (cd[2 * hh + j] - dl) * scale : 0.f;
+                }
+                *reinterpret_cast<uint32_t*>(pt + r * kPStr + tk) = pack_pair<T>(pj[0], pj[1]);
+                *reinterpret_cast<uint32_t*>(dst + r * kPStr + tk) = pack_pair<T>(dj[0], dj[1]);
             }
         }
         __syncthreads();
         // ---- phase 2: warp w owns channels 16w .. 16w+15 of dEk and of dEv ----
-        for (int k = 0; k < kExtraTileRows; k += 16) {
-            wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::col_major> a;      // A(token, row) = w[row][token]
-            wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> bm;
-            if (16 * warp < D) {
-                wmma::load_matrix_sync(a, dst + k * kPStr, kPStr);
-                wmma::load_matrix_sync(bm, qt + k * qstr + 16 * warp, qstr);
-                wmma::mma_sync(acc_k, a, bm, acc_k);
-            }
-            if (16 * warp < Dv) {
-                wmma::load_matrix_sync(a, pt + k * kPStr, kPStr);
-                wmma::load_matrix_sync(bm, gt + k * vstr + 16 * warp, vstr);
-                wmma::mma_sync(acc_v, a, bm, acc_v);
+        {
+            const int arow = lr + 8 * (lm >> 1), acol = 8 * (lm & 1);                // A(token, row) = w[row][token], transposed on load
+            const int brow = lr + 8 * (lm & 1), bcol = 16 * warp + 8 * (lm >> 1);    // B(row, channel), transposed on load
+#pragma unroll
+            for (int k = 0; k < kExtraTileRows; k += 16) {
+                uint32_t a[4], bm[4];
+                if (16 * warp < D) {
+                    ldsm_x4_t(a, shared_addr(dst + (k + arow) * kPStr + acol));
+                    ldsm_x4_t(bm, shared_addr(qt + (k + brow) * qstr + bcol));
+                    mma_16816<T>(acc_k[0], a, bm[0], bm[1]);
+                    mma_16816<T>(acc_k[1], a, bm[2], bm[3]);
+                }
+                if (16 * warp < Dv) {
+                    ldsm_x4_t(a, shared_addr(pt + (k + arow) * kPStr + acol));
+                    ldsm_x4_t(bm, shared_addr(gt + (k + brow) * vstr + bcol));
+                    mma_16816<T>(acc_v[0], a, bm[0], bm[1]);
+                    mma_16816<T>(acc_v[1], a, bm[2], bm[3]);
+                }
             }
         }
     }
     // ---- this block's partial sums: [token][D | Dv], through shared memory ----
     __syncthreads();
     float* red = reinterpret_cast<float*>(smem_raw);            // [16][W], over the row tiles
-    if (16 * warp < D) wmma::store_matrix_sync(red + 16 * warp, acc_k, W, wmma::mem_row_major);
-    if (16 * warp < Dv) wmma::store_matrix_sync(red + D + 16 * warp, acc_v, W, wmma::mem_row_major);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+        const int ch = 16 * warp + 8 * nt + 2 * ft;
+        if (16 * warp < D) {
+            red[fg * W + ch] = acc_k[nt][0]; red[fg * W + ch + 1] = acc_k[nt][1];
+            red[(fg + 8) * W + ch] = acc_k[nt][2]; red[(fg + 8) * W + ch + 1] = acc_k[nt][3];
+        }
+        if (16 * warp < Dv) {
+            red[fg * W + D + ch] = acc_v[nt][0]; red[fg * W + D + ch + 1] = acc_v[nt][1];
+            red[(fg + 8) * W + D + ch] = acc_v[nt][2]; red[(fg + 8) * W + D + ch + 1] = acc_v[nt][3];
+        }
+    }
     __syncthreads();
     float* out = partial + ((((long long)b * g.Hkv + hk) * gridDim.x + seg) * kExtraGroup) * W;
     for (int i = tid; i < ne * W; i += 256) out[i] = red[i];
@@ -1426,10 +1511,11 @@ bool launch_extra_fast(const Geo& g, const void* q, const void* ek, const void* 
             // rows must be readable 16 bytes at a time
             const bool aligned = g.D % 8 == 0 && g.Dv % 8 == 0 && g.qs[0] % 8 == 0 && g.qs[1] % 8 == 0 && g.qs[2] % 8 == 0 &&
                                  ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(dout)) & 15u) == 0;
-            if (aligned && g.D % 16 == 0 && g.Dv % 16 == 0) {        // warp-level tensor-core products
+            const bool tokens_aligned = ((reinterpret_cast<uintptr_t>(ek) | reinterpret_cast<uintptr_t>(ev)) & 15u) == 0;
+            if (aligned && tokens_aligned && g.D % 16 == 0 && g.Dv % 16 == 0) {        // warp-level tensor-core products
                 const size_t msmem = (size_t)(kExtraTileRows + kExtraGroup) * (g.D + 8 + g.Dv + 8) * sizeof(T) +
                                      (size_t)2 * kExtraTileRows * (kExtraGroup + 8) * sizeof(T) +
-                                     (size_t)kExtraTileRows * (2 * kExtraGroup + 2) * sizeof(float) + (size_t)kExtraTileRows * 2 * sizeof(long long);
+                                     (size_t)kExtraTileRows * 2 * sizeof(float) + (size_t)kExtraTileRows * 2 * sizeof(long long);
                 ensure_dynamic_smem((const void*)extra_grad_mma_kernel<T>, 96 * 1024);
                 extra_grad_mma_kernel<T><<<grid, 256, msmem, s>>>(g, (const T*)q, (const T*)ek, (const T*)ev, (const float*)lse,
                     (const float*)delta, (const T*)dout, (const float*)dlse, (float*)partial, e0, ne);
