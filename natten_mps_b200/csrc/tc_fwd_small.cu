@@ -1,6 +1,6 @@
-// Fused neighbourhood-attention forward for head dim 64 on tcgen05 tensor cores (sm_100a),
-// built from small persistent CTAs: four of them share an SM, each working on one tile of 128 queries
-// at a time (tiles blockIdx.x, + gridDim.x, ...).
+// Fused neighbourhood-attention forward for head dims up to 128 on tcgen05 tensor cores (sm_100a),
+// built from small persistent CTAs: four of them share an SM up to head dim 64, two above it, each working
+// on one tile of 128 queries at a time (tiles blockIdx.x, + gridDim.x, ...).
 //
 // Per tile the union of the queries' neighbourhoods is a box of keys walked in chunks of 64 keys
 // (additional tokens follow as extra chunks):
@@ -13,11 +13,13 @@
 // chunk carries a share of every warp's window and the four warps of a tile finish a chunk together.
 // A row's stabiliser m is fixed at the first valid columns it meets and only moves if a later score
 // exceeds it by 2^60 (2^14 for fp16); O, the row sum and the probabilities already stored for the
-// chunk are then rescaled.  Four independent CTAs per SM give the schedulers sixteen softmax warps in
-// different phases of their tiles, which is what hides the TMEM / barrier / MMA latencies; a CTA needs
-// 128 TMEM columns and 49 KB of shared memory.
+// chunk are then rescaled.  Up to head dim 64 four independent CTAs per SM give the schedulers sixteen
+// softmax warps in different phases of their tiles, which is what hides the TMEM / barrier / MMA latencies
+// (128 TMEM columns and 49 KB of shared memory per CTA).  Above it only two CTAs fit (256 columns, 97 KB),
+// so the scores get two buffers there: S(c + 1) is computed while the threads work on S(c).
 //
-// TMEM columns: S [0,64) (P over [0,32)), O [64,128).
+// TMEM columns: head dim 64: S [0,64) (P over [0,32)), O [64,128);
+//               head dim 128: S of even chunks [0,64), of odd chunks [64,128), O [128,256).
 #include "tc_kernels.cuh"
 
 #include "tc_fwd_geom.cuh"
@@ -58,7 +60,7 @@ constexpr int kThreads = 160;               // 4 softmax warps + 1 warp that loa
 constexpr int kHdrSlots = 3;                // tile headers published by the issuing warp
 constexpr int kHdrBytes = 144;
 static_assert(sizeof(FwdTile) <= kHdrBytes, "header slot too small");
-constexpr uint32_t kColS = 0, kColO = 64;
+constexpr uint32_t kColS = 0;
 
 // Shared memory and TMEM of one CTA for head dim DH (64: four CTAs per SM, 128 TMEM columns; 128: two CTAs per
 // SM, 256 TMEM columns).  Tiles are stored as blocks of 64 channels (128-byte rows, 128-byte swizzle).
@@ -71,10 +73,14 @@ struct FwdSmall {
     static constexpr int kKVBytes = kKVHalf * kHalves;
     static constexpr int kOffQ = 0, kOffK = kQBytes, kOffV = kQBytes + kStages * kKVBytes;
     static constexpr int kBar = kQBytes + 2 * kStages * kKVBytes;
-    static constexpr int kHdr = kBar + 128;
+    static constexpr int kHdr = kBar + 160;
     static constexpr int kSmemTotal = kHdr + kHdrSlots * kHdrBytes;
     static constexpr uint32_t kTmemCols = DH == 64 ? 128 : 256;     // S 64 + O DH, rounded up to a power of two
     static constexpr int kPerSm = DH == 64 ? 4 : 2;
+    // At head dim 128 the 256 TMEM columns hold two score buffers: S(c + 1) is computed while the threads turn
+    // S(c) into probabilities (at 64 the four CTAs of an SM fill each other's gaps instead).
+    static constexpr bool kTwoS = DH == 128;
+    static constexpr uint32_t kColO = kTwoS ? 128 : 64;
 };
 
 template <int DH, bool BF16, int kInner>
@@ -87,7 +93,8 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     using FS = FwdSmall<DH>;
     constexpr int kHalves = FS::kHalves, kQHalf = FS::kQHalf, kKVHalf = FS::kKVHalf, kQBytes = FS::kQBytes, kKVBytes = FS::kKVBytes;
     constexpr int kOffQ = FS::kOffQ, kOffK = FS::kOffK, kOffV = FS::kOffV, kBar = FS::kBar, kHdr = FS::kHdr;
-    constexpr uint32_t kTmemCols = FS::kTmemCols;
+    constexpr uint32_t kTmemCols = FS::kTmemCols, kColO = FS::kColO;
+    constexpr bool kTwoS = FS::kTwoS;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef NATTEN_TRACE
@@ -106,6 +113,14 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t bar_p = sbase + kBar + 56;           // every thread stored its P
     const uint32_t bar_o = sbase + kBar + 64;           // last P V of the tile finished
     const uint32_t bar_hdr = sbase + kBar + 72;         // [3] geometry of the CTA's t-th tile published
+    const uint32_t bar_s1 = sbase + kBar + 96;          // two score buffers: bar_s / bar_p of the odd chunks
+    const uint32_t bar_p1 = sbase + kBar + 104;
+    const uint32_t bar_pv = sbase + kBar + 128;         // [2] two score buffers: P V of the chunk finished (by chunk parity)
+    // chunk n (counted over the CTA's whole run) -> its score columns, barriers and wait parity
+    auto s_cols = [&](unsigned n) -> uint32_t { return kTwoS ? 64u * (n & 1u) : 0u; };
+    auto bar_s_of = [&](unsigned n) -> uint32_t { return (kTwoS && (n & 1u)) ? bar_s1 : bar_s; };
+    auto bar_p_of = [&](unsigned n) -> uint32_t { return (kTwoS && (n & 1u)) ? bar_p1 : bar_p; };
+    auto par_of = [&](unsigned n) -> uint32_t { return kTwoS ? ((n >> 1) & 1u) : (n & 1u); };
     auto hdr_slot = [&](unsigned t) { return reinterpret_cast<FwdTile*>(smem + kHdr + (t % kHdrSlots) * kHdrBytes); };
 
     if (warp == 4) {
@@ -117,6 +132,10 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int s = 0; s < kStages; ++s) { mbar_init(bar_kv + 8 * s, 1); mbar_init(bar_kvfree + 8 * s, 1); }
             mbar_init(bar_s, 1);
             mbar_init(bar_p, 128);
+            mbar_init(bar_s1, 1);
+            mbar_init(bar_p1, 128);
+            mbar_init(bar_pv, 1);
+            mbar_init(bar_pv + 8, 1);
             mbar_init(bar_o, 1);
             for (int i = 0; i < kHdrSlots; ++i) mbar_init(bar_hdr + 8 * i, 1);
             mbar_init_fence();
@@ -252,9 +271,9 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < DH / 16; ++ks)            // 32 bytes per k-step inside a 64-channel block
-                        mma_ss_e(tmem + kColS, dq0 + ((((ks / 4) * kQHalf) + (ks % 4) * 32) >> 4),
+                        mma_ss_e(tmem + kColS + s_cols(n_qk), dq0 + ((((ks / 4) * kQHalf) + (ks % 4) * 32) >> 4),
                                  dk0 + ((((ks / 4) * kKVHalf) + (ks % 4) * 32) >> 4), idesc_qk, ks > 0, leader);
-                    mma_commit_e(bar_s, leader);
+                    mma_commit_e(bar_s_of(n_qk), leader);
                     if (c + 1 == H->nch) mma_commit_e(bar_qfree, leader);     // last scores of the tile: Q may go once they are done
                 }
                 if (c < H->nnb) { if (++qc[2] == H->nc[2]) { qc[2] = 0; if (++qc[1] == H->nc[1]) { qc[1] = 0; ++qc[0]; } } }
@@ -269,8 +288,9 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < kKeys / 16; ++ks)
-                        mma_ts_e(tmem + kColO, tmem + kColS + 8 * ks, dv0 + 128 * ks, idesc_pv, (c > 0 || ks > 0) ? 1u : 0u, leader);
+                        mma_ts_e(tmem + kColO, tmem + kColS + s_cols(n_pv) + 8 * ks, dv0 + 128 * ks, idesc_pv, (c > 0 || ks > 0) ? 1u : 0u, leader);
                     mma_commit_e(bar_kvfree + 8 * s, leader);
+                    if (kTwoS) mma_commit_e(bar_pv + 8 * (n_pv & 1u), leader);
                     if (last) mma_commit_e(bar_o, leader);
                 }
                 ++n_pv;
@@ -288,11 +308,15 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 discover();                      // the next tile's geometry, while the threads work on this chunk
                 while (refill()) {}
                 for (int c = 0; c < nch && ok; ++c) {
-                    ok = mbar_wait(bar_p, (n_pv & 1), abort_flag, P.wait_budget);      // P(c) stored over S(c)
+                    // two score buffers: S(c + 1) goes into the other buffer while the threads work on S(c); that
+                    // buffer's P(c - 1) is read by a product issued earlier from this warp, so the order holds
+                    if (kTwoS && c + 1 < nch) issue_qk(H, c + 1);
+                    if (!ok) break;
+                    ok = mbar_wait(bar_p_of(n_pv), par_of(n_pv), abort_flag, P.wait_budget);      // P(c) stored over S(c)
                     if (!ok) break;
                     STAMP(210);
                     issue_pv(c, c + 1 == nch);       // reads P(c) ...
-                    if (c + 1 < nch) issue_qk(H, c + 1);   // ... before the next scores overwrite it (issue order)
+                    if (!kTwoS && c + 1 < nch) issue_qk(H, c + 1);   // ... before the next scores overwrite it (issue order)
                     STAMP(220);
                     while (refill()) {}
                 }
@@ -304,6 +328,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // =====================================================================
         const uint32_t trow = tmem + (static_cast<uint32_t>(warp * 32) << 16);
         constexpr float kGrow = BF16 ? 60.f : 14.f;      // exponent headroom of the stored probabilities
+        constexpr float kGrowSum = BF16 ? 1.152921504606847e18f : 16384.f;      // 2^kGrow: a piece's row sum below it has no probability above it
         // With 16-column inner rows every piece is one inner row of the chunk: a piece is either inside the
         // row's window along the outer axes or not (one bit), and which of its 16 columns are valid is the
         // same for every piece.  The column mask then lives in the addends of the scale-and-shift, one
@@ -311,6 +336,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         constexpr bool kRows16 = kInner == 16;
         bool ok = true;
         unsigned n = 0;                      // chunks processed so far (all tiles of this CTA)
+        uint32_t scol = trow + kColS;        // TMEM address of this row's scores of the current chunk
         float m = -INFINITY, l = 0.f;
         float add[16];
         uint32_t add_cols = 0u;              // column mask the addends were built for
@@ -327,6 +353,11 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         auto rescale = [&](bool grow, float xmax, int c, int pc, uint32_t stored) {
             const float fac = grow ? fast_exp2(-xmax) : 1.f;
             if (c > 0) {
+                // with two score buffers S(c) was issued before P V of chunk c - 1: wait for that product itself
+                if (kTwoS) {
+                    ok = mbar_wait(bar_pv + 8 * ((n - 1) & 1u), par_of(n - 1), abort_flag, P.wait_budget) && ok;
+                    tc_fence_after();
+                }
 #pragma unroll 1
                 for (int part = 0; part < DH / 16; ++part) {
                     uint32_t o[16];
@@ -344,7 +375,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                              : "=r"(old[0]), "=r"(old[1]), "=r"(old[2]), "=r"(old[3]), "=r"(old[4]), "=r"(old[5]),
                                "=r"(old[6]), "=r"(old[7])
-                             : "r"(trow + kColS + 8 * pp) : "memory");
+                             : "r"(scol + 8 * pp) : "memory");
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -359,7 +390,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                     old[i] = cvt_pack<BF16>(lo * fac, hi * fac);
                 }
-                tmem_st8(trow + kColS + 8 * pp, old);
+                tmem_st8(scol + 8 * pp, old);
             }
             l *= fac;
             if (grow) m += xmax / P.scale_log2;
@@ -443,12 +474,77 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (fast && colbits != add_cols) refresh_add(colbits);
 
             STAMP(300 + c);
-            ok = ok && mbar_wait(bar_s, n & 1, abort_flag, P.wait_budget);     // also: every earlier product has finished
+            scol = trow + kColS + s_cols(n);
+            ok = ok && mbar_wait(bar_s_of(n), par_of(n), abort_flag, P.wait_budget);     // one score buffer: every earlier product has finished, too
             tc_fence_after();
             STAMP(310);
             if (!ok) { words[0] = 0u; words[1] = 0u; rowbits = 0u; dirty = 7u; }
 
             uint32_t stored = 0u;            // pieces of this chunk that hold probabilities (bit per piece)
+            // one 16-column piece on the general path: scores s, validity bits wd -> probabilities pk
+            auto generic_piece = [&](int pc, uint32_t (&s)[16], uint32_t wd, uint32_t (&pk)[8]) {
+                if (m == -INFINITY && wd != 0u) {           // first valid columns of this row: fix the stabiliser
+                    float mm = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if ((wd >> i) & 1u) mm = fmaxf(mm, __uint_as_float(s[i]));
+                    m = mm;
+                    add_cols = 0xffffffffu;                 // the addends of the fast path are stale now
+                }
+                const float mb = (m == -INFINITY) ? 0.f : m * P.scale_log2;
+                // A piece that lies inside every row's window (most pieces of a long 1-D window) needs no
+                // masks and no running maximum: two columns per packed instruction, and the row sum tells
+                // whether any probability may have outgrown its stabiliser (then the general form redoes it).
+                bool done = false;
+                if (__all_sync(0xffffffffu, wd == 0xFFFFu)) {
+                    const uint64_t sc2 = pack2(P.scale_log2, P.scale_log2), nb2 = pack2(-mb, -mb);
+                    uint64_t rr = 0ull;
+                    uint32_t pq[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint64_t xx = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), sc2, nb2);
+                        const float p0 = fast_exp2(lo_of(xx)), p1 = fast_exp2(hi_of(xx));
+                        rr = add2(rr, pack2(p0, p1));
+                        pq[i] = cvt_pack<BF16>(p0, p1);
+                    }
+                    const float rs = lo_of(rr) + hi_of(rr);
+                    if (!__any_sync(0xffffffffu, !(rs <= kGrowSum))) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) pk[i] = pq[i];
+                        l += rs;
+                        stored |= 1u << pc;
+                        done = true;
+                    }
+                }
+                if (!done) {
+                float x[16], xmax = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    x[i] = fmaf(__uint_as_float(s[i]), P.scale_log2, -mb);
+                    if (!((wd >> i) & 1u)) x[i] = -INFINITY;
+                    xmax = fmaxf(xmax, x[i]);
+                }
+                const bool grow = xmax > kGrow;
+                if (__any_sync(0xffffffffu, grow)) {
+                    rescale(grow, xmax, c, pc, stored);
+                    if (grow) {
+                        add_cols = 0xffffffffu;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) x[i] -= xmax;
+                    }
+                }
+                float r0 = 0.f, r1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float p0 = fast_exp2(x[2 * i]), p1 = fast_exp2(x[2 * i + 1]);
+                    r0 += p0;
+                    r1 += p1;
+                    pk[i] = cvt_pack<BF16>(p0, p1);
+                }
+                l += r0 + r1;
+                stored |= 1u << pc;
+                }
+            };
 #pragma unroll 1
             for (int pc = 0; pc < 4; ++pc) {
                 uint32_t pk[8];
@@ -460,7 +556,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #endif
                     if (__any_sync(0xffffffffu, rowok)) {
                         uint32_t s[16];
-                        tmem_ld16(trow + kColS + 16 * pc, s);
+                        tmem_ld16(scol + 16 * pc, s);
                         tmem_ld_wait();
 #if NATTEN_ABL == 3
 #pragma unroll
@@ -514,54 +610,20 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const uint32_t wd = ((pc & 2) ? words[1] : words[0]) >> (16 * (pc & 1)) & 0xFFFFu;
                     if (__any_sync(0xffffffffu, wd != 0u)) {
                         uint32_t s[16];
-                        tmem_ld16(trow + kColS + 16 * pc, s);
+                        tmem_ld16(scol + 16 * pc, s);
                         tmem_ld_wait();
-                        if (m == -INFINITY && wd != 0u) {           // first valid columns of this row: fix the stabiliser
-                            float mm = -INFINITY;
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                if ((wd >> i) & 1u) mm = fmaxf(mm, __uint_as_float(s[i]));
-                            m = mm;
-                            add_cols = 0xffffffffu;                 // the addends of the fast path are stale now
-                        }
-                        const float mb = (m == -INFINITY) ? 0.f : m * P.scale_log2;
-                        float x[16], xmax = -INFINITY;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            x[i] = fmaf(__uint_as_float(s[i]), P.scale_log2, -mb);
-                            if (!((wd >> i) & 1u)) x[i] = -INFINITY;
-                            xmax = fmaxf(xmax, x[i]);
-                        }
-                        const bool grow = xmax > kGrow;
-                        if (__any_sync(0xffffffffu, grow)) {
-                            rescale(grow, xmax, c, pc, stored);
-                            if (grow) {
-                                add_cols = 0xffffffffu;
-#pragma unroll
-                                for (int i = 0; i < 16; ++i) x[i] -= xmax;
-                            }
-                        }
-                        float r0 = 0.f, r1 = 0.f;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float p0 = fast_exp2(x[2 * i]), p1 = fast_exp2(x[2 * i + 1]);
-                            r0 += p0;
-                            r1 += p1;
-                            pk[i] = cvt_pack<BF16>(p0, p1);
-                        }
-                        l += r0 + r1;
-                        stored |= 1u << pc;
+                        generic_piece(pc, s, wd, pk);
                     } else {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) pk[i] = 0u;
                     }
                 }
                 // P over the scores it came from: piece pc lands in columns this thread has already read
-                tmem_st8(trow + kColS + 8 * pc, pk);
+                tmem_st8(scol + 8 * pc, pk);
             }
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(bar_p);
+            mbar_arrive(bar_p_of(n));
             STAMP(330);
             if (!mapped) {
                 ++ci[2];
