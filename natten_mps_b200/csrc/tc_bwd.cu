@@ -123,6 +123,15 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
     const uint32_t bar_tab_full = sbase + Smem::kBar + 128;   // [2] row table written
     const uint32_t bar_tab_empty = sbase + Smem::kBar + 144;  // [2] row table read by every compute thread and the MMA warp
     const uint32_t bar_rowfree = sbase + Smem::kBar + 176;    // every S / dP product of the tile finished: the row tiles are free
+    // At head dim 128 one CTA owns all 512 TMEM columns and 128 of them are spare: S and dP get a second buffer
+    // ([384,448) and [448,512), used by the odd chunks), so the products of chunk g + 1 run while the threads work
+    // on chunk g.  Each buffer has its own bar_s / bar_sp, completed once per two chunks.
+    constexpr bool kTwoBuf = DH == 128;
+    const uint32_t bar_s1 = sbase + Smem::kBar + 160, bar_sp1 = sbase + Smem::kBar + 168;
+    auto buf_cols = [&](unsigned g) -> uint32_t { return (kTwoBuf && (g & 1u)) ? 384u : 0u; };
+    auto bar_s_of = [&](unsigned g) -> uint32_t { return (kTwoBuf && (g & 1u)) ? bar_s1 : bar_s; };
+    auto bar_sp_of = [&](unsigned g) -> uint32_t { return (kTwoBuf && (g & 1u)) ? bar_sp1 : bar_sp; };
+    auto par_of = [&](unsigned g) -> uint32_t { return kTwoBuf ? ((g >> 1) & 1u) : (g & 1u); };
     float* stats = reinterpret_cast<float*>(smem + Smem::kStats);
 
     if (warp == kComputeWarps) {
@@ -136,6 +145,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             }
             mbar_init(bar_s, 2);                 // one commit per MMA stream
             mbar_init(bar_sp, kComputeWarps * 32);
+            mbar_init(bar_s1, 2);
+            mbar_init(bar_sp1, kComputeWarps * 32);
             for (int i = 0; i < 2; ++i) { mbar_init(bar_tab_full + 8 * i, 32); mbar_init(bar_tab_empty + 8 * i, kComputeWarps * 32 + 2); }
             mbar_init(bar_rowfree, 2);
             mbar_init_fence();
@@ -196,9 +207,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 // 32 bytes per k-step inside a 64-channel block; blocks are kRowHalf / kColHalf apart
 #pragma unroll
                 for (int ks = 0; ks < DH / 16; ++ks)
-                    mma_ss_e(tmem + col_out, dR + (((ks / 4) * kRowHalf + (ks % 4) * 32) >> 4),
+                    mma_ss_e(tmem + col_out + buf_cols(g), dR + (((ks / 4) * kRowHalf + (ks % 4) * 32) >> 4),
                              dC + (((ks / 4) * kColHalf + (ks % 4) * 32) >> 4), idesc_kk, ks > 0, leader);
-                mma_commit_e(bar_s, leader);
+                mma_commit_e(bar_s_of(g), leader);
                 if (cc + 1 == X.total) mma_commit_e(bar_rowfree, leader);      // the tile's last read of this stream's row tile
             };
             // k-step ks covers columns 16*ks..16*ks+15 of the chunk; their 16-bit pairs sit in the first 8 of
@@ -213,7 +224,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < kCols / 16; ++ks)
-                        mma_ts_e(tmem + (second ? kColA2 : kColA1), tmem + col_out + pair_col(ks), dC + 128 * ks, idesc_acc,
+                        mma_ts_e(tmem + (second ? kColA2 : kColA1), tmem + col_out + buf_cols(g) + pair_col(ks), dC + 128 * ks, idesc_acc,
                                  (accumulate || ks > 0) ? 1u : 0u, leader);
                 }
                 if (has_acc) mma_commit_e(bar_free + 8 * s, leader);     // the stage's column tiles (and statistics) may be replaced
@@ -238,12 +249,19 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 issue_s_dp(g, 0, T);
                 for (int cc = 0; cc < T.total && ok; ++cc, ++g) {
                     STAMP(200 + cc);
-                    ok = mbar_wait(bar_sp, g & 1, abort_flag, P.wait_budget);               // S/dP consumed, P/dS stored
+                    if (kTwoBuf && cc + 1 < T.total) {
+                        // two buffers: the next chunk's products go into the other buffer, whose P / dS were read
+                        // by products this warp issued earlier, so they need not wait for the threads
+                        ok = mbar_wait(bar_col + 8 * ((g + 1) % kStages), ((g + 1) / kStages) & 1, abort_flag, P.wait_budget);
+                        if (!ok) break;
+                        issue_s_dp(g + 1, cc + 1, T);
+                    }
+                    ok = mbar_wait(bar_sp_of(g), par_of(g), abort_flag, P.wait_budget);               // S/dP consumed, P/dS stored
                     if (!ok) break;
                     STAMP(210);
                     issue_acc(g, cc > 0);                                    // reads P/dS ...
                     STAMP(215);
-                    if (cc + 1 < T.total) {
+                    if (!kTwoBuf && cc + 1 < T.total) {
                         ok = mbar_wait(bar_col + 8 * ((g + 1) % kStages), ((g + 1) / kStages) & 1, abort_flag, P.wait_budget);
                         if (!ok) break;
                         STAMP(216);
@@ -482,6 +500,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
             auto col0 = [&](int h) { return kInner == 16 ? 16 * (piece + 2 * h) : 32 * piece + 16 * h; };
             auto dst0 = [&](int h) { return kInner == 16 ? 16 * (piece + 2 * h) : 32 * piece + 8 * h; };
             int ci[3] = {0, 0, 0};               // chunk index per axis, advanced without divisions
+            const bool line = line_chunks(P);    // chunks are runs of the innermost axis (1-D windows): cheap validity words
             uint32_t colmask[kPairs];            // separable geometry: 16-bit lane masks per column pair
             bool cols_any = false;
             int cached_c2 = -1;
@@ -554,10 +573,14 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                         }
                     }
                 } else {
-                    int jl[3], jh[3];
+                    if (line) {
+                        word = line_word(P, piece, ci, f, e);
+                    } else {
+                        int jl[3], jh[3];
 #pragma unroll
-                    for (int a = 0; a < 3; ++a) chunk_range(P, a, ci[a], f[a], e[a], jl[a], jh[a]);
-                    word = piece_word_ranges(P, piece, jl, jh);
+                        for (int a = 0; a < 3; ++a) chunk_range(P, a, ci[a], f[a], e[a], jl[a], jh[a]);
+                        word = piece_word_ranges(P, piece, jl, jh);
+                    }
                     mine[0] = (word & 0xFFFFu) != 0u;
                     mine[1] = (word >> 16) != 0u;
                 }
@@ -569,7 +592,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                 const bool separable = kInner > 0 && !extra;
                 const bool full = !separable && __all_sync(0xffffffffu, word == 0xffffffffu);
                 STAMP(310 + ((any[0] || any[1]) ? 1 : 0));
-                ok = ok && mbar_wait(bar_s, g & 1, abort_flag, P.wait_budget);      // also: the previous chunk's P/dS were consumed
+                ok = ok && mbar_wait(bar_s_of(g), par_of(g), abort_flag, P.wait_budget);      // also: the P/dS this buffer held were consumed
+                const uint32_t tbuf = trow + buf_cols(g);
                 if (kKeySide) ok = ok && mbar_wait(bar_stats + 8 * (g % kStages), (g / kStages) & 1, abort_flag, P.wait_budget);
                 tc_fence_after();
                 STAMP(320);
@@ -582,8 +606,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                         const float* stp = stats + (g % kStages) * 128 + col0(half);
                         const float4* st4 = reinterpret_cast<const float4*>(stp);
                         uint32_t s[16], dp[16];
-                        tmem_ld16(trow + kColS + col0(half), s);
-                        tmem_ld16(trow + kColDP + col0(half), dp);
+                        tmem_ld16(tbuf + kColS + col0(half), s);
+                        tmem_ld16(tbuf + kColDP + col0(half), dp);
                         tmem_ld_wait();
                         if (separable || full) {
                             // P = 2^(s*c - lse2), dS = P * (dP*scale - delta*scale); fp32, rounded once each
@@ -641,12 +665,12 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
                         for (int i = 0; i < 8; ++i) { pk_p[i] = 0u; pk_ds[i] = 0u; }
                     }
                     // the pairs overwrite columns this warp has already read (or will not read)
-                    tmem_st8(trow + kColDP + dst0(half), pk_ds);
-                    if (kKeySide) tmem_st8(trow + kColS + dst0(half), pk_p);
+                    tmem_st8(tbuf + kColDP + dst0(half), pk_ds);
+                    if (kKeySide) tmem_st8(tbuf + kColS + dst0(half), pk_p);
                 }
                 tmem_st_wait();
                 tc_fence_before();
-                mbar_arrive(bar_sp);
+                mbar_arrive(bar_sp_of(g));
                 STAMP(330);
                 // next chunk (innermost axis fastest; wraps to the next query head on the key side)
                 if (mapped) {

@@ -410,6 +410,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         l = 0.f;
         add_cols = 0xffffffffu;              // the addends belong to the previous tile's stabiliser
         int ci[3] = {0, 0, 0};
+        const bool line = line_chunks(P);    // chunks are runs of the innermost axis (1-D windows): cheap validity words
         int jl[3] = {0, 0, 0}, jh[3] = {0, 0, 0};
         uint32_t rowbits = 0u, colbits = 0u, dirty = 7u;     // 16-column rows: one bit per piece, one per column
         // 16-column rows with a single chunk along the innermost axis and at most 16 chunks: which pieces of
@@ -449,6 +450,10 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             } else if (mapped) {
                 rowbits = (uint32_t)(rowmap >> (4 * c)) & 15u;
             } else {
+                if (kInner == 0 && line) {
+#pragma unroll
+                    for (int pc = 0; pc < 2; ++pc) words[pc] = line_word(P, pc, ci, f, e);
+                } else {
 #pragma unroll
                 for (int a = 0; a < 3; ++a)
                     if ((dirty >> a) & 1u) chunk_range(P, a, ci[a], f[a], e[a], jl[a], jh[a]);
@@ -467,6 +472,7 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 } else {
 #pragma unroll
                     for (int pc = 0; pc < 2; ++pc) words[pc] = piece_word_ranges(P, pc, jl, jh);
+                }
                 }
                 dirty = 0u;
             }

@@ -523,6 +523,20 @@ __device__ __forceinline__ uint32_t low_bits(int n)
     return n <= 0 ? 0u : (n >= 32 ? 0xffffffffu : ((1u << n) - 1u));
 }
 
+// What piece_word_ranges gives, for chunks that are one run of the innermost axis (cb[0] == cb[1] == 1, not
+// interleaved along it): validity bits of columns [32*pc, 32*pc + 32) of chunk (ci[0], ci[1], ci[2]) for a row
+// whose window is [f, e) per axis.  A dozen instructions instead of the general form's ranges per axis.
+__device__ __forceinline__ bool line_chunks(const TcParams& P) { return P.cb[0] == 1 && P.cb[1] == 1 && P.il[2] == 1; }
+__device__ __forceinline__ uint32_t line_word(const TcParams& P, int pc, const int (&ci)[3], const int (&f)[3], const int (&e)[3])
+{
+    if (ci[0] < f[0] || ci[0] >= e[0] || ci[1] < f[1] || ci[1] >= e[1]) return 0u;
+    const int base = ci[2] * P.cb[2] + 32 * pc;
+    int lo = f[2] - base, hi = e[2] - base;
+    lo = lo > 0 ? lo : 0;
+    hi = hi < 32 ? hi : 32;
+    return hi > lo ? (low_bits(hi) & ~low_bits(lo)) : 0u;
+}
+
 // CTAs of a persistent launch: `per_sm` per multiprocessor, never more than there is work.
 inline unsigned persistent_grid(unsigned work, int per_sm)
 {

@@ -164,8 +164,8 @@ def test_tc_additional_tokens_match_simt(case, dtype):
 def test_tc_forward_rescales_when_later_chunks_dominate(spatial, ks, slope, D, dtype):
     """Scores that grow steeply along the key axis (`slope` per key along the innermost axis): later
     chunks of a tile raise the row maximum by far more than the stored probabilities may exceed their
-    stabiliser by (2^8 in the 128-channel kernel; 2^14 for fp16 and 2^60 for bf16 in the 64-channel
-    kernel, which the steep case exceeds), so the output accumulated in TMEM has to be rescaled."""
+    stabiliser by (2^14 for fp16 and 2^60 for bf16, which the steep case exceeds), so the output
+    accumulated in TMEM has to be rescaled."""
     rank = len(spatial)
     B, H = 2, 2
     g = torch.Generator(device="cpu").manual_seed(23)
