@@ -12,15 +12,17 @@
 // The row accumulators live in TMEM for the whole tile, so dK/dV are reduced in a
 // fixed order: results are bit-reproducible, no atomics.
 //
-// Chunks are 64 columns wide so that a CTA needs only 256 TMEM columns and 107 KB of
-// shared memory: two CTAs share an SM and one computes while the other waits for its
-// MMAs or loads.  The grid is persistent (CTAs walk the tiles), so barriers, TMEM and the
-// column-stage ring are set up once and the next tile's loads run ahead.  Warps: 8 compute
-// warps (two per TMEM lane quadrant, each owns one 32-column piece of the chunk), one TMA + MMA
-// issuing warp, one helper warp (per-row tables one tile ahead; column statistics on the key side).
-// TMEM: S [0,64)  dP [64,128)  acc1 [128,192)  acc2 [192,256).  The 16-bit P and dS that
-// feed the accumulating MMAs overwrite the first half of the S / dP columns of the piece
-// they were computed from (same warp, after it has read them).
+// Chunks are 64 columns wide so that, up to head dim 64, a CTA needs only 256 TMEM columns and 102 KB of
+// shared memory: two CTAs share an SM and one computes while the other waits for its MMAs or loads.  At head
+// dim 128 one CTA owns the SM's 512 columns; the 128 spare ones hold a second S / dP buffer, so that the
+// products of chunk g + 1 run while the threads work on chunk g.  The grid is persistent (CTAs walk the
+// tiles), so barriers, TMEM and the column-stage ring are set up once and the next tile's loads run ahead.
+// Warps: 8 compute warps (two per TMEM lane quadrant, each owns half of the chunk's columns), two MMA-issuing
+// warps (independent streams: dP / acc1 and S / acc2), one helper warp (per-axis tables one tile ahead, the
+// TMA loads, column statistics on the key side).
+// TMEM: S [0,64)  dP [64,128)  acc1 [128,128+D)  acc2 [128+D,128+2D); head dim 128: second S [384,448) and
+// dP [448,512).  The 16-bit P and dS that feed the accumulating MMAs overwrite the first half of the S / dP
+// columns of the piece they were computed from (same warp, after it has read them).
 #include "tc_kernels.cuh"
 
 #include "simt_kernels.cuh"
@@ -747,31 +749,40 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
 
 // delta[row] = sum_d out[row,d]*dout[row,d] - dlse[row]      (kPer threads per row, 16 bytes each, kPer the
 // power of two >= D/8; every thread takes kDeltaRows rows a grid-width apart, so that eight 16-byte loads
-// are in flight)
+// are in flight).  blockIdx.y picks a slab of `slab_rows` consecutive rows; with per-sample lengths of a 1-D
+// problem (lens != nullptr) a slab is one sample, row = position * heads + head inside it, and the rows past
+// the sample's length are not read: nothing attends from them, their delta is 0.
 constexpr int kDeltaRows = 4;
 template <int kPer, bool BF16>
 __global__ void __launch_bounds__(256)
 tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ dout,
-                const float* __restrict__ dlse, float* __restrict__ delta, long long rows, long long row_step, int D)
+                const float* __restrict__ dlse, float* __restrict__ delta, long long slab_rows, long long row_step, int D,
+                const int* __restrict__ lens, int heads)
 {
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long row0 = t / kPer;
+    const long long local0 = t / kPer;
     const int part = (int)(t % kPer);
     const bool mine = 8 * part < D;
+    const long long base = (long long)blockIdx.y * slab_rows;
+    long long live_rows = slab_rows;
+    if (lens) {
+        live_rows = (long long)lens[blockIdx.y] * heads;
+        live_rows = live_rows < slab_rows ? live_rows : slab_rows;
+    }
     uint4 a[kDeltaRows], g[kDeltaRows];
 #pragma unroll
     for (int r = 0; r < kDeltaRows; ++r) {
-        const long long row = row0 + r * row_step;
+        const long long local = local0 + r * row_step, row = base + local;
         a[r] = make_uint4(0, 0, 0, 0);
         g[r] = make_uint4(0, 0, 0, 0);
-        if (row < rows && mine) {
+        if (local < live_rows && mine) {
             a[r] = reinterpret_cast<const uint4*>(out + row * D)[part];
             g[r] = reinterpret_cast<const uint4*>(dout + row * D)[part];
         }
     }
 #pragma unroll
     for (int r = 0; r < kDeltaRows; ++r) {
-        const long long row = row0 + r * row_step;
+        const long long local = local0 + r * row_step, row = base + local;
         const uint32_t aw[4] = {a[r].x, a[r].y, a[r].z, a[r].w}, gw[4] = {g[r].x, g[r].y, g[r].z, g[r].w};
         float acc = 0.f;
 #pragma unroll
@@ -788,7 +799,7 @@ tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ d
         }
 #pragma unroll
         for (int o = 1; o < kPer; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (row < rows && part == 0) delta[row] = acc - (dlse ? dlse[row] : 0.f);
+        if (local < slab_rows && part == 0) delta[row] = local < live_rows ? acc - (dlse ? dlse[row] : 0.f) : 0.f;
     }
 }
 
@@ -873,13 +884,19 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
     const Geo& go = ex ? *ex->original : g;      // geometry of out / dout / lse as the caller holds them
     {
         const long long qrows = (long long)go.B * go.otot * go.Hq;
-        // rows handled per pass of the grid: a whole number of blocks, a quarter of the rows each
+        // per-sample lengths of a 1-D problem without output stride: one slab of rows per sample, rows past its
+        // length are skipped; otherwise the whole tensor is one slab
+        const int* lens = (go.extents && go.rank == 1 && go.otot == go.ltot && go.B <= 65535) ? go.extents : nullptr;
+        const long long slab_rows = lens ? go.otot * go.Hq : qrows;
+        const unsigned slabs = lens ? (unsigned)go.B : 1u;
+        // rows handled per pass of the grid: a whole number of blocks, a quarter of a slab's rows each
         auto run_delta = [&](auto per) {
             constexpr int kPer = decltype(per)::value;
             const long long rows_per_block = 256 / kPer;
-            const long long blocks = ((qrows + kDeltaRows - 1) / kDeltaRows + rows_per_block - 1) / rows_per_block;
-            tc_delta_kernel<kPer, BF16><<<(unsigned)blocks, 256, 0, s>>>(
-                (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, qrows, blocks * rows_per_block, g.D);
+            const long long blocks = ((slab_rows + kDeltaRows - 1) / kDeltaRows + rows_per_block - 1) / rows_per_block;
+            tc_delta_kernel<kPer, BF16><<<dim3((unsigned)blocks, slabs), 256, 0, s>>>(
+                (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, slab_rows, blocks * rows_per_block, g.D,
+                lens, go.Hq);
         };
         if (g.D <= 32) run_delta(std::integral_constant<int, 4>{});
         else if (g.D <= 64) run_delta(std::integral_constant<int, 8>{});
