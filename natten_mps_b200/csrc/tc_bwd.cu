@@ -753,7 +753,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
 // problem (lens != nullptr) a slab is one sample, row = position * heads + head inside it, and the rows past
 // the sample's length are not read: nothing attends from them, their delta is 0.
 constexpr int kDeltaRows = 4;
-template <int kPer, bool BF16>
+template <int kPer, bool BF16, bool kLens>
 __global__ void __launch_bounds__(256)
 tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ dout,
                 const float* __restrict__ dlse, float* __restrict__ delta, long long slab_rows, long long row_step, int D,
@@ -763,26 +763,30 @@ tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ d
     const long long local0 = t / kPer;
     const int part = (int)(t % kPer);
     const bool mine = 8 * part < D;
-    const long long base = (long long)blockIdx.y * slab_rows;
     long long live_rows = slab_rows;
-    if (lens) {
+    if constexpr (kLens) {   // this slab's rows are rows 0 .. slab_rows-1 from here on
+        const long long base = (long long)blockIdx.y * slab_rows;
+        out += base * D;
+        dout += base * D;
+        delta += base;
+        if (dlse) dlse += base;
         live_rows = (long long)lens[blockIdx.y] * heads;
         live_rows = live_rows < slab_rows ? live_rows : slab_rows;
     }
     uint4 a[kDeltaRows], g[kDeltaRows];
 #pragma unroll
     for (int r = 0; r < kDeltaRows; ++r) {
-        const long long local = local0 + r * row_step, row = base + local;
+        const long long local = local0 + r * row_step;
         a[r] = make_uint4(0, 0, 0, 0);
         g[r] = make_uint4(0, 0, 0, 0);
         if (local < live_rows && mine) {
-            a[r] = reinterpret_cast<const uint4*>(out + row * D)[part];
-            g[r] = reinterpret_cast<const uint4*>(dout + row * D)[part];
+            a[r] = reinterpret_cast<const uint4*>(out + local * D)[part];
+            g[r] = reinterpret_cast<const uint4*>(dout + local * D)[part];
         }
     }
 #pragma unroll
     for (int r = 0; r < kDeltaRows; ++r) {
-        const long long local = local0 + r * row_step, row = base + local;
+        const long long local = local0 + r * row_step;
         const uint32_t aw[4] = {a[r].x, a[r].y, a[r].z, a[r].w}, gw[4] = {g[r].x, g[r].y, g[r].z, g[r].w};
         float acc = 0.f;
 #pragma unroll
@@ -799,7 +803,7 @@ tc_delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ d
         }
 #pragma unroll
         for (int o = 1; o < kPer; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (local < slab_rows && part == 0) delta[row] = local < live_rows ? acc - (dlse ? dlse[row] : 0.f) : 0.f;
+        if (local < slab_rows && part == 0) delta[local] = (!kLens || local < live_rows) ? acc - (dlse ? dlse[local] : 0.f) : 0.f;
     }
 }
 
@@ -894,9 +898,14 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
             constexpr int kPer = decltype(per)::value;
             const long long rows_per_block = 256 / kPer;
             const long long blocks = ((slab_rows + kDeltaRows - 1) / kDeltaRows + rows_per_block - 1) / rows_per_block;
-            tc_delta_kernel<kPer, BF16><<<dim3((unsigned)blocks, slabs), 256, 0, s>>>(
-                (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, slab_rows, blocks * rows_per_block, g.D,
-                lens, go.Hq);
+            if (lens)
+                tc_delta_kernel<kPer, BF16, true><<<dim3((unsigned)blocks, slabs), 256, 0, s>>>(
+                    (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, slab_rows, blocks * rows_per_block, g.D,
+                    lens, go.Hq);
+            else
+                tc_delta_kernel<kPer, BF16, false><<<(unsigned)blocks, 256, 0, s>>>(
+                    (const uint16_t*)out, (const uint16_t*)dout, (const float*)dlse, delta, slab_rows, blocks * rows_per_block, g.D,
+                    nullptr, go.Hq);
         };
         if (g.D <= 32) run_delta(std::integral_constant<int, 4>{});
         else if (g.D <= 64) run_delta(std::integral_constant<int, 8>{});
