@@ -577,33 +577,42 @@ tc_fwd_small_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                             m = mm;
                             refresh_add(colbits);
                         }
-                        float x[16], xa = -INFINITY, xb = -INFINITY;
+                        // No running maximum in the common case: the probabilities are formed at once and their
+                        // row sum tells whether one of them may have outgrown the stabiliser; only then are the
+                        // exponents looked at one by one (and, if it is so, everything rescaled and redone).
                         const uint64_t sc2 = pack2(P.scale_log2, P.scale_log2);
-#pragma unroll
-                        for (int i = 0; i < 16; i += 2) {              // two columns per packed fp32 fma
-                            const uint64_t xx = fma2(pack2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, pack2(add[i], add[i + 1]));
-                            x[i] = lo_of(xx);
-                            x[i + 1] = hi_of(xx);
-                            xa = fmaxf(xa, x[i]);
-                            xb = fmaxf(xb, x[i + 1]);
-                        }
-                        const float xmax = fmaxf(xa, xb);
-                        const bool grow = rowok && xmax > kGrow;
-                        if (__any_sync(0xffffffffu, grow)) {
-                            rescale(grow, xmax, c, pc, stored);
-                            if (grow) {
-                                refresh_add(colbits);
-#pragma unroll
-                                for (int i = 0; i < 16; ++i) x[i] -= xmax;
-                            }
-                        }
-                        uint64_t rr = 0ull;                                 // two partial row sums
                         const uint32_t keep = rowok ? 0xffffffffu : 0u;     // rows outside their window store zeros
+                        uint64_t rr = 0ull;                                 // two partial row sums
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float p0 = fast_exp2(x[2 * i]), p1 = fast_exp2(x[2 * i + 1]);
+                        for (int i = 0; i < 8; ++i) {                       // two columns per packed fp32 fma
+                            const uint64_t xx = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), sc2, pack2(add[2 * i], add[2 * i + 1]));
+                            const float p0 = fast_exp2(lo_of(xx)), p1 = fast_exp2(hi_of(xx));
                             rr = add2(rr, pack2(p0, p1));
                             pk[i] = cvt_pack<BF16>(p0, p1) & keep;
+                        }
+                        if (__any_sync(0xffffffffu, rowok && !(lo_of(rr) + hi_of(rr) <= kGrowSum))) {
+                            float x[16], xmax = -INFINITY;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                x[i] = fmaf(__uint_as_float(s[i]), P.scale_log2, add[i]);
+                                xmax = fmaxf(xmax, x[i]);
+                            }
+                            const bool grow = rowok && xmax > kGrow;
+                            if (__any_sync(0xffffffffu, grow)) {
+                                rescale(grow, xmax, c, pc, stored);
+                                if (grow) {
+                                    refresh_add(colbits);
+#pragma unroll
+                                    for (int i = 0; i < 16; ++i) x[i] -= xmax;
+                                }
+                            }
+                            rr = 0ull;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float p0 = fast_exp2(x[2 * i]), p1 = fast_exp2(x[2 * i + 1]);
+                                rr = add2(rr, pack2(p0, p1));
+                                pk[i] = cvt_pack<BF16>(p0, p1) & keep;
+                            }
                         }
                         if (rowok) l += lo_of(rr) + hi_of(rr);
                         stored |= 1u << pc;

@@ -159,17 +159,22 @@ def test_tc_additional_tokens_match_simt(case, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
 @pytest.mark.parametrize("D", [64, 128])
-@pytest.mark.parametrize("spatial,ks,slope", [((700,), (255,), 12.0 / 128.0), ((40, 48), (13, 13), 1.0),
-                                              ((40, 48), (13, 13), 4.0)], ids=["1d", "2d", "2d_steep"])
-def test_tc_forward_rescales_when_later_chunks_dominate(spatial, ks, slope, D, dtype):
-    """Scores that grow steeply along the key axis (`slope` per key along the innermost axis): later
-    chunks of a tile raise the row maximum by far more than the stored probabilities may exceed their
-    stabiliser by (2^14 for fp16 and 2^60 for bf16, which the steep case exceeds), so the output
-    accumulated in TMEM has to be rescaled."""
+@pytest.mark.parametrize("spatial,ks,slope,axis", [((700,), (255,), 12.0 / 128.0, -1), ((40, 48), (13, 13), 1.0, -1),
+                                                   ((40, 48), (13, 13), 4.0, -1), ((48, 40), (7, 7), 12.0, 0)],
+                         ids=["1d", "2d", "2d_steep", "2d_k7_rows"])
+def test_tc_forward_rescales_when_later_chunks_dominate(spatial, ks, slope, axis, D, dtype):
+    """Scores that grow steeply along one key axis (`slope` per key along `axis`): later chunks of a tile
+    raise the row maximum by far more than the stored probabilities may exceed their stabiliser by (2^14
+    for fp16 and 2^60 for bf16, which the steep cases exceed), so the output accumulated in TMEM has to be
+    rescaled.  The 7 x 7 case ramps along the rows, which are the 16-column pieces of its chunks: the
+    rescale then happens on the kernel's 16-column fast path."""
     rank = len(spatial)
     B, H = 2, 2
     g = torch.Generator(device="cpu").manual_seed(23)
-    ramp = (torch.arange(spatial[-1], dtype=torch.float32) * slope).reshape((1,) * (rank - 1) + (spatial[-1], 1, 1))
+    axis = axis % rank
+    shape = [1] * rank + [1, 1]
+    shape[axis] = spatial[axis]
+    ramp = (torch.arange(spatial[axis], dtype=torch.float32) * slope).reshape(shape)
     q = torch.randn((B, *spatial, H, D), generator=g) * 0.1 + 1.0
     k = torch.randn((B, *spatial, H, D), generator=g) * 0.1 + ramp.unsqueeze(0) / (D ** 0.5)
     v = torch.randn((B, *spatial, H, D), generator=g)
