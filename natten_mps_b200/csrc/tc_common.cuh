@@ -97,12 +97,6 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
-// Pull a box into L2 only (no shared memory, no barrier): hides DRAM latency of a later load.
-__device__ __forceinline__ void tma_prefetch_l2_5d(const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4)
-{
-    asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global [%0, {%1, %2, %3, %4, %5}];"
-                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
-}
 // Tile store, shared memory -> global (bulk group of the issuing thread).  Rows of the box that fall outside
 // the tensor are not written.  The first coordinate times the element size must be a multiple of 16 bytes and
 // no coordinate may be negative.
@@ -116,10 +110,6 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // every bulk store of this thread has completed
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map)
-{
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
-}
 
 // ----------------------------------------------------------------------------- TMEM
 // One warp allocates / frees; `cols` is a power of two in [32, 512].

@@ -104,12 +104,6 @@ __device__ __forceinline__ void tma_store_heads(const CUtensorMap* map, uint32_t
     if (P.split_heads) tma_store_5d(map, src, c0 & (dh - 1), c0 / dh, c1, c2, c4);
     else tma_store_5d(map, src, c0, c1, c2, c3, c4);
 }
-__device__ __forceinline__ void tma_prefetch_heads(const CUtensorMap* map, const TcParams& P, int dh, int c0, int c1,
-                                                   int c2, int c3, int c4)
-{
-    if (P.split_heads) tma_prefetch_l2_5d(map, c0 & (dh - 1), c0 / dh, c1, c2, c4);
-    else tma_prefetch_l2_5d(map, c0, c1, c2, c3, c4);
-}
 
 // Chunks needed to cover `extent` columns along axis a (chunk extents are powers of two).
 __device__ __forceinline__ int chunks_along(const TcParams& P, int a, int extent)
