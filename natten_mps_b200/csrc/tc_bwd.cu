@@ -589,7 +589,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ 
 #if NATTEN_ABL == 2
                 const bool any[2] = {false, false};
 #else
-                const bool any[2] = {__any_sync(0xffffffffu, mine[0]), __any_sync(0xffffffffu, mine[1])};
+                const bool any[2] = {__any_sync(0xffffffffu, mine[0]) != 0, __any_sync(0xffffffffu, mine[1]) != 0};
 #endif
                 const bool separable = kInner > 0 && !extra;
                 const bool full = !separable && __all_sync(0xffffffffu, word == 0xffffffffu);
@@ -853,7 +853,6 @@ int launch_bwd(int dtype, const Geo& g, const Plan& plan, const void* q, const v
                void* dv, float* delta, cudaStream_t s, const Expanded* ex = nullptr)
 {
     const TcParams& p = plan.p;
-    const long long qrows = (long long)g.B * g.otot * g.Hq;
     // With an output stride the kernels run on the unit-stride geometry `g` over full-resolution copies of
     // dout / lse / delta (see expand_strided_kernel); the caller's arrays are only read to build them.
     const void* dout_k = ex ? ex->dout_full : dout;
